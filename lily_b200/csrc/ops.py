@@ -1,0 +1,288 @@
+"""Python faces of the CUDA kernels in this folder.
+
+Every function takes CUDA tensors, checks dtypes, shapes and contiguity, and launches on the
+current stream.  There is no CPU path and no library stand-in: a tensor that is not on a CUDA
+device, or a library that cannot be built, raises.  bfloat16 matrix products go to cuBLAS through
+``torch.mm`` where the reference's engine uses a library product (lily/layers/quantization/
+base.py:69-72); float32 products use this folder's own FFMA kernel so that no reduced-precision
+matrix mode can slip in.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from lily_b200.csrc import build as _build
+
+_F32, _BF16 = 0, 1
+_vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+
+_SIGNATURES = {
+    "lily_embed": [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
+    "lily_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _vp],
+    "lily_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
+    "lily_qk_norm_rope_write": [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                _i, _i, _i, _vp],
+    "lily_cast": [_vp, _i, _vp, _i, _sz, _vp],
+    "lily_gemm_fp32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "lily_argmax": [_vp, _vp, _i, _i, _vp],
+    "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+    "lily_sample": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+}
+
+_lib = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library():
+    """Loads (building first if needed) the kernel library and declares its entry points."""
+    global _lib
+    if _lib is None:
+        lib = _build.load()
+        for name, args in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = _i
+        lib.lily_attention_prefill_simt_rows.restype = _i
+        lib.lily_attention_decode_scratch_floats.argtypes = [_i, _i, _i, _i]
+        lib.lily_attention_decode_scratch_floats.restype = _sz
+        _lib = lib
+    return _lib
+
+
+def _call(name: str, *args) -> None:
+    lib = library()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise KernelError(f"{name}: {lib.lily_last_error().decode(errors='replace')}")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _F32
+    if t.dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _dev(*tensors) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelError("lily_b200 kernels run on a CUDA device only; got a tensor on " + str(t.device))
+        if not t.is_contiguous():
+            raise KernelError(f"kernels take contiguous tensors (shape {tuple(t.shape)}, strides {t.stride()})")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _i32(t: Optional[torch.Tensor], name: str):
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{name} must be int32, got {t.dtype}")
+    return _p(t)
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+# ------------------------------------------------------------------------------ elementwise
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows of ``table`` [vocab, hidden] at ``ids`` [tokens] as float32 (the residual stream)."""
+    _dev(table, ids, out)
+    n, (vocab, hidden) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _call("lily_embed", _p(table), _dt(table), _i32(ids, "ids"), _p(out), n, hidden, vocab, _stream())
+    return out
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, write_residual: bool = True,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``resid += delta`` (float32, in place when ``write_residual``), then RMSNorm with ``weight``.
+    With ``rows`` only those rows are normalised (and the residual is left as it is)."""
+    _dev(resid, delta, weight, rows, out)
+    if resid.dtype != torch.float32:
+        raise KernelError("the residual stream is float32")
+    hidden = resid.shape[-1]
+    m = resid.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        write_residual = False
+    if out is None:
+        out = torch.empty((m, hidden), dtype=out_dtype, device=resid.device)
+    if delta is not None and (delta.dtype != out.dtype or delta.shape != resid.shape):
+        raise KernelError(f"delta {delta.dtype} {tuple(delta.shape)} does not match out {out.dtype} / residual "
+                          f"{tuple(resid.shape)}")
+    if weight.numel() != hidden:
+        raise KernelError(f"norm gain has {weight.numel()} entries, rows have {hidden}")
+    _call("lily_add_rmsnorm", _p(resid), _p(delta), _p(weight), _p(out), _i32(rows, "rows"), m, hidden, float(eps),
+          int(write_residual), _dt(out), _dt(weight), _stream())
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+    _dev(gate_up, out)
+    n, two_i = gate_up.shape
+    if out is None:
+        out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _call("lily_silu_mul", _p(gate_up), _p(out), n, two_i // 2, _dt(gate_up), _stream())
+    return out
+
+
+def qk_norm_rope_write(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
+                       eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                       positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
+                       kv_layer: torch.Tensor, nq: int, nkv: int, d: int, rotary_dim: int, page_size: int,
+                       write_kv: bool = True, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-head RMSNorm of q and k (when gains are given), rotation by the tables, q to ``q_out``
+    [tokens, nq * d], k and v into the token's place in its page of ``kv_layer``."""
+    _dev(qkv, q_gain, k_gain, cos, sin, positions, token_req, block_table, kv_layer, q_out)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * d:
+        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(nq + 2 * nkv) * d}")
+    if kv_layer.dtype != qkv.dtype:
+        raise KernelError(f"cache dtype {kv_layer.dtype} differs from activations {qkv.dtype}")
+    if tuple(kv_layer.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError(f"cache layer shape {tuple(kv_layer.shape)} does not fit kv_heads={nkv} page={page_size} d={d}")
+    if cos is not None and (cos.dtype != torch.float32 or cos.shape[-1] != rotary_dim // 2):
+        raise KernelError("rotation tables must be float32 [positions, rotary_dim / 2]")
+    if q_gain is not None and q_gain.dtype != k_gain.dtype:
+        raise KernelError("q and k gains must share a dtype")
+    if q_out is None:
+        q_out = torch.empty((n, nq * d), dtype=qkv.dtype, device=qkv.device)
+    _call("lily_qk_norm_rope_write", _p(qkv), _p(q_gain), _p(k_gain), float(eps), _p(cos), _p(sin),
+          _i32(positions, "positions"), _i32(token_req, "token_req"), _i32(block_table, "block_table"),
+          block_table.shape[-1], _p(kv_layer), _p(q_out), n, nq, nkv, d, rotary_dim, page_size, int(write_kv),
+          _dt(qkv), _dt(q_gain) if q_gain is not None else _F32, _stream())
+    return q_out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    _dev(x)
+    if x.dtype == dtype:
+        return x
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _call("lily_cast", _p(x), _dt(x), _p(out), _dt(out), x.numel(), _stream())
+    return out
+
+
+# ------------------------------------------------------------------------------ matrix products
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x [M, K] . weight [N, K]^T (+ bias)``.  float32: this package's FFMA kernel.
+    bfloat16: cuBLAS with float32 accumulation; ``out_dtype=float32`` keeps the accumulator's
+    precision (used for the logits)."""
+    _dev(x, weight, bias)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or weight.dtype != x.dtype:
+        raise KernelError(f"linear: x {tuple(x.shape)} {x.dtype} against weight {tuple(weight.shape)} {weight.dtype}")
+    if x.dtype == torch.float32:
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        if bias is not None and bias.dtype != torch.float32:
+            raise KernelError("float32 linear takes a float32 bias")
+        _call("lily_gemm_fp32", _p(x), _p(weight), _p(bias), _p(out), m, n, k, k, n, _stream())
+        return out
+    if out_dtype == torch.float32:
+        out = torch.mm(x, weight.t(), out_dtype=torch.float32)
+        if bias is not None:
+            out += bias.float()
+        return out
+    if bias is not None:
+        return torch.addmm(bias.to(x.dtype), x, weight.t())
+    return torch.mm(x, weight.t())
+
+
+# ------------------------------------------------------------------------------ attention
+
+def prefill_tile_rows() -> int:
+    return int(library().lily_attention_prefill_simt_rows())
+
+
+def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
+                      prefix_lens: torch.Tensor, tile_req: torch.Tensor, tile_start: torch.Tensor, out: torch.Tensor,
+                      nq: int, nkv: int, d: int, page_size: int, scale: float, window: Optional[int] = None) -> None:
+    """Causal attention of each request's new tokens over its cached prefix and themselves.
+    ``q`` and ``out`` are [tokens, nq * d] indexed by ``cu_seqlens``; tiles list (request, offset)."""
+    _dev(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out)
+    if q.dtype != kv_layer.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q, cache and out must share a dtype")
+    _call("lily_attention_prefill_simt", _p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"),
+          block_table.shape[-1], _i32(cu_seqlens, "cu_seqlens"), _i32(prefix_lens, "prefix_lens"),
+          _i32(tile_req, "tile_req"), _i32(tile_start, "tile_start"), tile_req.numel(), nq, nkv, d, page_size,
+          int(window or 0), float(scale), _dt(q), _stream())
+
+
+def decode_scratch_floats(requests: int, nq: int, d: int, splits: int) -> int:
+    return int(library().lily_attention_decode_scratch_floats(requests, nq, d, splits))
+
+
+def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
+                     out: torch.Tensor, scratch: Optional[torch.Tensor], splits: int, nq: int, nkv: int, d: int,
+                     page_size: int, scale: float, window: Optional[int] = None) -> None:
+    """One query token per request (rows of ``q`` [requests, nq * d]) over ``seq_lens`` cached
+    positions, keys cut into ``splits`` ranges merged through ``scratch`` (float32)."""
+    _dev(q, kv_layer, block_table, seq_lens, out, scratch)
+    requests = q.shape[0]
+    if q.dtype != kv_layer.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q, cache and out must share a dtype")
+    need = decode_scratch_floats(requests, nq, d, splits)
+    if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
+        raise KernelError(f"attention_decode: scratch of {need} float32 needed")
+    _call("lily_attention_decode_simt", _p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"),
+          block_table.shape[-1], _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits, nq, nkv, d, page_size,
+          int(window or 0), float(scale), _dt(q), _stream())
+
+
+# ------------------------------------------------------------------------------ sampling
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _dev(logits, out)
+    if logits.dtype != torch.float32:
+        raise KernelError("argmax takes float32 logits")
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _call("lily_argmax", _p(logits), _i32(out, "out"), rows, vocab, _stream())
+    return out
+
+
+def apply_penalties(logits: torch.Tensor, entry_row: torch.Tensor, entry_token: torch.Tensor,
+                    entry_count: torch.Tensor, entry_bias: torch.Tensor, repetition: torch.Tensor,
+                    frequency: torch.Tensor, presence: torch.Tensor) -> None:
+    _dev(logits, entry_row, entry_token, entry_count, entry_bias, repetition, frequency, presence)
+    rows, vocab = logits.shape
+    _call("lily_apply_penalties", _p(logits), _i32(entry_row, "entry_row"), _i32(entry_token, "entry_token"),
+          _i32(entry_count, "entry_count"), _p(entry_bias), _p(repetition), _p(frequency), _p(presence),
+          entry_row.numel(), vocab, _stream())
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, uniform: torch.Tensor, want_logprob: bool = False):
+    """One token per row of float32 ``logits``; per-row parameters are float32 (``top_k`` int32).
+    Returns (tokens int32, logprobs float32 or None)."""
+    _dev(logits, temperature, top_k, top_p, min_p, uniform)
+    rows, vocab = logits.shape
+    for t, name in ((temperature, "temperature"), (top_p, "top_p"), (min_p, "min_p"), (uniform, "uniform")):
+        if t.dtype != torch.float32 or t.numel() != rows:
+            raise KernelError(f"sample: {name} must be float32 [rows]")
+    tokens = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    logprob = torch.empty((rows,), dtype=torch.float32, device=logits.device) if want_logprob else None
+    _call("lily_sample", _p(logits), _p(temperature), _i32(top_k, "top_k"), _p(top_p), _p(min_p), _p(uniform),
+          _p(tokens), _p(logprob), rows, vocab, _stream())
+    return tokens, logprob

@@ -1,0 +1,210 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+``ModelRunner`` owns the model, the cache manager and the scratch space.  ``step`` takes, for each
+request in it, that request's next tokens (a portion of a prompt cut anywhere, or one decoded
+token) and the places among them whose logits are wanted; it grows the requests' block tables,
+runs only the tokens it is given as one batch against the cache that earlier steps left, and
+returns float32 logits ``[wanted, vocab]`` in the order the entries and their ``want`` were given.
+Generation (scheduler, engine), the command line and trace replay all drive this one function.
+
+Takes the place of ``ModelRunner.forward(ForwardBatch)`` (lily/model_executor/model_runner.py:
+292-304) together with the batch preparation of lily/scheduler/schedule_batch.py:184-237; pool
+sizing follows model_runner.py:160-242.
+"""
+
+from __future__ import annotations
+
+import logging
+import time
+from typing import Any, Dict, List, Optional, Sequence
+
+import torch
+
+from lily_b200.cache.kv_cache import KVCacheManager, OutOfPages, bytes_per_token, pool_pages_from_memory
+from lily_b200.config.model_config import read_model_dir
+from lily_b200.config.registry import resolve_architecture
+from lily_b200.config.server_args import ServerArgs
+from lily_b200.engine.batch import StepBatch, StepEntry, Workspace, build_step_batch, order_entries
+from lily_b200.models.assembled import AssembledModel
+from lily_b200.parts.base import BuildContext, ModelSpec
+from lily_b200.weights.loader import CheckpointSource, load_model_weights
+
+logger = logging.getLogger(__name__)
+
+_DTYPES = {"auto": torch.bfloat16, "bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class _PinnedRing:
+    """A few pinned int32 buffers used in turn for the per-step metadata copy; a buffer is
+    reused only after the copy that read it has finished."""
+
+    def __init__(self, count: int = 4, ints: int = 1 << 16):
+        self.ints = ints
+        self.buffers = [torch.empty(ints, dtype=torch.int32, pin_memory=True) for _ in range(count)]
+        self.events: List[Optional[torch.cuda.Event]] = [None] * count
+        self.next = 0
+
+    def take(self, need: int):
+        if need > self.ints:
+            return None, -1
+        i = self.next
+        self.next = (i + 1) % len(self.buffers)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        return self.buffers[i], i
+
+    def mark(self, i: int) -> None:
+        if i >= 0:
+            ev = torch.cuda.Event()
+            ev.record()
+            self.events[i] = ev
+
+
+class ModelRunner:
+    def __init__(self, spec: ModelSpec, source: Any, args: ServerArgs, ops: Any = None):
+        if ops is None:
+            from lily_b200.csrc import ops as _ops
+            if not torch.cuda.is_available():
+                raise RuntimeError("lily_b200 runs on a CUDA device (B200, sm_100a) and has no CPU path")
+            _ops.library()                    # build / load now: a missing extension fails here, loudly
+            ops = _ops
+        self.args = args
+        self.spec = spec
+        self.device = torch.device(args.device)
+        self.dtype = _DTYPES[args.dtype]
+        self.context_len = int(args.context_length or spec.max_position)
+        self.page_size = args.page_size
+        if args.random_seed is not None:
+            torch.manual_seed(args.random_seed)
+        ctx = BuildContext(device=self.device, dtype=self.dtype, ops=ops, page_size=self.page_size,
+                           max_position=self.context_len)
+        t0 = time.time()
+        self.model = AssembledModel(spec, ctx)
+        moved = load_model_weights(self.model, source, self.dtype, self.device)
+        self.weight_bytes = moved
+        logger.info("loaded %s in %.1f s (%.2f GB on the device)", spec.architecture, time.time() - t0, moved / 1e9)
+
+        groups = self.model.cache_groups
+        if args.max_total_tokens is not None:
+            pages = -(-args.max_total_tokens // self.page_size)
+        else:
+            if self.device.type == "cuda":
+                torch.cuda.empty_cache()
+                free, total = torch.cuda.mem_get_info(self.device)
+            else:
+                free = total = 1 << 30
+            pages = pool_pages_from_memory(groups, self.dtype, self.page_size, free, total,
+                                           args.mem_fraction_static or 0.85)
+            if pages < 1:
+                raise RuntimeError("no memory left for the KV cache; raise --mem-fraction-static or give "
+                                   "--max-total-tokens")
+        self.max_requests = int(args.max_running_requests or min(max(pages, 1), 256))
+        self.cache = KVCacheManager(groups, self.model.state_needs, page_size=self.page_size, num_pages=pages,
+                                    max_requests=self.max_requests, max_context=self.context_len, dtype=self.dtype,
+                                    device=self.device)
+        logger.info("KV cache: %d pages of %d tokens (%.2f GB), %d request slots", pages, self.page_size,
+                    pages * self.page_size * bytes_per_token(groups, self.dtype) / 1e9, self.max_requests)
+        self.workspace = Workspace(self.device)
+        self.seq_lens: Dict[int, int] = {}
+        self._ring = _PinnedRing() if self.device.type == "cuda" else None
+        self._kv_heads = max((need.kv_heads for need, _ in groups), default=1)
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ---- construction ---------------------------------------------------------------
+
+    @classmethod
+    def from_model_dir(cls, args: ServerArgs, ops: Any = None) -> "ModelRunner":
+        cfg, gen = read_model_dir(args.model_path)
+        arch = resolve_architecture(cfg.get("architectures"))
+        config = arch.config_from_dict(cfg, gen, architecture=arch.name)
+        return cls(arch.build_spec(config), CheckpointSource(args.model_path), args, ops)
+
+    @classmethod
+    def from_random(cls, config_json: Dict[str, Any], seed: int, args: ServerArgs, ops: Any = None,
+                    std: float = 0.02, gain_jitter: float = 0.0) -> "ModelRunner":
+        """A model with seeded random weights drawn on the device, without a file."""
+        from lily_b200.weights.random_init import RandomSource, expected_tensors
+
+        arch = resolve_architecture(config_json.get("architectures"))
+        config = arch.config_from_dict(config_json, {}, architecture=arch.name)
+        store = torch.float32 if args.dtype == "float32" else torch.bfloat16
+        source = RandomSource(expected_tensors(config, arch), seed, store, args.device, std, gain_jitter)
+        return cls(arch.build_spec(config), source, args, ops)
+
+    # ---- requests --------------------------------------------------------------------
+
+    def open_request(self) -> int:
+        slot = self.cache.open_request()
+        self.seq_lens[slot] = 0
+        return slot
+
+    def close_request(self, slot: int) -> None:
+        self.cache.close_request(slot)
+        del self.seq_lens[slot]
+
+    def free_tokens(self) -> int:
+        return self.cache.free_tokens()
+
+    # ---- one step --------------------------------------------------------------------
+
+    def prepare(self, entries: Sequence[StepEntry], logit_rows_in_given_order: bool = True) -> StepBatch:
+        """Grows the block tables and packs the batch.  Raises ``OutOfPages`` before anything is
+        changed when the pool cannot hold the step."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        vocab = self.spec.vocab_size
+        seen = set()
+        for e in entries:
+            if e.slot not in self.seq_lens:
+                raise KeyError(f"request slot {e.slot} is not open")
+            if e.slot in seen:
+                raise ValueError(f"request slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if len(e.tokens) == 0:
+                raise ValueError("an entry brings at least one token")
+            if any(not (0 <= int(t) < vocab) for t in e.tokens):
+                raise ValueError(f"token id outside [0, {vocab})")
+            if self.seq_lens[e.slot] + len(e.tokens) > self.context_len:
+                raise ValueError(f"request would reach {self.seq_lens[e.slot] + len(e.tokens)} positions; "
+                                 f"the context length is {self.context_len}")
+        wants = [(e.slot, self.seq_lens[e.slot] + len(e.tokens)) for e in entries]
+        if not self.cache.can_grow(wants):
+            raise OutOfPages(f"step of {sum(len(e.tokens) for e in entries)} tokens does not fit: "
+                             f"{self.cache.free_pages()} pages free")
+        for slot, new_len in wants:
+            self.cache.grow(slot, new_len)
+        order = order_entries(entries)
+        ordered = [entries[i] for i in order]
+        prefix = [self.seq_lens[e.slot] for e in ordered]
+        offsets, run = {}, 0
+        for i, e in zip(order, ordered):
+            offsets[i] = run
+            run += len(e.tokens)
+        rows: List[int] = []
+        for i, e in enumerate(entries):
+            for w in e.want:
+                if not (0 <= w < len(e.tokens)):
+                    raise ValueError(f"wanted place {w} is outside the {len(e.tokens)} tokens of the entry")
+                rows.append(offsets[i] + int(w))
+        tables = [[self.cache.block_table(g, e.slot) for e in ordered] for g in range(len(self.cache.groups))]
+        need = 3 * run + 4 * len(entries) + 1 + len(rows) + sum(
+            len(entries) * max((len(t) for t in g), default=1) for g in tables) + 8
+        pinned, ring_index = self._ring.take(need) if self._ring is not None else (None, -1)
+        batch = build_step_batch(ordered, prefix, tables, self.device, kv_heads_for_splits=self._kv_heads,
+                                 workspace=self.workspace, pinned=pinned, logit_rows=rows)
+        if self._ring is not None:
+            self._ring.mark(ring_index)
+        return batch
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs one step and returns float32 logits ``[sum(len(e.want)), vocab]`` on the device."""
+        batch = self.prepare(entries)
+        with torch.no_grad():
+            logits = self.model.forward(batch, self.cache)
+        for e in entries:
+            self.seq_lens[e.slot] += len(e.tokens)
+            self.cache.advance(e.slot, self.seq_lens[e.slot])
+        self.steps_run += 1
+        self.tokens_run += batch.num_tokens
+        return logits

@@ -1,0 +1,172 @@
+"""Plain PyTorch statements of what each CUDA kernel computes, with the kernels' signatures.
+
+Two uses, both in tests only: (1) each kernel is compared with its function here on the GPU, at
+sizes other than the engine's; (2) handed to the engine as ``ops`` on the CPU they let the cache
+manager, batch packing, step function, scheduler and replay be tested without a device.  They
+compute in float32 and round once to the output dtype.  Nothing in ``lily_b200`` imports this.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+
+def library():
+    return None
+
+
+def embed(table, ids, out=None):
+    return table[ids.long()].float()
+
+
+def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_residual=True, out=None):
+    if rows is not None:
+        v = resid[rows.long()]
+        if delta is not None:
+            v = v + delta[rows.long()].float()
+    else:
+        if delta is not None:
+            if write_residual:
+                resid += delta.float()
+                v = resid
+            else:
+                v = resid + delta.float()
+        else:
+            v = resid
+    var = v.pow(2).mean(-1, keepdim=True)
+    return ((v * torch.rsqrt(var + eps)) * weight.float()).to(out_dtype)
+
+
+def silu_mul(gate_up, out=None):
+    i = gate_up.shape[1] // 2
+    g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
+    return ((g / (1 + torch.exp(-g))) * u).to(gate_up.dtype)
+
+
+def qk_norm_rope_write(qkv, q_gain, k_gain, eps, cos, sin, positions, token_req, block_table, kv_layer, nq, nkv, d,
+                       rotary_dim, page_size, write_kv=True, q_out=None):
+    n = qkv.shape[0]
+    x = qkv.float().view(n, nq + 2 * nkv, d)
+    q, k, v = x[:, :nq], x[:, nq:nq + nkv], x[:, nq + nkv:]
+
+    def norm(t, gain):
+        if gain is None:
+            return t
+        return (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)) * gain.float()
+
+    def rot(t):
+        if cos is None:
+            return t
+        half = rotary_dim // 2
+        c = cos[positions.long()].unsqueeze(1)
+        s = sin[positions.long()].unsqueeze(1)
+        x1, x2, rest = t[..., :half], t[..., half:rotary_dim], t[..., rotary_dim:]
+        return torch.cat((x1 * c - x2 * s, x2 * c + x1 * s, rest), dim=-1)
+
+    q = rot(norm(q, q_gain))
+    if write_kv:
+        k = rot(norm(k, k_gain))
+        pos = positions.long()
+        page = block_table[token_req.long(), pos // page_size].long()
+        within = pos % page_size
+        kv_layer[page, 0, :, within] = k.to(kv_layer.dtype)
+        kv_layer[page, 1, :, within] = v.to(kv_layer.dtype)
+    return q.reshape(n, nq * d).to(qkv.dtype)
+
+
+def cast(x, dtype):
+    return x.to(dtype)
+
+
+def linear(x, weight, bias=None, out_dtype=None):
+    out = x.float() @ weight.float().t()
+    if bias is not None:
+        out = out + bias.float()
+    return out.to(out_dtype or x.dtype)
+
+
+def prefill_tile_rows():
+    return 32
+
+
+def decode_scratch_floats(requests, nq, d, splits):
+    return requests * nq * splits * (d + 2) if splits > 1 else 0
+
+
+def _gather_kv(kv_layer, table_row, length, page_size):
+    pos = torch.arange(length, device=kv_layer.device)
+    page = table_row[(pos // page_size)].long()
+    k = kv_layer[page, 0, :, pos % page_size]          # [length, nkv, d]
+    v = kv_layer[page, 1, :, pos % page_size]
+    return k.float(), v.float()
+
+
+def _attend(q, k, v, q_pos, scale, window):
+    """q [rows, nq, d] at positions q_pos [rows]; k, v [keys, nkv, d] at positions 0..keys-1."""
+    rep = q.shape[1] // k.shape[1]
+    kk, vv = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+    s = torch.einsum("qhd,khd->hqk", q, kk) * scale
+    kpos = torch.arange(k.shape[0], device=q.device)
+    seen = kpos[None, :] <= q_pos[:, None]
+    if window:
+        seen &= kpos[None, :] > q_pos[:, None] - window
+    s = s.masked_fill(~seen[None], float("-inf"))
+    return torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vv)
+
+
+def attention_prefill(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out, nq, nkv, d,
+                      page_size, scale, window=None):
+    for r in sorted(set(tile_req.tolist())):
+        t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
+        prefix = int(prefix_lens[r])
+        k, v = _gather_kv(kv_layer, block_table[r], prefix + t1 - t0, page_size)
+        qpos = torch.arange(prefix, prefix + t1 - t0, device=q.device)
+        o = _attend(q[t0:t1].float().view(-1, nq, d), k, v, qpos, scale, window)
+        out[t0:t1] = o.reshape(t1 - t0, nq * d).to(out.dtype)
+
+
+def attention_decode(q, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv, d, page_size, scale,
+                     window=None):
+    for r in range(q.shape[0]):
+        n = int(seq_lens[r])
+        k, v = _gather_kv(kv_layer, block_table[r], n, page_size)
+        o = _attend(q[r:r + 1].float().view(1, nq, d), k, v, torch.tensor([n - 1], device=q.device), scale, window)
+        out[r] = o.reshape(nq * d).to(out.dtype)
+
+
+def argmax(logits, out=None):
+    return torch.argmax(logits, dim=-1).to(torch.int32)
+
+
+def apply_penalties(logits, entry_row, entry_token, entry_count, entry_bias, repetition, frequency, presence):
+    for e in range(entry_row.numel()):
+        r, t, c = int(entry_row[e]), int(entry_token[e]), int(entry_count[e])
+        v = logits[r, t]
+        if c > 0:
+            rep = repetition[r]
+            if rep != 1.0:
+                v = v / rep if v > 0 else v * rep
+            v = v - c * frequency[r] - presence[r]
+        logits[r, t] = v + entry_bias[e]
+
+
+def sample(logits, temperature, top_k, top_p, min_p, uniform, want_logprob=False):
+    import plain_impl
+
+    toks, lps = [], []
+    for r in range(logits.shape[0]):
+        t, k = float(temperature[r]), int(top_k[r])
+        if t == 0 or k == 1:
+            tok = int(torch.argmax(logits[r]))
+            lp = float(torch.log_softmax(logits[r].float(), -1)[tok])
+        else:
+            probs = plain_impl.filtered_probs(logits[r].cpu(), t, k, float(top_p[r]), float(min_p[r]))
+            tok = plain_impl.inverse_cdf_pick(probs, float(uniform[r]))
+            lp = float(torch.log(probs[tok]))
+        toks.append(tok)
+        lps.append(lp)
+    dev = logits.device
+    return (torch.tensor(toks, dtype=torch.int32, device=dev),
+            torch.tensor(lps, dtype=torch.float32, device=dev) if want_logprob else None)
