@@ -1,0 +1,289 @@
+"""Continuous batching above the step function.
+
+Each ``step()``:
+
+1. **decode**: every running request brings its last token.  If the pool cannot give the pages
+   these tokens need, the youngest running requests are *retracted*: everything they hold is
+   given back, their produced tokens are kept, and they go to the front of the waiting queue to
+   be run again over prompt + produced tokens (lily/scheduler/scheduler.py:374-380,399-417).
+2. **admit**: waiting requests are taken first come first served while request slots and a token
+   budget remain.  The budget is ``min(max_prefill_tokens, chunked_prefill_size, what the free
+   pages hold after one page is kept back for each running request)``; a request that needs more
+   than what is left takes what is left and stays at the front of the queue for the next step with
+   what it has cached (chunked prefill: scheduler.py:56-70,320-359,577-582).
+3. one batch of decode tokens and prompt portions goes through ``ModelRunner.step``; logits are
+   asked for at the decode tokens and at the last token of every portion that completes its prompt.
+4. sampled tokens are appended; a request finishes on ``max_new_tokens`` (``{"type": "length"}``),
+   on an eos or stop token unless ``ignore_eos`` (``{"type": "stop"}``), or when it fills the
+   context; a finished request gives back its pages and slot (lily/scheduler/schedule_batch.py:
+   88-97, scheduler.py:629-650).
+
+When pages run out: decode retracts as above; a waiting request simply waits; a request that
+could never fit (prompt beyond the context or beyond the whole pool) is refused when it is added
+(``{"type": "abort"}``), and a lone running request that cannot grow even with the pool to itself
+finishes with ``{"type": "length", "message": "KV cache exhausted"}``.
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Sequence
+
+from lily_b200.cache.pages import pages_for
+from lily_b200.engine.batch import StepEntry
+from lily_b200.sampling.params import SamplingParams
+from lily_b200.sampling.sampler import SampleRow, Sampler
+
+logger = logging.getLogger(__name__)
+
+
+@dataclass
+class Req:
+    rid: str
+    origin_input_ids: List[int]
+    sampling_params: SamplingParams
+    eos_token_ids: List[int]
+    seed: int = 0
+    output_ids: List[int] = field(default_factory=list)
+    output_logprobs: Optional[List[float]] = None
+    slot: Optional[int] = None
+    seq_len: int = 0                    # positions cached
+    extend_input_len: int = 0           # tokens this step brings
+    is_chunked: bool = False
+    finished_reason: Optional[dict] = None
+    retractions: int = 0
+
+    @property
+    def fill_ids(self) -> List[int]:
+        return self.origin_input_ids + self.output_ids
+
+    @property
+    def finished(self) -> bool:
+        return self.finished_reason is not None
+
+    def check_finished(self, context_len: int) -> Optional[dict]:
+        """lily/scheduler/schedule_batch.py:88-97, plus the context limit."""
+        if self.finished_reason is not None:
+            return self.finished_reason
+        p = self.sampling_params
+        if len(self.output_ids) >= p.max_new_tokens:
+            self.finished_reason = {"type": "length"}
+        elif self.output_ids and not p.ignore_eos and (
+                self.output_ids[-1] in set(self.eos_token_ids) | set(p.stop_token_ids)):
+            self.finished_reason = {"type": "stop", "value": self.output_ids[-1]}
+        elif len(self.origin_input_ids) + len(self.output_ids) >= context_len:
+            self.finished_reason = {"type": "length", "message": "context length reached"}
+        return self.finished_reason
+
+
+@dataclass
+class SchedulerOutput:
+    rid: str
+    output_ids: List[int]
+    prompt_tokens: int
+    completion_tokens: int
+    finished: bool
+    finish_reason: Optional[dict]
+    logprobs: Optional[List[float]] = None
+
+
+class Scheduler:
+    def __init__(self, runner: Any, *, max_prefill_tokens: int = 16384, chunked_prefill_size: int = 8192,
+                 max_running_requests: Optional[int] = None, eos_token_ids: Sequence[int] = (),
+                 random_seed: Optional[int] = None, sampler: Optional[Sampler] = None):
+        self.runner = runner
+        self.max_prefill_tokens = max_prefill_tokens
+        self.chunked_prefill_size = chunked_prefill_size
+        self.max_running_requests = min(max_running_requests or runner.max_requests, runner.max_requests)
+        self.eos_token_ids = list(eos_token_ids)
+        self.sampler = sampler or Sampler(runner.model.ctx.ops, runner.device)
+        self.base_seed = random_seed if random_seed is not None else int.from_bytes(os.urandom(8), "little")
+        self.waiting_queue: List[Req] = []
+        self.running: List[Req] = []
+        self.results: Dict[str, SchedulerOutput] = {}
+        self.on_token: Optional[Callable[[Req, int], None]] = None
+        self._arrivals = 0
+        self.prefill_tokens_computed = 0
+        self.decode_steps = 0
+        self.retractions = 0
+        self.last_batch: Dict[str, int] = {}
+
+    # ---- intake --------------------------------------------------------------------
+
+    def add_request(self, rid: str, input_ids: Sequence[int], sampling_params: Optional[SamplingParams] = None) -> Req:
+        params = sampling_params or SamplingParams()
+        seed = params.seed if params.seed is not None else (self.base_seed * 1000003 + self._arrivals)
+        self._arrivals += 1
+        req = Req(rid=rid, origin_input_ids=[int(t) for t in input_ids], sampling_params=params,
+                  eos_token_ids=self.eos_token_ids, seed=seed)
+        if params.logprobs:
+            req.output_logprobs = []
+        cache = self.runner.cache
+        n = len(req.origin_input_ids)
+        problem = None
+        if n == 0:
+            problem = "empty prompt"
+        elif n >= self.runner.context_len:
+            problem = f"prompt of {n} tokens leaves no room in the context of {self.runner.context_len}"
+        elif pages_for(n + 1, cache.page_size) > cache.num_pages:
+            problem = f"prompt of {n} tokens exceeds the whole KV pool ({cache.num_pages} pages of {cache.page_size})"
+        elif any(not (0 <= t < self.runner.spec.vocab_size) for t in req.origin_input_ids):
+            problem = "token id outside the vocabulary"
+        if problem:
+            req.finished_reason = {"type": "abort", "message": problem}
+            self._publish(req)
+            return req
+        self.waiting_queue.append(req)
+        return req
+
+    def abort_request(self, rid: str) -> None:
+        """lily/scheduler/scheduler.py:241-258: wherever the request is, what it holds goes back."""
+        for queue in (self.waiting_queue, self.running):
+            for req in list(queue):
+                if req.rid == rid:
+                    queue.remove(req)
+                    self._release(req)
+                    req.finished_reason = {"type": "abort", "message": "aborted"}
+                    self._publish(req)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting_queue or self.running)
+
+    # ---- bookkeeping ---------------------------------------------------------------
+
+    def _release(self, req: Req) -> None:
+        if req.slot is not None:
+            self.runner.close_request(req.slot)
+            req.slot = None
+        req.seq_len = 0
+
+    def _publish(self, req: Req) -> None:
+        self.results[req.rid] = SchedulerOutput(
+            rid=req.rid, output_ids=list(req.output_ids), prompt_tokens=len(req.origin_input_ids),
+            completion_tokens=len(req.output_ids), finished=req.finished, finish_reason=req.finished_reason,
+            logprobs=list(req.output_logprobs) if req.output_logprobs is not None else None)
+
+    def _retract(self, req: Req) -> None:
+        self._release(req)
+        req.is_chunked = False
+        req.extend_input_len = 0
+        req.retractions += 1
+        self.retractions += 1
+        self.waiting_queue.insert(0, req)
+        logger.info("retract: %s goes back to the queue (%d running)", req.rid, len(self.running))
+
+    # ---- decisions -----------------------------------------------------------------
+
+    def _decode_pages(self, reqs: Sequence[Req]) -> int:
+        cache = self.runner.cache
+        return sum(cache.pages_needed(r.slot, r.seq_len + 1) for r in reqs)
+
+    def _plan_decode(self) -> List[Req]:
+        """Running requests that decode this step, after retracting the youngest while the pool
+        cannot give every one of them its next position."""
+        cache = self.runner.cache
+        while self.running and self._decode_pages(self.running) > cache.free_pages():
+            if len(self.running) == 1:
+                req = self.running.pop()
+                self._release(req)
+                req.finished_reason = {"type": "length", "message": "KV cache exhausted"}
+                self._publish(req)
+                break
+            self._retract(self.running.pop())
+        return list(self.running)
+
+    def _plan_prefill(self, decoding: Sequence[Req]) -> List[Req]:
+        cache = self.runner.cache
+        page = cache.page_size
+        # pages the decode tokens take now, and one kept back per running request for its next page
+        free_pages = cache.free_pages() - self._decode_pages(decoding) - len(decoding)
+        budget = min(self.max_prefill_tokens, self.chunked_prefill_size)
+        slots = self.max_running_requests - len(decoding)
+        selected: List[Req] = []
+        for req in list(self.waiting_queue):
+            if slots <= 0 or budget <= 0 or free_pages <= 0:
+                break
+            needed = len(req.fill_ids) - req.seq_len
+            held = pages_for(req.seq_len, page)
+            room = (held + free_pages) * page - req.seq_len        # tokens the request could still cache
+            take = min(needed, budget, room)
+            if take <= 0:
+                break
+            req.extend_input_len = take
+            req.is_chunked = take < needed
+            selected.append(req)
+            budget -= take
+            slots -= 1
+            free_pages -= pages_for(req.seq_len + take, page) - held
+            if req.is_chunked:
+                break                      # the rest of this prompt comes before any later request
+        return selected
+
+    # ---- one step ------------------------------------------------------------------
+
+    def step(self) -> bool:
+        """Runs one batch.  Returns False when there was nothing to run."""
+        decoding = self._plan_decode()
+        prefilling = self._plan_prefill(decoding)
+        if not decoding and not prefilling:
+            if self.waiting_queue and not self.running:
+                # nothing runs and the head of the queue cannot start: it never will
+                req = self.waiting_queue.pop(0)
+                self._release(req)
+                req.finished_reason = {"type": "abort", "message": "request does not fit the KV pool"}
+                self._publish(req)
+                return True
+            return False
+        entries: List[StepEntry] = []
+        for req in decoding:
+            entries.append(StepEntry(req.slot, [req.output_ids[-1]], [0]))
+        for req in prefilling:
+            if req.slot is None:
+                req.slot = self.runner.open_request()
+            ids = req.fill_ids[req.seq_len:req.seq_len + req.extend_input_len]
+            entries.append(StepEntry(req.slot, ids, [] if req.is_chunked else [len(ids) - 1]))
+            self.waiting_queue.remove(req)
+        self.last_batch = {"decode": len(decoding), "prefill_requests": len(prefilling),
+                           "prefill_tokens": sum(r.extend_input_len for r in prefilling)}
+        logits = self.runner.step(entries)
+        self.decode_steps += len(decoding)
+        self.prefill_tokens_computed += self.last_batch["prefill_tokens"]
+
+        sampled = [r for r in decoding] + [r for r in prefilling if not r.is_chunked]
+        rows = [SampleRow(r.sampling_params, r.seed, len(r.output_ids),
+                          r.fill_ids if not r.sampling_params.plain else ()) for r in sampled]
+        tokens, logprobs = self.sampler(logits, rows)
+
+        for req in decoding:
+            req.seq_len += 1
+        for req in prefilling:
+            req.seq_len += req.extend_input_len
+        still_running: List[Req] = []
+        requeue: List[Req] = []
+        for i, req in enumerate(sampled):
+            req.output_ids.append(int(tokens[i]))
+            if req.output_logprobs is not None and logprobs is not None:
+                req.output_logprobs.append(float(logprobs[i]))
+            if self.on_token is not None:
+                self.on_token(req, int(tokens[i]))
+            if req.check_finished(self.runner.context_len):
+                self._release(req)
+                self._publish(req)
+            else:
+                still_running.append(req)
+        for req in prefilling:
+            if req.is_chunked:
+                req.is_chunked = False
+                requeue.append(req)
+        self.waiting_queue[:0] = requeue
+        self.running = still_running
+        return True
+
+    def run_to_completion(self, max_steps: int = 1 << 30) -> None:
+        steps = 0
+        while self.has_work() and steps < max_steps:
+            if not self.step():
+                break
+            steps += 1

@@ -1,0 +1,94 @@
+"""From logits to the next token of each request.
+
+Order as in lily/layers/sampler.py:34-133: penalties and bias on the logits, argmax when every
+row is greedy, else temperature, top-k, top-p, min-p and a draw, all in CUDA kernels
+(lily_b200/csrc/sampling.cu).  The draw's uniform number comes from ``uniform_for``: a counter
+generator keyed by the request's seed and the index of the token being drawn, so a request's
+tokens depend neither on the batch it is in nor on whether it was retracted and run again.
+"""
+
+from __future__ import annotations
+
+from collections import Counter
+from dataclasses import dataclass
+from typing import Any, List, Optional, Sequence, Tuple
+
+import torch
+
+from lily_b200.sampling.params import SamplingParams
+
+_MASK = (1 << 64) - 1
+
+
+def _splitmix64(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & _MASK
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & _MASK
+    return x ^ (x >> 31)
+
+
+def uniform_for(seed: int, index: int) -> float:
+    """A number in [0, 1) with 24 random bits, a pure function of (seed, index)."""
+    return (_splitmix64(_splitmix64(seed & _MASK) ^ (index & _MASK)) >> 40) / float(1 << 24)
+
+
+@dataclass
+class SampleRow:
+    params: SamplingParams
+    seed: int
+    index: int                         # how many tokens the request has produced so far
+    seen: Sequence[int] = ()           # prompt + produced tokens (for the penalties)
+
+
+class Sampler:
+    def __init__(self, ops: Any, device):
+        self.ops, self.device = ops, device
+
+    def __call__(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> Tuple[List[int], Optional[List[float]]]:
+        """``logits`` float32 [len(rows), vocab] on the device (modified in place by penalties).
+        Returns the tokens and, when any row asks for them, the chosen tokens' log-probabilities."""
+        if len(rows) == 0:
+            return [], None
+        assert logits.shape[0] == len(rows), (logits.shape, len(rows))
+        ops, dev = self.ops, self.device
+        if any(not r.params.plain for r in rows):
+            self._penalties(logits, rows)
+        need_lp = any(r.params.logprobs for r in rows)
+        if all(r.params.greedy for r in rows) and not need_lp:
+            return ops.argmax(logits).tolist(), None
+        f32 = dict(dtype=torch.float32, device=dev)
+        temperature = torch.tensor([0.0 if r.params.greedy else r.params.temperature for r in rows], **f32)
+        top_k = torch.tensor([r.params.top_k for r in rows], dtype=torch.int32, device=dev)
+        top_p = torch.tensor([r.params.top_p for r in rows], **f32)
+        min_p = torch.tensor([r.params.min_p for r in rows], **f32)
+        uniform = torch.tensor([uniform_for(r.seed, r.index) for r in rows], **f32)
+        tokens, logprobs = ops.sample(logits, temperature, top_k, top_p, min_p, uniform, want_logprob=need_lp)
+        return tokens.tolist(), (logprobs.tolist() if logprobs is not None else None)
+
+    def _penalties(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> None:
+        e_row: List[int] = []
+        e_tok: List[int] = []
+        e_cnt: List[int] = []
+        e_bias: List[float] = []
+        for i, r in enumerate(rows):
+            p = r.params
+            if p.plain:
+                continue
+            counts = Counter(r.seen) if (p.repetition_penalty != 1.0 or p.frequency_penalty or p.presence_penalty) else {}
+            bias = p.logit_bias or {}
+            for tok in set(counts) | set(bias):
+                e_row.append(i)
+                e_tok.append(tok)
+                e_cnt.append(counts.get(tok, 0))
+                e_bias.append(bias.get(tok, 0.0))
+        if not e_row:
+            return
+        dev = self.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.ops.apply_penalties(
+            logits, torch.tensor(e_row, **i32), torch.tensor(e_tok, **i32), torch.tensor(e_cnt, **i32),
+            torch.tensor(e_bias, **f32),
+            torch.tensor([r.params.repetition_penalty for r in rows], **f32),
+            torch.tensor([r.params.frequency_penalty for r in rows], **f32),
+            torch.tensor([r.params.presence_penalty for r in rows], **f32))

@@ -60,6 +60,8 @@ def run_mixed(runner: ModelRunner, requests: Dict[str, List[int]], plan: List[Di
             if name not in slots:
                 slots[name] = runner.open_request()
             toks = requests[name][done[name]:done[name] + n]
+            if not toks:
+                continue
             entries.append(StepEntry(slots[name], toks, list(range(len(toks)))))
             names.append(name)
             done[name] += len(toks)

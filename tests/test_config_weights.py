@@ -1,0 +1,139 @@
+"""Configuration, registry, safetensors reading and the loader's one error."""
+
+import json
+import os
+import tempfile
+
+import pytest
+import torch
+from safetensors.torch import load_file, save_file
+
+import tiny_models
+from lily_b200.config import (ConfigError, DenseDecoderConfig, ServerArgs, register_architecture,
+                              resolve_architecture, supported_architectures)
+from lily_b200.models.assembled import AssembledModel
+from lily_b200.parts.base import BuildContext, TensorSpec
+from lily_b200.weights.loader import CheckpointSource, WeightsError, check, kept_dtype, load_model_weights
+from lily_b200.weights.random_init import RandomSource, expected_tensors, write_random_model
+from lily_b200.weights.safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
+
+
+def test_config_reads_its_own_keys_with_the_reference_defaults():
+    c = DenseDecoderConfig.from_dict(tiny_models.TINY_LLAMA)
+    assert (c.num_hidden_layers, c.hidden_size, c.num_attention_heads, c.num_key_value_heads, c.head_dim) == (3, 128, 8, 2, 32)
+    assert c.rope_scaling.rope_type == "llama3" and c.rope_scaling.original_max_position_embeddings == 64
+    assert not c.qk_norm and not c.tie_word_embeddings and c.rms_norm_eps == 1e-5
+    q = DenseDecoderConfig.from_dict(tiny_models.ODD_QWEN3)
+    assert q.qk_norm and q.head_dim == 288 // 6 and q.rope_theta == 30000.0 and q.attention_bias
+    assert q.rope_scaling.rope_type == "default" and q.rotary_dim == 48
+    o = DenseDecoderConfig.from_dict(tiny_models.ODD_LLAMA)            # "type" is read as "rope_type"
+    assert o.rope_scaling.rope_type == "llama3" and o.rope_scaling.factor == 4.0
+    minimal = {"architectures": ["LlamaForCausalLM"], "hidden_size": 32, "num_hidden_layers": 1,
+               "num_attention_heads": 4, "intermediate_size": 64, "vocab_size": 100}
+    m = DenseDecoderConfig.from_dict(minimal, {"eos_token_id": [2, 3]})
+    assert (m.num_key_value_heads, m.head_dim, m.rope_theta, m.rms_norm_eps, m.max_position_embeddings) == (4, 8, 10000.0, 1e-6, 4096)
+    assert m.eos_token_ids == [2, 3] and not m.tie_word_embeddings
+    assert DenseDecoderConfig.from_dict(m.to_hf_dict()) == m
+    nested = {"architectures": ["Qwen3ForCausalLM"], "text_config": dict(minimal, eos_token_id=7)}
+    assert DenseDecoderConfig.from_dict(nested).eos_token_ids == [7]
+
+
+@pytest.mark.parametrize("patch,msg", [
+    ({"hidden_act": "gelu"}, "Unsupported activation"), ({"num_key_value_heads": 3}, "multiple"),
+    ({"vocab_size": None}, "vocab_size"), ({"rope_scaling": {"rope_type": "yarn", "factor": 2}}, "yarn"),
+    ({"rope_scaling": {"rope_type": "llama3", "factor": 2}}, "low_freq_factor"),
+    ({"partial_rotary_factor": 0.3}, "rotary_dim"), ({"num_hidden_layers": 0}, "positive")])
+def test_config_errors(patch, msg):
+    bad = dict(tiny_models.TINY_LLAMA, **patch)
+    with pytest.raises(ConfigError, match=msg):
+        DenseDecoderConfig.from_dict(bad)
+
+
+def test_registry():
+    assert supported_architectures() == ["LlamaForCausalLM", "Qwen3ForCausalLM"]
+    assert resolve_architecture(["Nope", "Qwen3ForCausalLM"]).name == "Qwen3ForCausalLM"
+    with pytest.raises(ValueError, match="No registered model.*LlamaForCausalLM"):
+        resolve_architecture(["GPT2LMHeadModel"])
+
+
+def test_server_args_flags_and_checks():
+    a = ServerArgs.parse(["--model-path", "x", "--dtype", "float32", "--chunked-prefill-size", "64",
+                          "--max-total-tokens", "4096", "--disable-cuda-graph", "--cuda-graph-bs", "1", "8"])
+    assert (a.model_path, a.dtype, a.chunked_prefill_size, a.max_total_tokens, a.disable_cuda_graph, a.cuda_graph_bs) == \
+        ("x", "float32", 64, 4096, True, [1, 8])
+    assert a.max_prefill_tokens == 16384 and a.schedule_policy == "fcfs"
+    for kw in ({"mem_fraction_static": 1.5}, {"dtype": "float16"}, {"schedule_policy": "lpm"}, {"page_size": 48},
+               {"chunked_prefill_size": 0}):
+        with pytest.raises(ValueError):
+            ServerArgs(**kw)
+
+
+def test_safetensors_round_trip_against_the_library():
+    g = torch.Generator().manual_seed(0)
+    tensors = {"a.weight": torch.randn(3, 5, generator=g), "b": torch.randn(7, generator=g).bfloat16(),
+               "t": torch.arange(6, dtype=torch.int32).view(2, 3), "empty": torch.zeros(0, 4)}
+    with tempfile.TemporaryDirectory() as tmp:
+        mine, theirs = os.path.join(tmp, "mine.safetensors"), os.path.join(tmp, "theirs.safetensors")
+        write_safetensors(mine, tensors, {"k": "v"})
+        save_file(tensors, theirs)
+        back = load_file(mine)                                   # the library reads what this package wrote
+        f = SafetensorsFile(theirs)                              # this package reads what the library wrote
+        for k, v in tensors.items():
+            assert torch.equal(back[k], v) and torch.equal(f.tensor(k), v) and f.entries[k] == (v.dtype, tuple(v.shape))
+        assert SafetensorsFile(mine).metadata == {"k": "v"}
+        with open(os.path.join(tmp, "bad.safetensors"), "wb") as fh:
+            fh.write(b"\xff" * 16)
+        with pytest.raises(SafetensorsError):
+            SafetensorsFile(os.path.join(tmp, "bad.safetensors"))
+
+
+def test_loader_lists_missing_unexpected_and_wrong_shapes_in_one_error():
+    cfg = tiny_models.TINY_QWEN3
+    w = tiny_models.make_weights(cfg, 1)
+    del w["model.layers.1.mlp.up_proj.weight"], w["model.norm.weight"]
+    w["model.layers.0.self_attn.q_norm.weight"] = torch.zeros(17)
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)      # ignorable (llama.py:217-218)
+    w["lm_head.weight"] = torch.zeros(256, 64)                              # ignorable when tied
+    w["model.layers.0.self_attn.extra"] = torch.zeros(2)
+    with tempfile.TemporaryDirectory() as tmp:
+        tiny_models.write_model_dir(tmp, cfg, w)
+        arch = resolve_architecture(cfg["architectures"])
+        model = AssembledModel(arch.build_spec(arch.config_from_dict(cfg, {}, architecture=arch.name)),
+                               BuildContext(torch.device("cpu"), torch.float32, None, max_position=8))
+        with pytest.raises(WeightsError) as e:
+            load_model_weights(model, CheckpointSource(tmp), torch.float32, "cpu")
+    err = e.value
+    assert err.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
+    assert err.unexpected == ["model.layers.0.self_attn.extra"]
+    assert err.wrong_shape == [("model.layers.0.self_attn.q_norm.weight", (17,), (16,))]
+    text = str(err)
+    for needle in ("2 missing", "model.norm.weight", "1 unexpected", "self_attn.extra", "wrong shape", "[17]", "[16]"):
+        assert needle in text
+    with pytest.raises(FileNotFoundError):
+        CheckpointSource(tempfile.mkdtemp())
+
+
+def test_kept_dtypes():
+    mat, vec, tab = TensorSpec((2, 2)), TensorSpec((2,), role="vector"), TensorSpec((2,), role="table")
+    bf, f32 = torch.bfloat16, torch.float32
+    assert kept_dtype(mat, bf, bf) == bf and kept_dtype(mat, f32, bf) == bf and kept_dtype(mat, bf, f32) == f32
+    assert kept_dtype(vec, f32, bf) == f32 and kept_dtype(vec, bf, bf) == bf      # 32-bit stays 32-bit
+    assert kept_dtype(tab, torch.int64, bf) == torch.int32
+
+
+def test_random_weights_mode_writes_a_loadable_folder():
+    with tempfile.TemporaryDirectory() as tmp:
+        write_random_model(tmp, tiny_models.TINY_LLAMA, seed=4, dtype="bfloat16", gain_jitter=0.01)
+        cfg = json.load(open(os.path.join(tmp, "config.json")))
+        assert cfg["torch_dtype"] == "bfloat16" and cfg["num_hidden_layers"] == 3
+        a = load_file(os.path.join(tmp, "model.safetensors"))
+        arch = resolve_architecture(cfg["architectures"])
+        specs = expected_tensors(arch.config_from_dict(cfg, {}, architecture=arch.name), arch)
+        assert set(a) == set(specs) and all(tuple(a[k].shape) == specs[k].shape for k in a)
+        assert all(v.dtype == torch.bfloat16 for v in a.values())
+        assert abs(float(a["model.embed_tokens.weight"].float().std()) - 0.02) < 2e-3
+        assert abs(float(a["model.norm.weight"].float().mean()) - 1.0) < 0.01
+        # the same seed gives the same tensors whatever else is made; another seed differs
+        src = RandomSource(specs, 4, torch.bfloat16, gain_jitter=0.01)
+        assert torch.equal(src.get("lm_head.weight"), a["lm_head.weight"])
+        assert not torch.equal(RandomSource(specs, 5, torch.bfloat16).get("lm_head.weight"), a["lm_head.weight"])

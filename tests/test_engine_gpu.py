@@ -1,0 +1,83 @@
+"""The engine on the GPU against the plain implementation, in float32 and in bfloat16: whole
+requests, most of a request in one step and the last 32 tokens one by one, portions of changing
+size down to two tokens, and mixed batches over so few pages that they are used again."""
+
+import tempfile
+
+import pytest
+import torch
+
+import plain_impl
+import tiny_models
+from harness import make_runner, model_dir, run_mixed, run_portions, run_whole
+
+pytestmark = pytest.mark.gpu
+
+# float32: rounding only.  bfloat16: activations carry 8 bits; with logits of order one the
+# expected error is a few 1e-3 and the bound below is ten times that.
+TOL = {"float32": 1e-4, "bfloat16": 4e-2}
+MEAN_TOL = {"float32": 1e-5, "bfloat16": 6e-3}
+
+
+def rounded(weights, dtype):
+    """What the engine holds: matrices in the compute dtype, float32 gains kept."""
+    if dtype == "float32":
+        return weights
+    return {k: (v if v.dim() == 1 and "bias" not in k else v.bfloat16().float()) for k, v in weights.items()}
+
+
+def close(got, want, dtype, what=""):
+    err = (got - want).abs()
+    assert float(err.max()) < TOL[dtype], f"{what}: max error {float(err.max()):.3e} at {int(err.argmax()) // want.shape[1]}"
+    assert float(err.mean()) < MEAN_TOL[dtype], f"{what}: mean error {float(err.mean()):.3e}"
+
+
+@pytest.fixture(scope="module", params=["tiny_qwen3", "tiny_llama", "odd_qwen3", "odd_llama"])
+def setup(request):
+    cfg = tiny_models.CONFIGS[request.param]
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 31, tmp)
+        yield cfg, weights, path
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_decode_and_portions(setup, dtype):
+    cfg, weights, path = setup
+    ids = tiny_models.random_tokens(150, cfg["vocab_size"], 3)
+    want = plain_impl.all_logits(cfg, rounded(weights, dtype), ids)
+    runner = make_runner(path, dtype=dtype, device="cuda", page_size=16, max_tokens=160)
+    close(run_whole(runner, ids), want, dtype, "whole")
+    close(run_portions(runner, ids, [118] + [1] * 32), want, dtype, "last 32 one by one")
+    close(run_portions(runner, ids, [8, 2, 30, 17, 2, 3, 40, 2, 5]), want, dtype, "portions")
+    close(run_portions(runner, ids, [1, 1, 1, 2, 1]), want, dtype, "first tokens")
+    assert runner.cache.held_pages() == [0] * len(runner.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_reuse_pages(setup, dtype):
+    cfg, weights, path = setup
+    v = cfg["vocab_size"]
+    reqs = {"a": tiny_models.random_tokens(50, v, 5), "b": tiny_models.random_tokens(37, v, 6),
+            "c": tiny_models.random_tokens(20, v, 7), "d": tiny_models.random_tokens(41, v, 8),
+            "e": tiny_models.random_tokens(30, v, 9)}
+    plan = [{"a": 30}, {"a": 1, "b": 20}, {"b": 17, "a": 1, "c": 20}, {"a": 18, "d": 2}, {"d": 39, "e": 7},
+            {"e": 1}, {"e": 22}]
+    ends = {2: ["c", "b"], 3: ["a"], 4: ["d"]}
+    runner = make_runner(path, dtype=dtype, device="cuda", page_size=16, max_tokens=9 * 16)
+    got = run_mixed(runner, reqs, plan, ends)
+    for name, ids in reqs.items():
+        close(got[name], plain_impl.all_logits(cfg, rounded(weights, dtype), ids), dtype, name)
+    assert runner.cache.held_pages() == [0] * len(runner.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_with_four_live_requests(setup, dtype):
+    cfg, weights, path = setup
+    v, ctx = cfg["vocab_size"], cfg["max_position_embeddings"]
+    n = min(ctx, 230)
+    reqs = {k: tiny_models.random_tokens(n - 7 * i, v, 40 + i) for i, k in enumerate("abcd")}
+    plan = [{"a": 3, "b": 64, "c": 2, "d": 17}] + [{k: 1 for k in "abcd"}] * (n - 3)
+    runner = make_runner(path, dtype=dtype, device="cuda", page_size=16, max_tokens=4 * 240)
+    got = run_mixed(runner, reqs, plan)
+    for name, ids in reqs.items():
+        close(got[name], plain_impl.all_logits(cfg, rounded(weights, dtype), ids), dtype, name)

@@ -1,0 +1,268 @@
+"""Each CUDA kernel alone against its plain PyTorch statement (tests/kernel_refs.py), at sizes
+other than the engine's: odd widths, head sizes in steps of 16, any grouping, windows, page edges."""
+
+import pytest
+import torch
+
+import kernel_refs as ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def ops():
+    from lily_b200.csrc import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(64, 256), (136, 331), (4096, 1009)])
+def test_embed(dtype, hidden, vocab):
+    g = torch.Generator(device=DEV).manual_seed(0)
+    table = torch.randn(vocab, hidden, device=DEV, generator=g).to(dtype)
+    ids = torch.randint(0, vocab, (37,), device=DEV, generator=g, dtype=torch.int32)
+    assert torch.equal(ops().embed(table, ids), ref.embed(table, ids))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("wdtype", DTYPES)
+@pytest.mark.parametrize("hidden", [64, 136, 1000, 4096, 12288])
+def test_add_rmsnorm(dtype, wdtype, hidden):
+    if dtype == torch.float32 and wdtype == torch.bfloat16:
+        pytest.skip("float32 activations keep float32 gains")
+    g = torch.Generator(device=DEV).manual_seed(1)
+    n = 19
+    resid = torch.randn(n, hidden, device=DEV, generator=g) * 3
+    delta = torch.randn(n, hidden, device=DEV, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV, generator=g)).to(wdtype)
+    for d in (delta, None):
+        r1, r2 = resid.clone(), resid.clone()
+        got = ops().add_rmsnorm(r1, d, w, 1e-5, dtype)
+        want = ref.add_rmsnorm(r2, d, w, 1e-5, dtype)
+        torch.testing.assert_close(r1, r2, atol=0, rtol=0)
+        torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    rows = torch.tensor([18, 0, 7, 7], device=DEV, dtype=torch.int32)
+    r1 = resid.clone()
+    got = ops().add_rmsnorm(r1, delta, w, 1e-6, dtype, rows=rows)
+    want = ref.add_rmsnorm(resid.clone(), delta, w, 1e-6, dtype, rows=rows)
+    assert torch.equal(r1, resid)                       # gathered rows leave the residual alone
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [128, 200, 352, 12288])
+def test_silu_mul(dtype, inter):
+    g = torch.Generator(device=DEV).manual_seed(2)
+    gu = (torch.randn(23, 2 * inter, device=DEV, generator=g) * 2).to(dtype)
+    torch.testing.assert_close(ops().silu_mul(gu).float(), ref.silu_mul(gu).float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (7, 331, 136), (65, 129, 200), (33, 1009, 4096), (300, 24, 17)])
+def test_gemm_fp32_is_true_fp32(m, n, k):
+    g = torch.Generator(device=DEV).manual_seed(3)
+    x = torch.randn(m, k, device=DEV, generator=g)
+    w = torch.randn(n, k, device=DEV, generator=g)
+    b = torch.randn(n, device=DEV, generator=g)
+    want = (x.double() @ w.double().t() + b.double()).float()
+    got = ops().linear(x, w, b)
+    # float32 accumulation error grows like sqrt(k) * 2^-24 * |x||w|; TF32 would be ~1e-3 relative
+    assert float((got - want).abs().max()) < 4e-6 * (k ** 0.5) * 4
+    # a row's result does not depend on the other rows in the batch
+    assert torch.equal(ops().linear(x[:1].contiguous(), w, b), got[:1])
+
+
+def test_linear_bf16_and_fp32_logits():
+    g = torch.Generator(device=DEV).manual_seed(4)
+    x = torch.randn(9, 136, device=DEV, generator=g).bfloat16()
+    w = torch.randn(331, 136, device=DEV, generator=g).bfloat16()
+    b = torch.randn(331, device=DEV, generator=g).bfloat16()
+    want = x.float() @ w.float().t()
+    torch.testing.assert_close(ops().linear(x, w).float(), want, atol=0.1, rtol=2e-2)
+    out = ops().linear(x, w, out_dtype=torch.float32)
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out, want, atol=1e-3, rtol=1e-4)       # logits keep the accumulator's precision
+    # the product may be rounded to bfloat16 before the bias is added: half an ulp at its magnitude (~64)
+    torch.testing.assert_close(ops().linear(x, w, b).float(), want + b.float(), atol=0.5, rtol=2e-2)
+
+
+def _cache(pages, nkv, page_size, d, dtype, g):
+    return (torch.randn(pages + 1, 2, nkv, page_size, d, device=DEV, generator=g)).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rd,norm", [(4, 2, 16, 16, True), (8, 2, 32, 32, False), (6, 2, 48, 24, True),
+                                               (5, 1, 80, 80, False), (32, 8, 128, 128, True), (3, 3, 256, 64, True)])
+def test_qk_norm_rope_write(dtype, nq, nkv, d, rd, norm):
+    g = torch.Generator(device=DEV).manual_seed(5)
+    page, n, reqs = 16, 50, 3
+    qkv = torch.randn(n, (nq + 2 * nkv) * d, device=DEV, generator=g).to(dtype)
+    token_req = torch.tensor([i % reqs for i in range(n)], device=DEV, dtype=torch.int32)
+    # distinct (request, position) pairs so that no two tokens write the same place
+    positions = torch.arange(n, device=DEV, dtype=torch.int32) + 3
+    table = (torch.randperm(reqs * 6, device=DEV, generator=g) + 1).view(reqs, 6).to(torch.int32)
+    cos = torch.rand(128, rd // 2, device=DEV, generator=g)
+    sin = torch.rand(128, rd // 2, device=DEV, generator=g)
+    qg = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)).to(dtype) if norm else None
+    kg = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)).to(dtype) if norm else None
+    c1 = _cache(18, nkv, page, d, dtype, g)
+    c0, c2 = c1.clone(), c1.clone()
+    got = ops().qk_norm_rope_write(qkv, qg, kg, 1e-6, cos, sin, positions, token_req, table, c1, nq, nkv, d, rd, page)
+    want = ref.qk_norm_rope_write(qkv, qg, kg, 1e-6, cos, sin, positions, token_req, table, c2, nq, nkv, d, rd, page)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    torch.testing.assert_close(c1.float(), c2.float(), **tol(dtype))
+    assert not torch.equal(c1, c0)
+    # without rotation tables and without the cache write
+    c3 = c1.clone()
+    got = ops().qk_norm_rope_write(qkv, qg, kg, 1e-6, None, None, positions, token_req, table, c3, nq, nkv, d, 0, page,
+                                   write_kv=False)
+    want = ref.qk_norm_rope_write(qkv, qg, kg, 1e-6, None, None, positions, token_req, table, c2.clone(), nq, nkv, d,
+                                  0, page, write_kv=False)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    assert torch.equal(c3, c1)
+
+
+def _attention_case(dtype, nq, nkv, d, page, prefixes, news, window, seed=6, spike=False):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    reqs = len(prefixes)
+    width = max(-(-(p + n) // page) for p, n in zip(prefixes, news))
+    pages = reqs * width
+    cache = _cache(pages, nkv, page, d, dtype, g)
+    table = (torch.randperm(pages, device=DEV, generator=g) + 1).view(reqs, width).to(torch.int32)
+    total = sum(news)
+    q = torch.randn(total, nq * d, device=DEV, generator=g).to(dtype)
+    if spike:
+        # one far key per request dominates: its key is a scaled copy of the first query of that request
+        at = 0
+        for r, (p, n) in enumerate(zip(prefixes, news)):
+            far = 1 if p + n > 2 else 0
+            pg, off = int(table[r, far // page]), far % page
+            for h in range(nkv):
+                cache[pg, 0, h, off] = (q[at].view(nq, d)[h * (nq // nkv)].float() * 4).to(dtype)
+            at += n
+    cu = torch.tensor([0] + list(torch.tensor(news).cumsum(0)), device=DEV, dtype=torch.int32)
+    pre = torch.tensor(prefixes, device=DEV, dtype=torch.int32)
+    return cache, table, q, cu, pre
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,window", [
+    (4, 2, 16, 16, None), (8, 2, 32, 16, None), (6, 2, 48, 8, 40), (5, 1, 80, 32, None), (32, 8, 128, 64, None),
+    (2, 2, 256, 16, 100), (16, 2, 64, 16, 33), (40, 1, 32, 16, None)])
+def test_attention_prefill(dtype, nq, nkv, d, page, window):
+    prefixes, news = [0, 17, 130, 5, 300, 64], [1, 70, 33, 200, 129, 2]      # lengths of the reference's own test
+    cache, table, q, cu, pre = _attention_case(dtype, nq, nkv, d, page, prefixes, news, window, spike=True)
+    rows = ops().prefill_tile_rows()
+    treq = [r for r, n in enumerate(news) for _ in range(0, n, rows)]
+    tstart = [s for r, n in enumerate(news) for s in range(0, n, rows)]
+    treq_t = torch.tensor(treq, device=DEV, dtype=torch.int32)
+    tstart_t = torch.tensor(tstart, device=DEV, dtype=torch.int32)
+    got, want = torch.zeros_like(q), torch.zeros_like(q)
+    ops().attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, got, nq, nkv, d, page, d ** -0.5, window)
+    ref.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, want, nq, nkv, d, page, d ** -0.5, window)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [
+    (4, 2, 16, 16, None), (8, 2, 32, 16, None), (6, 2, 48, 8, 40), (5, 1, 80, 32, None), (32, 8, 128, 64, None),
+    (2, 2, 256, 16, 100), (40, 1, 32, 16, None), (16, 16, 64, 16, 7)])
+def test_attention_decode(dtype, splits, nq, nkv, d, page, window):
+    seqs = [1, 8, 65, 500, 1000, 3, 257]                                     # prefixes up to 999, as the reference tests
+    prefixes, news = [s - 1 for s in seqs], [1] * len(seqs)
+    cache, table, q, cu, pre = _attention_case(dtype, nq, nkv, d, page, prefixes, news, window, seed=7, spike=True)
+    seq_t = torch.tensor(seqs, device=DEV, dtype=torch.int32)
+    need = ops().decode_scratch_floats(len(seqs), nq, d, splits)
+    scratch = torch.full((max(need, 1),), float("nan"), device=DEV)
+    got, want = torch.zeros_like(q), torch.zeros_like(q)
+    ops().attention_decode(q, cache, table, seq_t, got, scratch, splits, nq, nkv, d, page, d ** -0.5, window)
+    ref.attention_decode(q, cache, table, seq_t, want, None, splits, nq, nkv, d, page, d ** -0.5, window)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+def test_attention_refuses_what_it_cannot_do():
+    o = ops()
+    q = torch.zeros(1, 2 * 272, device=DEV)
+    cache = torch.zeros(2, 2, 2, 16, 272, device=DEV)
+    table = torch.ones(1, 1, device=DEV, dtype=torch.int32)
+    seq = torch.ones(1, device=DEV, dtype=torch.int32)
+    with pytest.raises(o.KernelError, match="head_dim"):
+        o.attention_decode(q, cache, table, seq, torch.zeros_like(q), None, 1, 2, 2, 272, 16, 1.0)
+    with pytest.raises(o.KernelError, match="CUDA"):
+        o.silu_mul(torch.zeros(2, 4))
+
+
+@pytest.mark.parametrize("vocab", [256, 331, 1009, 151936])
+def test_argmax_and_penalties(vocab):
+    g = torch.Generator(device=DEV).manual_seed(8)
+    logits = torch.randn(5, vocab, device=DEV, generator=g)
+    logits[2, vocab - 1] = 50.0
+    logits[3, 7] = logits[3, 100] = 40.0                         # a tie goes to the lower index
+    got = ops().argmax(logits)
+    assert got.tolist() == torch.argmax(logits, -1).tolist() and got[3] == 7 and got[2] == vocab - 1
+    rows = torch.tensor([0, 0, 1, 4], device=DEV, dtype=torch.int32)
+    toks = torch.tensor([3, 9, 3, vocab - 1], device=DEV, dtype=torch.int32)
+    cnt = torch.tensor([2, 0, 1, 5], device=DEV, dtype=torch.int32)
+    bias = torch.tensor([0.0, 1.5, -2.0, 0.0], device=DEV)
+    rep = torch.tensor([1.3, 1.0, 1.0, 1.0, 2.0], device=DEV)
+    freq = torch.tensor([0.1, 0.2, 0.0, 0.0, 0.05], device=DEV)
+    pres = torch.tensor([0.5, 0.0, 0.0, 0.0, 0.25], device=DEV)
+    a, b = logits.clone(), logits.clone()
+    ops().apply_penalties(a, rows, toks, cnt, bias, rep, freq, pres)
+    ref.apply_penalties(b, rows, toks, cnt, bias, rep, freq, pres)
+    torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("vocab", [256, 1009, 151936])
+def test_sample_matches_filtered_distribution(vocab):
+    import plain_impl
+
+    g = torch.Generator(device=DEV).manual_seed(9)
+    cases = [(0.7, -1, 1.0, 0.0), (1.0, 5, 1.0, 0.0), (1.3, -1, 0.6, 0.0), (0.9, 50, 0.8, 0.05), (1.0, -1, 1.0, 0.2),
+             (0.0, -1, 1.0, 0.0), (1.0, 1, 1.0, 0.0), (2.0, -1, 0.05, 0.0)]
+    rows = len(cases)
+    logits = torch.randn(rows, vocab, device=DEV, generator=g) * 3
+    t = torch.tensor([c[0] for c in cases], device=DEV)
+    k = torch.tensor([c[1] for c in cases], device=DEV, dtype=torch.int32)
+    p = torch.tensor([c[2] for c in cases], device=DEV)
+    mp = torch.tensor([c[3] for c in cases], device=DEV)
+    for u_val in (0.0, 0.123, 0.5, 0.77, 0.999999):
+        u = torch.full((rows,), u_val, device=DEV)
+        toks, lps = ops().sample(logits, t, k, p, mp, u, want_logprob=True)
+        for r, (temp, kk, pp, mm) in enumerate(cases):
+            tok = int(toks[r])
+            if temp == 0 or kk == 1:
+                assert tok == int(torch.argmax(logits[r]))
+                assert abs(float(lps[r]) - float(torch.log_softmax(logits[r], -1)[tok])) < 1e-4
+                continue
+            probs = plain_impl.filtered_probs(logits[r].cpu(), temp, kk, pp, mm).double()
+            assert probs[tok] > 0, (r, tok)
+            cum = torch.cumsum(probs, 0)
+            lo, hi = float(cum[tok] - probs[tok]), float(cum[tok])
+            assert lo - 1e-5 <= u_val < hi + 1e-5, (r, u_val, lo, hi)      # the drawn token's interval holds u
+            assert abs(float(lps[r]) - float(torch.log(probs[tok]))) < 1e-3
+
+
+def test_sample_frequencies():
+    # chi-square of many draws against the softmax, as the reference tests its sampler
+    # (tests/test_engine.py:157-184 there): 12 tokens, temperature 1, 40000 draws.
+    g = torch.Generator(device=DEV).manual_seed(10)
+    vocab, draws = 12, 40000
+    row = torch.randn(vocab, device=DEV, generator=g)
+    logits = row.repeat(draws, 1).contiguous()
+    u = torch.rand(draws, device=DEV, generator=g)
+    ones = torch.ones(draws, device=DEV)
+    toks, _ = ops().sample(logits, ones, torch.full((draws,), -1, device=DEV, dtype=torch.int32), ones,
+                           torch.zeros(draws, device=DEV), u)
+    counts = torch.bincount(toks.long(), minlength=vocab).double().cpu()
+    expect = torch.softmax(row.double().cpu(), 0) * draws
+    chi2 = float(((counts - expect) ** 2 / expect).sum())
+    assert chi2 < 31.26                                         # df = 11, p = 0.001

@@ -1,0 +1,178 @@
+"""The scheduler's decisions, on the CPU with the kernels' plain PyTorch statements as ops:
+admission under a token budget, portions, mixed batches, finishing and freeing, and what happens
+when pages run out (retraction; refusal of what can never fit)."""
+
+import tempfile
+
+import pytest
+import torch
+
+import kernel_refs
+import plain_impl
+import tiny_models
+from harness import make_runner, model_dir
+from lily_b200.engine.scheduler import Scheduler
+from lily_b200.sampling.params import SamplingParams
+from lily_b200.sampling.sampler import uniform_for
+
+
+@pytest.fixture(scope="module")
+def setup():
+    cfg = tiny_models.TINY_QWEN3
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 51, tmp)
+        yield cfg, weights, path
+
+
+def scheduler(path, max_tokens=1024, page_size=16, max_requests=8, **kw):
+    runner = make_runner(path, max_tokens=max_tokens, page_size=page_size, max_requests=max_requests)
+    return Scheduler(runner, random_seed=7, **kw)
+
+
+def run(s, prompts, n, **params):
+    for i, p in enumerate(prompts):
+        s.add_request(f"r{i}", p, SamplingParams(max_new_tokens=n, ignore_eos=True, **params))
+    s.run_to_completion()
+    return [s.results[f"r{i}"].output_ids for i in range(len(prompts))]
+
+
+def prompts(cfg, lens, seed=0):
+    return [tiny_models.random_tokens(n, cfg["vocab_size"], seed + i) for i, n in enumerate(lens)]
+
+
+def test_greedy_equals_plain_and_batching_changes_nothing(setup):
+    cfg, weights, path = setup
+    ps = prompts(cfg, [1, 7, 33, 64])
+    want = [plain_impl.greedy_generate(cfg, weights, p, 16) for p in ps]
+    single = []
+    for p in ps:
+        single += run(scheduler(path, max_requests=1), [p], 16)
+    assert single == want
+    s = scheduler(path)
+    assert run(s, ps, 16) == want
+    assert s.runner.cache.held_pages() == [0] and s.runner.cache.slots.available == 8
+    assert s.prefill_tokens_computed == sum(len(p) for p in ps) and s.decode_steps == 4 * 15
+
+
+def test_chunked_prefill_equals_unchunked(setup):
+    cfg, weights, path = setup
+    long = prompts(cfg, [150], seed=5)
+    chunked = scheduler(path, chunked_prefill_size=64)
+    seen = []
+    orig = chunked.runner.step
+    chunked.runner.step = lambda entries: (seen.append([len(e.tokens) for e in entries]), orig(entries))[1]
+    assert run(chunked, long, 8) == run(scheduler(path), long, 8)
+    assert chunked.prefill_tokens_computed == 150
+    assert seen[:3] == [[64], [64], [22]]
+
+
+def test_budget_portions_and_mixed_batches(setup):
+    cfg, weights, path = setup
+    s = scheduler(path, chunked_prefill_size=40, max_running_requests=3)
+    ps = prompts(cfg, [30, 30, 30, 10], seed=9)
+    for i, p in enumerate(ps):
+        s.add_request(f"r{i}", p, SamplingParams(max_new_tokens=4, ignore_eos=True))
+    s.step()                        # 30 of r0 and 10 of r1: the budget of 40 is spent
+    assert s.last_batch == {"decode": 0, "prefill_requests": 2, "prefill_tokens": 40}
+    assert [r.rid for r in s.running] == ["r0"] and s.waiting_queue[0].rid == "r1" and s.waiting_queue[0].seq_len == 10
+    s.step()                        # r0 decodes beside the rest of r1 and a portion of r2 (3 requests at most)
+    assert s.last_batch == {"decode": 1, "prefill_requests": 2, "prefill_tokens": 40}
+    assert [r.rid for r in s.running] == ["r0", "r1"] and s.waiting_queue[0].rid == "r2"
+    s.step()                        # no slot for r3 while three requests are live
+    assert s.last_batch == {"decode": 2, "prefill_requests": 1, "prefill_tokens": 10}
+    s.run_to_completion()
+    want = [plain_impl.greedy_generate(cfg, weights, p, 4) for p in ps]
+    assert [s.results[f"r{i}"].output_ids for i in range(4)] == want
+    assert all(s.results[f"r{i}"].finish_reason == {"type": "length"} for i in range(4))
+
+
+def test_pages_run_out_retraction_keeps_outputs(setup):
+    cfg, weights, path = setup
+    ps = prompts(cfg, [20, 25, 18, 30, 22, 27, 19, 24], seed=20)
+    want = [plain_impl.greedy_generate(cfg, weights, p, 12) for p in ps]
+    s = scheduler(path, max_tokens=13 * 16, page_size=16)          # 13 pages for 8 requests of up to 42 tokens
+    assert run(s, ps, 12) == want
+    assert s.retractions > 0
+    assert s.runner.cache.held_pages() == [0] and s.runner.cache.slots.available == 8
+
+
+def test_what_can_never_fit_is_refused_and_a_lone_request_ends(setup):
+    cfg, weights, path = setup
+    s = scheduler(path, max_tokens=4 * 16, page_size=16)
+    s.add_request("big", tiny_models.random_tokens(70, 256, 1), SamplingParams(max_new_tokens=4))
+    assert s.results["big"].finish_reason["type"] == "abort" and "KV pool" in s.results["big"].finish_reason["message"]
+    s.add_request("ctx", tiny_models.random_tokens(256, 256, 1), SamplingParams(max_new_tokens=4))
+    assert "context" in s.results["ctx"].finish_reason["message"]
+    s.add_request("bad", [5, 999], None)
+    assert "vocabulary" in s.results["bad"].finish_reason["message"]
+    assert not s.has_work()
+    s.add_request("lone", tiny_models.random_tokens(60, 256, 2), SamplingParams(max_new_tokens=50, ignore_eos=True))
+    s.run_to_completion()
+    r = s.results["lone"]
+    assert r.finish_reason == {"type": "length", "message": "KV cache exhausted"} and len(r.output_ids) == 5
+    assert s.runner.cache.held_pages() == [0]
+
+
+def test_finish_on_eos_stop_ids_context_and_abort(setup):
+    cfg, weights, path = setup
+    p = prompts(cfg, [12], seed=30)[0]
+    free_run = plain_impl.greedy_generate(cfg, weights, p, 10)
+    s = scheduler(path, eos_token_ids=[free_run[3]])
+    s.add_request("a", p, SamplingParams(max_new_tokens=10))
+    s.add_request("b", p, SamplingParams(max_new_tokens=10, ignore_eos=True))
+    s.add_request("c", p, SamplingParams(max_new_tokens=10, stop_token_ids=[free_run[1]], ignore_eos=False))
+    s.run_to_completion()
+    first = free_run.index(free_run[3])
+    assert s.results["a"].output_ids == free_run[:first + 1]
+    assert s.results["a"].finish_reason == {"type": "stop", "value": free_run[3]}
+    assert s.results["b"].output_ids == free_run
+    assert s.results["c"].output_ids == free_run[:free_run.index(free_run[1]) + 1]
+    s = scheduler(path)
+    s.add_request("x", tiny_models.random_tokens(250, 256, 3), SamplingParams(max_new_tokens=50, ignore_eos=True))
+    s.add_request("y", p, SamplingParams(max_new_tokens=50, ignore_eos=True))
+    s.step()
+    s.step()
+    s.abort_request("y")
+    s.run_to_completion()
+    assert s.results["x"].finish_reason == {"type": "length", "message": "context length reached"}
+    assert len(s.results["x"].output_ids) == 6
+    assert s.results["y"].finish_reason["type"] == "abort"
+    assert s.runner.cache.held_pages() == [0] and s.runner.cache.slots.available == 8
+
+
+def test_temperature_seeds(setup):
+    cfg, weights, path = setup
+    p = prompts(cfg, [9], seed=40)[0]
+    s = scheduler(path)
+    kw = dict(max_new_tokens=12, temperature=0.7, ignore_eos=True)
+    s.add_request("a", p, SamplingParams(seed=3, **kw))
+    s.add_request("b", p, SamplingParams(seed=3, **kw))
+    s.add_request("c", p, SamplingParams(seed=4, top_k=20, top_p=0.9, **kw))
+    s.add_request("d", p, SamplingParams(seed=3, logprobs=True, **kw))
+    s.run_to_completion()
+    a, b, c, d = (s.results[k] for k in "abcd")
+    assert a.output_ids == b.output_ids == d.output_ids and a.output_ids != c.output_ids
+    assert len(d.logprobs) == 12 and all(lp <= 0 for lp in d.logprobs)
+    # the same request alone draws the same tokens: the draw does not depend on the batch
+    s2 = scheduler(path)
+    s2.add_request("a", p, SamplingParams(seed=3, **kw))
+    s2.run_to_completion()
+    assert s2.results["a"].output_ids == a.output_ids
+    # and follows the plain sampler step by step
+    ids = list(p)
+    for i, tok in enumerate(a.output_ids):
+        probs = plain_impl.filtered_probs(plain_impl.all_logits(cfg, weights, ids)[-1], 0.7)
+        assert plain_impl.inverse_cdf_pick(probs, uniform_for(3, i)) == tok
+        ids.append(tok)
+
+
+def test_sampling_params_checks():
+    for kw in ({"max_new_tokens": 0}, {"temperature": -1}, {"top_p": 0}, {"top_k": 0}, {"min_p": 1.0},
+               {"repetition_penalty": 0}, {"stop": "x"}, {"top_logprobs": 2}, {"n": 2}):
+        with pytest.raises(ValueError):
+            SamplingParams(**kw)
+    assert SamplingParams().greedy and SamplingParams(temperature=1.0, top_k=1).greedy
+    assert not SamplingParams(temperature=0.5).greedy
+    assert SamplingParams(logit_bias={"3": 1}).logit_bias == {3: 1.0}
+    us = [uniform_for(1, i) for i in range(1000)]
+    assert all(0 <= u < 1 for u in us) and 0.45 < sum(us) / 1000 < 0.55 and uniform_for(1, 5) != uniform_for(2, 5)
