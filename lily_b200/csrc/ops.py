@@ -58,8 +58,12 @@ def library():
     return _lib
 
 
+launches = {"count": 0}          # kernels of this package launched so far (bench.py reports the difference)
+
+
 def _call(name: str, *args) -> None:
     lib = library()
+    launches["count"] += 1
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise KernelError(f"{name}: {lib.lily_last_error().decode(errors='replace')}")
@@ -247,6 +251,8 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     _call("lily_attention_decode_simt", _p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"),
           block_table.shape[-1], _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits, nq, nkv, d, page_size,
           int(window or 0), float(scale), _dt(q), _stream())
+    if splits > 1:
+        launches["count"] += 1          # the combine kernel
 
 
 # ------------------------------------------------------------------------------ sampling

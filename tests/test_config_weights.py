@@ -50,7 +50,7 @@ def test_config_errors(patch, msg):
 
 
 def test_registry():
-    assert supported_architectures() == ["LlamaForCausalLM", "Qwen3ForCausalLM"]
+    assert {"LlamaForCausalLM", "Qwen3ForCausalLM"} <= set(supported_architectures())   # tests may add toys
     assert resolve_architecture(["Nope", "Qwen3ForCausalLM"]).name == "Qwen3ForCausalLM"
     with pytest.raises(ValueError, match="No registered model.*LlamaForCausalLM"):
         resolve_architecture(["GPT2LMHeadModel"])

@@ -1,0 +1,122 @@
+"""Generation through the Python entry point and the command line on the GPU."""
+
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import pytest
+import torch
+
+import plain_impl
+import tiny_models
+from harness import model_dir
+from test_engine_gpu import rounded
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def engine(path, dtype, **kw):
+    from lily_b200 import Engine, EngineConfig
+    return Engine(EngineConfig(path, dtype=dtype, max_total_tokens=kw.pop("max_total_tokens", 2048),
+                               max_running_requests=kw.pop("max_running_requests", 8), server_args=kw or None))
+
+
+def greedy_with_gaps(cfg, weights, prompt, n):
+    """Plain greedy tokens with the runner-up and the top-2 gap at each position
+    (the reference's tie-tolerant compare, tests/util.py:50-112 there)."""
+    ids, toks, second, gaps = list(prompt), [], [], []
+    for _ in range(n):
+        top = torch.topk(plain_impl.all_logits(cfg, weights, ids)[-1], 2)
+        toks.append(int(top.indices[0])); second.append(int(top.indices[1])); gaps.append(float(top.values[0] - top.values[1]))
+        ids.append(toks[-1])
+    return toks, second, gaps
+
+
+def matches_up_to_tie_flip(got, ref, second, gaps, tie_gap):
+    for i, (g, r) in enumerate(zip(got, ref)):
+        if g != r:
+            assert gaps[i] < tie_gap and g == second[i], f"position {i}: {g} vs {r}, gap {gaps[i]:.4f}"
+            return i
+    return len(ref)
+
+
+@pytest.mark.parametrize("name", ["tiny_qwen3", "tiny_llama"])
+def test_greedy_generation_float32_equals_plain(name):
+    cfg = tiny_models.CONFIGS[name]
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 61, tmp)
+        eng = engine(path, "float32", page_size=16)
+        lens = [1, 7, 33, 64] if name == "tiny_qwen3" else [3, 17, 50, 100, 200, 300]
+        prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], 70 + i) for i, n in enumerate(lens)]
+        want = [plain_impl.greedy_generate(cfg, weights, p, 16) for p in prompts]
+        from lily_b200 import SamplingParams
+        got = eng.generate(prompts, SamplingParams(max_new_tokens=16, ignore_eos=True))
+        assert [g["output_ids"] for g in got] == want
+        assert eng.generate_greedy(prompts[1], 16) == want[1]
+        free = eng.kv_available()
+        logits = eng.all_prefill_logits(prompts[2]).cpu()
+        assert float((logits - plain_impl.all_logits(cfg, weights, prompts[2])).abs().max()) < 1e-4
+        assert torch.equal(eng.prefill_logits(prompts[2]).cpu(), logits[-1])
+        assert eng.kv_available() == free, "pages leaked"
+
+
+def test_greedy_generation_bfloat16_up_to_tie_flips():
+    cfg = tiny_models.TINY_LLAMA
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 62, tmp)
+        eng = engine(path, "bfloat16", page_size=16)
+        w = rounded(weights, "bfloat16")
+        for i, n in enumerate([5, 40, 130]):
+            p = tiny_models.random_tokens(n, cfg["vocab_size"], 80 + i)
+            ref, second, gaps = greedy_with_gaps(cfg, w, p, 24)
+            assert matches_up_to_tie_flip(eng.generate_greedy(p, 24), ref, second, gaps, tie_gap=0.03) >= 3
+
+
+def test_temperature_generation_follows_the_plain_sampler():
+    # tiny-llama workload of the benchmark description: temperature 0.7 under a fixed seed, page size 16
+    cfg = tiny_models.TINY_LLAMA
+    from lily_b200 import SamplingParams
+    from lily_b200.sampling.sampler import uniform_for
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 63, tmp)
+        eng = engine(path, "float32", page_size=16, chunked_prefill_size=128)
+        prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], 90 + i) for i, n in enumerate([3, 17, 50, 100, 200, 300])]
+        params = [SamplingParams(max_new_tokens=24, temperature=0.7, seed=100 + i, ignore_eos=True) for i in range(6)]
+        got = eng.generate(prompts, params)
+        for i, (p, g) in enumerate(zip(prompts, got)):
+            ids = list(p)
+            for j, tok in enumerate(g["output_ids"]):
+                probs = plain_impl.filtered_probs(plain_impl.all_logits(cfg, weights, ids)[-1], 0.7).double()
+                cum = torch.cumsum(probs, 0)
+                u = uniform_for(100 + i, j)
+                assert float(cum[tok] - probs[tok]) - 1e-4 <= u < float(cum[tok]) + 1e-4, (i, j)
+                ids.append(tok)
+
+
+def test_small_pool_retracts_and_chunks_on_the_gpu():
+    cfg = tiny_models.TINY_QWEN3
+    from lily_b200 import SamplingParams
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 64, tmp)
+        prompts = [tiny_models.random_tokens(n, 256, 110 + i) for i, n in enumerate([20, 25, 18, 30, 22, 27, 19, 24])]
+        want = [plain_impl.greedy_generate(cfg, weights, p, 12) for p in prompts]
+        eng = engine(path, "float32", page_size=16, max_total_tokens=13 * 16, chunked_prefill_size=64)
+        got = eng.generate(prompts, SamplingParams(max_new_tokens=12, ignore_eos=True))
+        assert [g["output_ids"] for g in got] == want
+        assert eng.last_scheduler.retractions > 0 and eng.kv_available() == 13 * 16
+
+
+def test_command_line_generates():
+    cfg = tiny_models.TINY_QWEN3
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 65, tmp)
+        p = tiny_models.random_tokens(9, 256, 5)
+        out = subprocess.run([sys.executable, "-m", "lily_b200", "generate", "--model-path", path, "--dtype", "float32",
+                              "--max-total-tokens", "256", "--page-size", "16", "--prompt-ids",
+                              ",".join(map(str, p)), "--max-new-tokens", "6", "--ignore-eos"],
+                             cwd=ROOT, capture_output=True, text=True, timeout=600)
+        assert out.returncode == 0, out.stderr[-2000:]
+        assert json.loads(out.stdout.strip().splitlines()[-1])["output_ids"] == plain_impl.greedy_generate(cfg, weights, p, 6)
