@@ -96,14 +96,14 @@ def test_temperature_generation_follows_the_plain_sampler():
                 ids.append(tok)
 
 
-def test_small_pool_retracts_and_chunks_on_the_gpu():
+def test_small_pool_retracts_on_the_gpu():
     cfg = tiny_models.TINY_QWEN3
     from lily_b200 import SamplingParams
     with tempfile.TemporaryDirectory() as tmp:
         path, weights = model_dir(cfg, 64, tmp)
         prompts = [tiny_models.random_tokens(n, 256, 110 + i) for i, n in enumerate([20, 25, 18, 30, 22, 27, 19, 24])]
         want = [plain_impl.greedy_generate(cfg, weights, p, 12) for p in prompts]
-        eng = engine(path, "float32", page_size=16, max_total_tokens=13 * 16, chunked_prefill_size=64)
+        eng = engine(path, "float32", page_size=16, max_total_tokens=13 * 16)
         got = eng.generate(prompts, SamplingParams(max_new_tokens=12, ignore_eos=True))
         assert [g["output_ids"] for g in got] == want
         assert eng.last_scheduler.retractions > 0 and eng.kv_available() == 13 * 16
