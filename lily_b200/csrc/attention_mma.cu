@@ -1,0 +1,405 @@
+// Paged causal grouped-query attention in bfloat16 on the tensor cores (mma.sync m16n8k16,
+// float32 accumulation), for head sizes that are multiples of 64 up to 256.  Other head sizes and
+// the float32 path use attention_simt.cu; both read the same cache layout and take the same
+// arguments, and both are tested against the same plain statement.
+//
+//  * prefill: grid (query tiles of 64 new tokens, query heads), 4 warps of 16 query rows each.
+//  * decode:  grid (requests, kv heads x row chunks, splits).  The query heads that share a kv head
+//    are the (up to 16) rows; the 4 warps take 16 keys each of every 64-key tile and keep their own
+//    running (max, sum, output), merged through shared memory at the end; splits > 1 leave partial
+//    results in scratch for the combine kernel of attention_simt.cu.
+//
+// Key and value tiles of 64 positions are brought in with cp.async (16-byte pieces, any page
+// size: each row's page is looked up in the block table), double buffered, into shared memory
+// whose 16-byte pieces are XOR-swizzled by row so that ldmatrix reads without bank conflicts.
+// Scores, the running maximum and sum, and the output accumulate in float32; probabilities are
+// rounded to bfloat16 for p.v as in lily/layers/attention/triton_ops/extend_attention.py:110-112.
+#include "attention_args.cuh"
+#include "common.cuh"
+
+namespace lily {
+
+
+namespace mma {
+
+constexpr int BN = 64;        // keys per tile
+constexpr int THREADS = 128;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;     // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of the 16-byte piece `chunk` of row `row` in a tile whose rows hold D bfloat16.
+template <int D>
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    return (uint32_t)(row * (D * 2) + ((((chunk ^ row) & 7) | (chunk & ~7)) << 4));
+}
+
+template <int D, bool DECODE>
+__global__ void __launch_bounds__(THREADS)
+attention_mma_kernel(const AttnArgs a) {
+    constexpr int CH = D / 8;                  // 16-byte pieces per row
+    constexpr int KSTEPS = D / 16;
+    constexpr int BM = DECODE ? 16 : 64;
+    constexpr int NT = DECODE ? 2 : 8;         // score n-tiles (8 keys each) per warp and key tile
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    unsigned char* q_s = smem_raw;                                  // [BM][D]
+    unsigned char* k_s = q_s + BM * D * 2;                          // [2][BN][D]
+    unsigned char* v_s = k_s + 2 * BN * D * 2;                      // [2][BN][D]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    const __nv_bfloat16* q = (const __nv_bfloat16*)a.q;
+    const __nv_bfloat16* kv = (const __nv_bfloat16*)a.kv;
+    const int group = a.nq / a.nkv;
+
+    int req, kvh, kbeg, kend, nrows, head0 = 0, tok0 = 0, pos0 = 0;
+    if (DECODE) {
+        req = blockIdx.x;
+        const int chunks = (group + 15) / 16;
+        kvh = blockIdx.y / chunks;
+        const int r0 = (blockIdx.y % chunks) * 16;
+        const int seq = a.seq_lens[req];
+        const int lo = (a.window > 0 && seq > a.window) ? seq - a.window : 0;
+        int per = (seq - lo + a.splits - 1) / a.splits;
+        per = (per + BN - 1) / BN * BN;
+        kbeg = lo + blockIdx.z * per;
+        kend = min(seq, kbeg + per);
+        nrows = min(16, group - r0);
+        head0 = kvh * group + r0;
+        tok0 = req;
+        pos0 = seq - 1;
+    } else {
+        const int tile = blockIdx.x;
+        req = a.tile_req[tile];
+        const int start = a.tile_start[tile];
+        const int t0 = a.cu_seqlens[req], len = a.cu_seqlens[req + 1] - t0;
+        const int prefix = a.prefix_lens[req];
+        head0 = blockIdx.y;
+        kvh = head0 / group;
+        nrows = min(BM, len - start);
+        tok0 = t0 + start;
+        pos0 = prefix + start;
+        kend = pos0 + nrows;
+        kbeg = (a.window > 0 && pos0 + 1 > a.window) ? pos0 + 1 - a.window : 0;
+    }
+
+    // ---- queries to shared memory (zero rows beyond nrows), then to A fragments -------------
+    for (int i = tid; i < BM * CH; i += THREADS) {
+        const int r = i / CH, ch = i % CH;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (r < nrows) {
+            const size_t tok = DECODE ? (size_t)tok0 : (size_t)tok0 + r;
+            const int head = DECODE ? head0 + r : head0;
+            val = *reinterpret_cast<const uint4*>(q + (tok * a.nq + head) * D + ch * 8);
+        }
+        *reinterpret_cast<uint4*>(q_s + swz<D>(r, ch)) = val;
+    }
+    __syncthreads();
+    uint32_t qf[KSTEPS][4];
+    {
+        const int rbase = DECODE ? 0 : warp * 16;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk)
+            ldmatrix_x4(smem_u32(q_s + swz<D>(rbase + (lane & 15), kk * 2 + (lane >> 4))), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+    }
+    const int row_lo = DECODE ? g : warp * 16 + g;      // this thread's two rows within the block
+    const int row_hi = row_lo + 8;
+    const int qpos_lo = DECODE ? pos0 : pos0 + row_lo, qpos_hi = DECODE ? pos0 : pos0 + row_hi;
+
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    float o[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+    const int* table = a.block_table + (size_t)req * a.bt_stride;
+    const size_t head_stride = (size_t)a.page_size * D;
+    const size_t page_stride = 2 * (size_t)a.nkv * head_stride;
+    const int ntiles = kend > kbeg ? (kend - kbeg + BN - 1) / BN : 0;
+
+    auto load_tile = [&](int t, int buf) {
+        const int kb = kbeg + t * BN;
+        unsigned char* kd = k_s + buf * BN * D * 2;
+        unsigned char* vd = v_s + buf * BN * D * 2;
+        for (int i = tid; i < BN * CH; i += THREADS) {
+            const int r = i / CH, ch = i % CH;
+            const int kpos = kb + r;
+            const bool ok = kpos < kend;
+            const int page = ok ? table[kpos / a.page_size] : 0;
+            const __nv_bfloat16* src = kv + (size_t)page * page_stride + (size_t)kvh * head_stride +
+                                       (size_t)(ok ? kpos % a.page_size : 0) * D + ch * 8;
+            cp_async16(smem_u32(kd + swz<D>(r, ch)), src, ok);
+            cp_async16(smem_u32(vd + swz<D>(r, ch)), src + (size_t)a.nkv * head_stride, ok);
+        }
+        cp_async_commit();
+    };
+
+    if (ntiles > 0) load_tile(0, 0);
+    const float sl2 = a.scale * 1.4426950408889634f;       // scores are kept in units of log2(e)
+
+    for (int t = 0; t < ntiles; ++t) {
+        const int buf = t & 1;
+        cp_async_wait<0>();
+        __syncthreads();                                    // tile t has landed; tile t-1's readers are done
+        if (t + 1 < ntiles) load_tile(t + 1, buf ^ 1);
+        const unsigned char* kt = k_s + buf * BN * D * 2;
+        const unsigned char* vt = v_s + buf * BN * D * 2;
+        const int kb = kbeg + t * BN;
+        const int key0 = DECODE ? warp * 16 : 0;            // first key of this warp's share of the tile
+
+        // ---- s = q . k^T -------------------------------------------------------------------
+        float s[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+            for (int jp = 0; jp < NT / 2; ++jp) {
+                uint32_t b0, b1, b2, b3;
+                const int krow = key0 + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
+                ldmatrix_x4(smem_u32(kt + swz<D>(krow, kk * 2 + ((lane >> 3) & 1))), b0, b1, b2, b3);
+                mma_bf16(s[2 * jp], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+                mma_bf16(s[2 * jp + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+            }
+        }
+
+        // ---- mask, running maximum and sum ----------------------------------------------------
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int kpos = kb + key0 + j * 8 + 2 * c + (e & 1);
+                const int qpos = (e < 2) ? qpos_lo : qpos_hi;
+                const bool seen = kpos < kend && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window);
+                s[j][e] = seen ? s[j][e] * sl2 : -INFINITY;
+            }
+            mx_lo = fmaxf(mx_lo, fmaxf(s[j][0], s[j][1]));
+            mx_hi = fmaxf(mx_hi, fmaxf(s[j][2], s[j][3]));
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo, base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+        const float al_lo = exp2f(m_lo - base_lo), al_hi = exp2f(m_hi - base_hi);
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            s[j][0] = exp2f(s[j][0] - base_lo);
+            s[j][1] = exp2f(s[j][1] - base_lo);
+            s[j][2] = exp2f(s[j][2] - base_hi);
+            s[j][3] = exp2f(s[j][3] - base_hi);
+            sum_lo += s[j][0] + s[j][1];
+            sum_hi += s[j][2] + s[j][3];
+        }
+        l_lo = l_lo * al_lo + sum_lo;                       // per-thread partial sums; reduced at the end
+        l_hi = l_hi * al_hi + sum_hi;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+            o[j][0] *= al_lo;
+            o[j][1] *= al_lo;
+            o[j][2] *= al_hi;
+            o[j][3] *= al_hi;
+        }
+
+        // ---- o += p . v -------------------------------------------------------------------------
+#pragma unroll
+        for (int kb16 = 0; kb16 < NT / 2; ++kb16) {
+            const uint32_t a0 = pack_bf16(s[2 * kb16][0], s[2 * kb16][1]);
+            const uint32_t a1 = pack_bf16(s[2 * kb16][2], s[2 * kb16][3]);
+            const uint32_t a2 = pack_bf16(s[2 * kb16 + 1][0], s[2 * kb16 + 1][1]);
+            const uint32_t a3 = pack_bf16(s[2 * kb16 + 1][2], s[2 * kb16 + 1][3]);
+            const int vrow = key0 + kb16 * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+#pragma unroll
+            for (int jp = 0; jp < D / 16; ++jp) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(smem_u32(vt + swz<D>(vrow, jp * 2 + (lane >> 4))), b0, b1, b2, b3);
+                mma_bf16(o[2 * jp], a0, a1, a2, a3, b0, b1);
+                mma_bf16(o[2 * jp + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+    }
+
+    // sums over the four threads that share a row
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+    if (!DECODE) {
+        __nv_bfloat16* out = (__nv_bfloat16*)a.out;
+        const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+            const int col = j * 8 + 2 * c;
+            if (row_lo < nrows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(tok0 + row_lo) * a.nq + head0) * D + col) =
+                    pack_bf16(o[j][0] * inv_lo, o[j][1] * inv_lo);
+            if (row_hi < nrows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(tok0 + row_hi) * a.nq + head0) * D + col) =
+                    pack_bf16(o[j][2] * inv_hi, o[j][3] * inv_hi);
+        }
+        return;
+    }
+
+    // ---- decode: merge the four warps' partial results through shared memory ---------------------
+    __syncthreads();                                        // every warp is done with the key/value tiles
+    float* mo = reinterpret_cast<float*>(k_s);              // [4 warps][16 rows][D]
+    float* mml = mo + 4 * 16 * D;                           // [4 warps][16 rows][2]
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+        const int col = j * 8 + 2 * c;
+        mo[(warp * 16 + row_lo) * D + col] = o[j][0];
+        mo[(warp * 16 + row_lo) * D + col + 1] = o[j][1];
+        mo[(warp * 16 + row_hi) * D + col] = o[j][2];
+        mo[(warp * 16 + row_hi) * D + col + 1] = o[j][3];
+    }
+    if (c == 0) {
+        mml[(warp * 16 + row_lo) * 2] = m_lo;
+        mml[(warp * 16 + row_lo) * 2 + 1] = l_lo;
+        mml[(warp * 16 + row_hi) * 2] = m_hi;
+        mml[(warp * 16 + row_hi) * 2 + 1] = l_hi;
+    }
+    __syncthreads();
+    const float ln2 = 0.6931471805599453f;
+    for (int i = tid; i < nrows * D; i += THREADS) {
+        const int r = i / D, col = i % D;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mml[(w * 16 + r) * 2]);
+        float acc = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = mml[(w * 16 + r) * 2];
+            if (mw > -INFINITY) {
+                const float f = exp2f(mw - mx);
+                acc += mo[(w * 16 + r) * D + col] * f;
+                den += mml[(w * 16 + r) * 2 + 1] * f;
+            }
+        }
+        const int head = head0 + r;
+        if (a.splits > 1) {
+            const size_t base = ((size_t)tok0 * a.nq + head) * a.splits + blockIdx.z;
+            a.part_o[base * D + col] = acc;
+            if (col == 0) {
+                a.part_ml[base * 2] = mx * ln2;             // back to natural-log units for the combine kernel
+                a.part_ml[base * 2 + 1] = den;
+            }
+        } else {
+            ((__nv_bfloat16*)a.out)[((size_t)tok0 * a.nq + head) * D + col] =
+                __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+        }
+    }
+}
+
+template <int D, bool DECODE>
+static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
+    constexpr int BM = DECODE ? 16 : 64;
+    size_t smem = (size_t)BM * D * 2 + 4 * (size_t)BN * D * 2;
+    if (DECODE) {
+        const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
+        if ((size_t)BM * D * 2 + merge > smem) smem = (size_t)BM * D * 2 + merge;
+    }
+    auto kern = attention_mma_kernel<D, DECODE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            set_error("attention_mma: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+            return 2;
+        }
+        configured = true;
+    }
+    kern<<<grid, THREADS, smem, stream>>>(a);
+    return 0;
+}
+
+template <bool DECODE>
+static int dispatch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
+    switch (a.d) {
+        case 64: return launch<64, DECODE>(a, grid, stream);
+        case 128: return launch<128, DECODE>(a, grid, stream);
+        case 192: return launch<192, DECODE>(a, grid, stream);
+        case 256: return launch<256, DECODE>(a, grid, stream);
+    }
+    set_error("attention_mma: head_dim %d is not one of 64, 128, 192, 256", a.d);
+    return 1;
+}
+
+}  // namespace mma
+}  // namespace lily
+
+using namespace lily;
+
+// 1 when the tensor-core kernels take this head size (bfloat16 only); the caller uses the
+// CUDA-core kernels otherwise.
+LILY_API int lily_attention_mma_supports(int d) { return d == 64 || d == 128 || d == 192 || d == 256; }
+LILY_API int lily_attention_prefill_mma_rows() { return 64; }
+
+LILY_API int lily_attention_prefill_mma(const void* q, const void* kv, void* out, const int* block_table,
+                                        int bt_stride, const int* cu_seqlens, const int* prefix_lens,
+                                        const int* tile_req, const int* tile_start, int tiles, int nq, int nkv,
+                                        int d, int page_size, int window, float scale, cudaStream_t stream) {
+    if (tiles == 0) return 0;
+    LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill: %d query heads over %d kv heads", nq, nkv);
+    LILY_REQUIRE(nq <= 65535 && page_size > 0, "attention_prefill: nq=%d page_size=%d", nq, page_size);
+    AttnArgs a{};
+    a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride;
+    a.cu_seqlens = cu_seqlens; a.prefix_lens = prefix_lens; a.tile_req = tile_req; a.tile_start = tile_start;
+    a.splits = 1; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
+    int rc = mma::dispatch<false>(a, dim3(tiles, nq), stream);
+    if (rc) return rc;
+    LILY_CHECK_LAUNCH("attention_prefill_mma");
+    return 0;
+}
+
+// The partial results of splits > 1 go to `scratch` in the layout of attention_simt.cu
+// ([requests, nq, splits, d] outputs, then [requests, nq, splits, 2] (max, sum)); the caller runs
+// lily_attention_combine afterwards.
+LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out, const int* block_table,
+                                       int bt_stride, const int* seq_lens, float* scratch, int requests, int splits,
+                                       int nq, int nkv, int d, int page_size, int window, float scale,
+                                       cudaStream_t stream) {
+    if (requests == 0) return 0;
+    LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_decode: %d query heads over %d kv heads", nq, nkv);
+    LILY_REQUIRE(splits >= 1 && splits <= 65535 && page_size > 0, "attention_decode: splits=%d page_size=%d", splits, page_size);
+    LILY_REQUIRE(splits == 1 || scratch != nullptr, "attention_decode: splits need scratch");
+    const int group = nq / nkv, chunks = (group + 15) / 16;
+    LILY_REQUIRE(nkv * chunks <= 65535, "attention_decode: %d kv heads", nkv);
+    AttnArgs a{};
+    a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride; a.seq_lens = seq_lens;
+    a.splits = splits; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
+    a.part_o = scratch;
+    a.part_ml = scratch ? scratch + (size_t)requests * nq * splits * d : nullptr;
+    int rc = mma::dispatch<true>(a, dim3(requests, nkv * chunks, splits), stream);
+    if (rc) return rc;
+    LILY_CHECK_LAUNCH("attention_decode_mma");
+    return 0;
+}

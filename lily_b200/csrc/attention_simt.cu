@@ -17,6 +17,7 @@
 // lily/layers/attention/torch_native_backend.py:31-37,52-77; the split over keys follows
 // lily/layers/attention/triton_ops/decode_attention.py:21-157, the prefix + new tokens form
 // lily/layers/attention/triton_ops/extend_attention.py:17-169.
+#include "attention_args.cuh"
 #include "common.cuh"
 
 namespace lily {
@@ -26,23 +27,6 @@ constexpr int KEYS = 32;      // keys per tile (one per lane)
 constexpr int WARPS = 4;
 constexpr int RPW = ROWS / WARPS;
 
-struct AttnArgs {
-    const void* q;            // [tokens, nq, d]
-    const void* kv;           // layer base
-    void* out;                // [tokens, nq, d]
-    const int* block_table;   // [requests, bt_stride]
-    int bt_stride;
-    const int* cu_seqlens;    // prefill: [requests + 1] offsets of each request's new tokens
-    const int* prefix_lens;   // prefill: [requests] cached positions before the new tokens
-    const int* tile_req;      // prefill: [tiles]
-    const int* tile_start;    // prefill: [tiles] offset of the tile in its request's new tokens
-    const int* seq_lens;      // decode: [requests] positions after this step
-    float* part_o;            // decode: [requests, nq, splits, d]
-    float* part_ml;           // decode: [requests, nq, splits, 2]
-    int splits;
-    int nq, nkv, d, page_size, window;
-    float scale;
-};
 
 template <typename T, int DCH, bool DECODE>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -254,9 +238,11 @@ static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
 #define CASE(N)                                                                                          \
     case N: {                                                                                            \
         auto kern = attention_simt_kernel<T, N, DECODE>;                                                 \
-        if (smem > 48 * 1024) {                                                                          \
+        static size_t granted = 48 * 1024;      /* set once per size, never while a graph is captured */  \
+        if (smem > granted) {                                                                            \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) { set_error("attention: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return 2; } \
+            granted = smem;                                                                              \
         }                                                                                                \
         kern<<<grid, WARPS * 32, smem, stream>>>(a);                                                     \
         break;                                                                                           \
@@ -298,6 +284,22 @@ LILY_API int lily_attention_prefill_simt(const void* q, const void* kv, void* ou
     int rc = dtype == kBF16 ? launch<__nv_bfloat16, false>(a, grid, stream) : launch<float, false>(a, grid, stream);
     if (rc) return rc;
     LILY_CHECK_LAUNCH("attention_prefill");
+    return 0;
+}
+
+// Merges the partial results that a split-key decode kernel left in `scratch`
+// ([requests, nq, splits, d] outputs, then [requests, nq, splits, 2] (max, sum)).
+LILY_API int lily_attention_combine(const float* scratch, void* out, int requests, int nq, int d, int splits,
+                                    int dtype, cudaStream_t stream) {
+    if (requests == 0 || splits <= 1) return 0;
+    const float* part_o = scratch;
+    const float* part_ml = scratch + (size_t)requests * nq * splits * d;
+    dim3 cgrid(requests, nq);
+    if (dtype == kBF16)
+        attention_combine_kernel<<<cgrid, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, nq, d, splits);
+    else
+        attention_combine_kernel<<<cgrid, 128, 0, stream>>>(part_o, part_ml, (float*)out, nq, d, splits);
+    LILY_CHECK_LAUNCH("attention_combine");
     return 0;
 }
 

@@ -29,8 +29,8 @@ from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-SOURCES = ["elementwise.cu", "gemm_fp32.cu", "attention_simt.cu", "sampling.cu"]
-HEADERS = ["common.cuh"]
+SOURCES = ["elementwise.cu", "gemm_fp32.cu", "attention_simt.cu", "attention_mma.cu", "sampling.cu"]
+HEADERS = ["common.cuh", "attention_args.cuh"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
@@ -58,7 +58,7 @@ def _digest(paths: List[str], extra: str = "") -> str:
     h = hashlib.sha256(extra.encode())
     for p in paths:
         with open(p, "rb") as f:
-            h.update(p.encode())
+            h.update(os.path.basename(p).encode())     # not the folder: a copied checkout reuses its binaries
             h.update(f.read())
     return h.hexdigest()[:16]
 

@@ -30,6 +30,9 @@ _SIGNATURES = {
     "lily_gemm_fp32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
     "lily_argmax": [_vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_sample": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
@@ -52,6 +55,9 @@ def library():
             fn.argtypes = args
             fn.restype = _i
         lib.lily_attention_prefill_simt_rows.restype = _i
+        lib.lily_attention_prefill_mma_rows.restype = _i
+        lib.lily_attention_mma_supports.argtypes = [_i]
+        lib.lily_attention_mma_supports.restype = _i
         lib.lily_attention_decode_scratch_floats.argtypes = [_i, _i, _i, _i]
         lib.lily_attention_decode_scratch_floats.restype = _sz
         _lib = lib
@@ -214,22 +220,34 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
 # ------------------------------------------------------------------------------ attention
 
-def prefill_tile_rows() -> int:
-    return int(library().lily_attention_prefill_simt_rows())
+def uses_tensor_cores(dtype: torch.dtype, d: int) -> bool:
+    """Whether attention of this precision and head size runs on the mma.sync kernels
+    (bfloat16, head sizes 64, 128, 192, 256); everything else runs on the CUDA-core kernels."""
+    return dtype == torch.bfloat16 and bool(library().lily_attention_mma_supports(int(d)))
+
+
+def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0) -> int:
+    """New tokens per tile of the prefill kernel that will take this precision and head size."""
+    lib = library()
+    return int(lib.lily_attention_prefill_mma_rows() if uses_tensor_cores(dtype, d) else lib.lily_attention_prefill_simt_rows())
 
 
 def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
                       prefix_lens: torch.Tensor, tile_req: torch.Tensor, tile_start: torch.Tensor, out: torch.Tensor,
                       nq: int, nkv: int, d: int, page_size: int, scale: float, window: Optional[int] = None) -> None:
     """Causal attention of each request's new tokens over its cached prefix and themselves.
-    ``q`` and ``out`` are [tokens, nq * d] indexed by ``cu_seqlens``; tiles list (request, offset)."""
+    ``q`` and ``out`` are [tokens, nq * d] indexed by ``cu_seqlens``; tiles list (request, offset)
+    in steps of ``prefill_tile_rows(q.dtype, d)``."""
     _dev(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out)
     if q.dtype != kv_layer.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, cache and out must share a dtype")
-    _call("lily_attention_prefill_simt", _p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"),
-          block_table.shape[-1], _i32(cu_seqlens, "cu_seqlens"), _i32(prefix_lens, "prefix_lens"),
-          _i32(tile_req, "tile_req"), _i32(tile_start, "tile_start"), tile_req.numel(), nq, nkv, d, page_size,
-          int(window or 0), float(scale), _dt(q), _stream())
+    common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
+              _i32(cu_seqlens, "cu_seqlens"), _i32(prefix_lens, "prefix_lens"), _i32(tile_req, "tile_req"),
+              _i32(tile_start, "tile_start"), tile_req.numel(), nq, nkv, d, page_size, int(window or 0), float(scale))
+    if uses_tensor_cores(q.dtype, d):
+        _call("lily_attention_prefill_mma", *common, _stream())
+    else:
+        _call("lily_attention_prefill_simt", *common, _dt(q), _stream())
 
 
 def decode_scratch_floats(requests: int, nq: int, d: int, splits: int) -> int:
@@ -248,11 +266,17 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     need = decode_scratch_floats(requests, nq, d, splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"attention_decode: scratch of {need} float32 needed")
-    _call("lily_attention_decode_simt", _p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"),
-          block_table.shape[-1], _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits, nq, nkv, d, page_size,
-          int(window or 0), float(scale), _dt(q), _stream())
-    if splits > 1:
-        launches["count"] += 1          # the combine kernel
+    common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
+              _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0),
+              float(scale))
+    if uses_tensor_cores(q.dtype, d):
+        _call("lily_attention_decode_mma", *common, _stream())
+        if splits > 1:
+            _call("lily_attention_combine", _p(scratch), _p(out), requests, nq, d, splits, _dt(q), _stream())
+    else:
+        _call("lily_attention_decode_simt", *common, _dt(q), _stream())
+        if splits > 1:
+            launches["count"] += 1          # the combine kernel, launched inside
 
 
 # ------------------------------------------------------------------------------ sampling

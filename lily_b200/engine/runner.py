@@ -24,7 +24,8 @@ from lily_b200.cache.kv_cache import KVCacheManager, OutOfPages, bytes_per_token
 from lily_b200.config.model_config import read_model_dir
 from lily_b200.config.registry import resolve_architecture
 from lily_b200.config.server_args import ServerArgs
-from lily_b200.engine.batch import StepBatch, StepEntry, Workspace, build_step_batch, order_entries
+from lily_b200.engine.batch import (StepBatch, StepEntry, Workspace, build_step_batch, choose_decode_splits,
+                                    order_entries)
 from lily_b200.models.assembled import AssembledModel
 from lily_b200.parts.base import BuildContext, ModelSpec
 from lily_b200.weights.loader import CheckpointSource, load_model_weights
@@ -58,6 +59,76 @@ class _PinnedRing:
             ev = torch.cuda.Event()
             ev.record()
             self.events[i] = ev
+
+
+class _DecodeGraph:
+    """One captured decode step for up to ``bucket`` requests.  Its metadata lives in one static
+    int32 buffer that every replay overwrites; rows beyond the live requests point at slot 0 and
+    page 0, which no request owns (lily/model_executor/cuda_graph_runner.py:53-65,153-186 pads
+    the same way)."""
+
+    def __init__(self, runner: "ModelRunner", bucket: int):
+        self.bucket = b = bucket
+        self.widths = [runner.cache.max_pages_per_request for _ in runner.cache.groups]
+        self.sizes = [b, b, b, b + 1, b, b, b, b] + [b * w for w in self.widths]
+        total = sum(self.sizes)
+        self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
+        self.static = torch.zeros(total, dtype=torch.int32, device=runner.device)
+        self.copied: Optional[torch.cuda.Event] = None
+        parts = torch.split(self.static, self.sizes)
+        splits = choose_decode_splits(b, runner._kv_heads, runner.context_len)
+        self.batch = StepBatch(
+            num_tokens=b, num_requests=b, num_decode=b, token_ids=parts[0], positions=parts[1], token_req=parts[2],
+            cu_seqlens=parts[3], prefix_lens=parts[4], seq_lens=parts[5], slots=parts[6], logit_rows=parts[7],
+            block_tables=[parts[8 + i].view(b, w) for i, w in enumerate(self.widths)],
+            h_new_lens=[1] * b, h_prefix_lens=[0] * b, h_slots=[0] * b, max_seq_len=runner.context_len,
+            decode_splits=splits, workspace=runner.workspace)
+        self.fill([], [], [[] for _ in self.widths])
+        self.static.copy_(self.host)
+        stream = torch.cuda.Stream(device=runner.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream), torch.no_grad():
+            for _ in range(2):                      # sizes the workspace and sets kernel attributes
+                runner.model.forward(self.batch, runner.cache)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        counter = getattr(runner.model.ctx.ops, "launches", None)
+        before = counter["count"] if counter else 0
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.logits = runner.model.forward(self.batch, runner.cache)
+        self.kernels = (counter["count"] - before) if counter else 0     # this package's kernels in one replay
+        self._counter = counter
+
+    def fill(self, tokens: Sequence[int], prefix: Sequence[int], tables) -> None:
+        """Writes a decode batch (padded to the bucket) into the pinned host copy."""
+        b, n = self.bucket, len(tokens)
+        pad = b - n
+        flat: List[int] = list(tokens) + [0] * pad
+        flat += list(prefix) + [0] * pad                      # positions
+        flat += list(range(b))                                # token_req
+        flat += list(range(b + 1))                            # cu_seqlens
+        flat += list(prefix) + [0] * pad                      # prefix_lens
+        flat += [p + 1 for p in prefix] + [1] * pad           # seq_lens
+        flat += [0] * b                                       # slots are not read by graph-safe mixers
+        flat += list(range(b))                                # logit rows
+        for g, w in zip(tables, self.widths):
+            for t in g:
+                flat += list(t) + [0] * (w - len(t))
+            flat += [0] * (w * pad)
+        if self.copied is not None:
+            self.copied.synchronize()
+        self.host.copy_(torch.tensor(flat, dtype=torch.int32))
+
+    def run(self, tokens, prefix, tables) -> torch.Tensor:
+        self.fill(tokens, prefix, tables)
+        self.static.copy_(self.host, non_blocking=True)
+        self.copied = torch.cuda.Event()
+        self.copied.record()
+        self.graph.replay()
+        if self._counter:
+            self._counter["count"] += self.kernels
+        return self.logits[:len(tokens)]
 
 
 class ModelRunner:
@@ -110,6 +181,14 @@ class ModelRunner:
         self._kv_heads = max((need.kv_heads for need, _ in groups), default=1)
         self.steps_run = 0
         self.tokens_run = 0
+        self.graph_steps = 0
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        self.use_graphs = (self.device.type == "cuda" and not args.disable_cuda_graph and self.model.graph_safe
+                           and ops.__name__.endswith("csrc.ops"))
+        max_bs = args.cuda_graph_max_bs or min(self.max_requests, 256)
+        self.graph_buckets = sorted(set(args.cuda_graph_bs or
+                                        [b for b in (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256) if b <= max_bs]
+                                        + [max_bs]))
 
     # ---- construction ---------------------------------------------------------------
 
@@ -197,14 +276,53 @@ class ModelRunner:
             self._ring.mark(ring_index)
         return batch
 
+    def _graph_bucket(self, entries: Sequence[StepEntry]) -> Optional[int]:
+        if not self.use_graphs or len(entries) > self.graph_buckets[-1]:
+            return None
+        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+            return None
+        return next(b for b in self.graph_buckets if b >= len(entries))
+
+    def _decode_with_graph(self, entries: Sequence[StepEntry], bucket: int) -> torch.Tensor:
+        """A step of one token per request, each wanting its logits, through a captured graph."""
+        vocab = self.spec.vocab_size
+        wants = []
+        for e in entries:
+            if e.slot not in self.seq_lens:
+                raise KeyError(f"request slot {e.slot} is not open")
+            if not (0 <= int(e.tokens[0]) < vocab):
+                raise ValueError(f"token id outside [0, {vocab})")
+            if self.seq_lens[e.slot] + 1 > self.context_len:
+                raise ValueError(f"request would pass the context length {self.context_len}")
+            wants.append((e.slot, self.seq_lens[e.slot] + 1))
+        if len({e.slot for e in entries}) != len(entries):
+            raise ValueError("a request slot appears twice in one step")
+        if not self.cache.can_grow(wants):
+            raise OutOfPages(f"decode step of {len(entries)} tokens does not fit: {self.cache.free_pages()} pages free")
+        for slot, new_len in wants:
+            self.cache.grow(slot, new_len)
+        graph = self._graphs.get(bucket)
+        if graph is None:
+            graph = self._graphs[bucket] = _DecodeGraph(self, bucket)
+        tables = [[self.cache.block_table(g, e.slot) for e in entries] for g in range(len(self.cache.groups))]
+        self.graph_steps += 1
+        return graph.run([int(e.tokens[0]) for e in entries], [self.seq_lens[e.slot] for e in entries], tables)
+
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Runs one step and returns float32 logits ``[sum(len(e.want)), vocab]`` on the device."""
-        batch = self.prepare(entries)
-        with torch.no_grad():
-            logits = self.model.forward(batch, self.cache)
+        """Runs one step and returns float32 logits ``[sum(len(e.want)), vocab]`` on the device.
+        (A step replayed from a graph returns a view of the graph's output, valid until the next
+        step of the same batch bucket.)"""
+        bucket = self._graph_bucket(entries)
+        if bucket is not None:
+            logits = self._decode_with_graph(entries, bucket)
+            batch = None
+        else:
+            batch = self.prepare(entries)
+            with torch.no_grad():
+                logits = self.model.forward(batch, self.cache)
         for e in entries:
             self.seq_lens[e.slot] += len(e.tokens)
             self.cache.advance(e.slot, self.seq_lens[e.slot])
         self.steps_run += 1
-        self.tokens_run += batch.num_tokens
+        self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits

@@ -67,6 +67,10 @@ class AssembledModel:
                 self.state_needs.append(sneed)
         self.cache_groups = [(need, counts[g]) for need, g in sorted(group_of.items(), key=lambda kv: kv[1])]
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(b.mixer.graph_safe for b in self.blocks)
+
     # ---- weights -------------------------------------------------------------------
 
     def tensors(self) -> Dict[str, TensorSpec]:

@@ -47,6 +47,8 @@ class LayerCache:
 
 @register_part("mixer", "attention")
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec: AttentionSpec, prefix: str, ctx: BuildContext):
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError(f"{spec.num_heads} query heads do not group over {spec.num_kv_heads} kv heads")
@@ -117,7 +119,7 @@ class Attention(Mixer):
             ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out[:nd], scratch, splits,
                                  s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window)
         if batch.num_requests > nd:
-            tile_req, tile_start = batch.tiles(ops.prefill_tile_rows())
+            tile_req, tile_start = batch.tiles(ops.prefill_tile_rows(q.dtype, s.head_dim))
             ops.attention_prefill(q, cache.data, table, batch.cu_seqlens, batch.prefix_lens, tile_req, tile_start,
                                   out, s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window)
         return ops.linear(out, self.w_o, self.b_o)

@@ -100,6 +100,10 @@ class Part:
 
 
 class Mixer(Part):
+    # True when ``forward`` reads the batch's device tensors only (never its host lists), so that a
+    # decode step may be captured once in a CUDA graph and replayed with new contents.
+    graph_safe: bool = False
+
     def cache_need(self) -> Optional[CacheNeed]:
         return None
 

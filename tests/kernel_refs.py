@@ -87,7 +87,7 @@ def linear(x, weight, bias=None, out_dtype=None):
     return out.to(out_dtype or x.dtype)
 
 
-def prefill_tile_rows():
+def prefill_tile_rows(dtype=None, d=0):
     return 32
 
 

@@ -155,11 +155,12 @@ def _attention_case(dtype, nq, nkv, d, page, prefixes, news, window, seed=6, spi
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,page,window", [
     (4, 2, 16, 16, None), (8, 2, 32, 16, None), (6, 2, 48, 8, 40), (5, 1, 80, 32, None), (32, 8, 128, 64, None),
-    (2, 2, 256, 16, 100), (16, 2, 64, 16, 33), (40, 1, 32, 16, None)])
+    (2, 2, 256, 16, 100), (16, 2, 64, 16, 33), (40, 1, 32, 16, None), (40, 2, 64, 16, None), (6, 2, 192, 32, 500),
+    (8, 8, 128, 8, 64)])
 def test_attention_prefill(dtype, nq, nkv, d, page, window):
     prefixes, news = [0, 17, 130, 5, 300, 64], [1, 70, 33, 200, 129, 2]      # lengths of the reference's own test
     cache, table, q, cu, pre = _attention_case(dtype, nq, nkv, d, page, prefixes, news, window, spike=True)
-    rows = ops().prefill_tile_rows()
+    rows = ops().prefill_tile_rows(dtype, d)
     treq = [r for r, n in enumerate(news) for _ in range(0, n, rows)]
     tstart = [s for r, n in enumerate(news) for s in range(0, n, rows)]
     treq_t = torch.tensor(treq, device=DEV, dtype=torch.int32)
@@ -174,7 +175,8 @@ def test_attention_prefill(dtype, nq, nkv, d, page, window):
 @pytest.mark.parametrize("splits", [1, 3, 8])
 @pytest.mark.parametrize("nq,nkv,d,page,window", [
     (4, 2, 16, 16, None), (8, 2, 32, 16, None), (6, 2, 48, 8, 40), (5, 1, 80, 32, None), (32, 8, 128, 64, None),
-    (2, 2, 256, 16, 100), (40, 1, 32, 16, None), (16, 16, 64, 16, 7)])
+    (2, 2, 256, 16, 100), (40, 1, 32, 16, None), (16, 16, 64, 16, 7), (40, 2, 64, 16, None), (6, 2, 192, 32, 500),
+    (8, 8, 128, 8, 64)])
 def test_attention_decode(dtype, splits, nq, nkv, d, page, window):
     seqs = [1, 8, 65, 500, 1000, 3, 257]                                     # prefixes up to 999, as the reference tests
     prefixes, news = [s - 1 for s in seqs], [1] * len(seqs)
