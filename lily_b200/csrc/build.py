@@ -29,8 +29,9 @@ from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-SOURCES = ["elementwise.cu", "gemm_fp32.cu", "attention_simt.cu", "attention_mma.cu", "sampling.cu"]
-HEADERS = ["common.cuh", "attention_args.cuh"]
+SOURCES = ["elementwise.cu", "gemm_fp32.cu", "attention_simt.cu", "attention_mma.cu", "sampling.cu",
+           "attention_decode_static.cu"]
+HEADERS = ["common.cuh", "attention_args.cuh", "no_alloc.h"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
