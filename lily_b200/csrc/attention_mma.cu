@@ -24,6 +24,9 @@ namespace mma {
 
 constexpr int BN = 64;        // keys per tile
 constexpr int THREADS = 128;
+#ifndef LILY_DECODE_STAGES
+#define LILY_DECODE_STAGES 2
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -59,17 +62,17 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * (D * 2) + ((((chunk ^ row) & 7) | (chunk & ~7)) << 4));
 }
 
-template <int D, bool DECODE>
+template <int D, bool DECODE, int STAGES>
 __global__ void __launch_bounds__(THREADS)
-attention_mma_kernel(const AttnArgs a) {
+attention_mma_kernel(const AttnArgs a, const int page_shift) {
     constexpr int CH = D / 8;                  // 16-byte pieces per row
     constexpr int KSTEPS = D / 16;
     constexpr int BM = DECODE ? 16 : 64;
     constexpr int NT = DECODE ? 2 : 8;         // score n-tiles (8 keys each) per warp and key tile
     extern __shared__ __align__(128) unsigned char smem_raw[];
     unsigned char* q_s = smem_raw;                                  // [BM][D]
-    unsigned char* k_s = q_s + BM * D * 2;                          // [2][BN][D]
-    unsigned char* v_s = k_s + 2 * BN * D * 2;                      // [2][BN][D]
+    unsigned char* k_s = q_s + BM * D * 2;                          // [STAGES][BN][D]
+    unsigned char* v_s = k_s + STAGES * BN * D * 2;                 // [STAGES][BN][D]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
     const __nv_bfloat16* q = (const __nv_bfloat16*)a.q;
@@ -140,31 +143,39 @@ attention_mma_kernel(const AttnArgs a) {
     const size_t page_stride = 2 * (size_t)a.nkv * head_stride;
     const int ntiles = kend > kbeg ? (kend - kbeg + BN - 1) / BN : 0;
 
+    const __nv_bfloat16* kv_head = kv + (size_t)kvh * head_stride;
+    const int page_mask = (1 << page_shift) - 1;
     auto load_tile = [&](int t, int buf) {
         const int kb = kbeg + t * BN;
         unsigned char* kd = k_s + buf * BN * D * 2;
         unsigned char* vd = v_s + buf * BN * D * 2;
+#pragma unroll
         for (int i = tid; i < BN * CH; i += THREADS) {
             const int r = i / CH, ch = i % CH;
             const int kpos = kb + r;
             const bool ok = kpos < kend;
-            const int page = ok ? table[kpos / a.page_size] : 0;
-            const __nv_bfloat16* src = kv + (size_t)page * page_stride + (size_t)kvh * head_stride +
-                                       (size_t)(ok ? kpos % a.page_size : 0) * D + ch * 8;
-            cp_async16(smem_u32(kd + swz<D>(r, ch)), src, ok);
-            cp_async16(smem_u32(vd + swz<D>(r, ch)), src + (size_t)a.nkv * head_stride, ok);
+            const int page = ok ? table[kpos >> page_shift] : 0;
+            const __nv_bfloat16* src = kv_head + (size_t)page * page_stride + (((ok ? kpos : 0) & page_mask) * D + ch * 8);
+            const uint32_t off = swz<D>(r, ch);
+            cp_async16(smem_u32(kd + off), src, ok);
+            cp_async16(smem_u32(vd + off), src + (size_t)a.nkv * head_stride, ok);
         }
-        cp_async_commit();
     };
 
-    if (ntiles > 0) load_tile(0, 0);
+    // the pipeline keeps STAGES - 1 tiles in flight; every iteration commits one group (maybe empty)
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (st < ntiles) load_tile(st, st);
+        cp_async_commit();
+    }
     const float sl2 = a.scale * 1.4426950408889634f;       // scores are kept in units of log2(e)
 
     for (int t = 0; t < ntiles; ++t) {
-        const int buf = t & 1;
-        cp_async_wait<0>();
+        const int buf = t % STAGES;
+        cp_async_wait<STAGES - 2>();
         __syncthreads();                                    // tile t has landed; tile t-1's readers are done
-        if (t + 1 < ntiles) load_tile(t + 1, buf ^ 1);
+        if (t + STAGES - 1 < ntiles) load_tile(t + STAGES - 1, (t + STAGES - 1) % STAGES);
+        cp_async_commit();
         const unsigned char* kt = k_s + buf * BN * D * 2;
         const unsigned char* vt = v_s + buf * BN * D * 2;
         const int kb = kbeg + t * BN;
@@ -186,17 +197,24 @@ attention_mma_kernel(const AttnArgs a) {
             }
         }
 
-        // ---- mask, running maximum and sum ----------------------------------------------------
+        // ---- mask (boundary tiles only), running maximum and sum ----------------------------------
+        const int q_first = DECODE ? pos0 : pos0 + warp * 16, q_last = DECODE ? pos0 : q_first + 15;
+        const bool need_mask = kb + BN > kend || kb + BN - 1 > q_first || (a.window > 0 && kb <= q_last - a.window);
         float mx_lo = -INFINITY, mx_hi = -INFINITY;
+        if (need_mask) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int kpos = kb + key0 + j * 8 + 2 * c + (e & 1);
+                    const int qpos = (e < 2) ? qpos_lo : qpos_hi;
+                    const bool seen = kpos < kend && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window);
+                    if (!seen) s[j][e] = -INFINITY;
+                }
+            }
+        }
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int kpos = kb + key0 + j * 8 + 2 * c + (e & 1);
-                const int qpos = (e < 2) ? qpos_lo : qpos_hi;
-                const bool seen = kpos < kend && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window);
-                s[j][e] = seen ? s[j][e] * sl2 : -INFINITY;
-            }
             mx_lo = fmaxf(mx_lo, fmaxf(s[j][0], s[j][1]));
             mx_hi = fmaxf(mx_hi, fmaxf(s[j][2], s[j][3]));
         }
@@ -204,7 +222,8 @@ attention_mma_kernel(const AttnArgs a) {
         mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        // running maxima are kept in scaled (log2) units: scale > 0, so the order is the same
+        const float mn_lo = fmaxf(m_lo, mx_lo * sl2), mn_hi = fmaxf(m_hi, mx_hi * sl2);
         const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo, base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
         const float al_lo = exp2f(m_lo - base_lo), al_hi = exp2f(m_hi - base_hi);
         m_lo = mn_lo;
@@ -212,10 +231,10 @@ attention_mma_kernel(const AttnArgs a) {
         float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-            s[j][0] = exp2f(s[j][0] - base_lo);
-            s[j][1] = exp2f(s[j][1] - base_lo);
-            s[j][2] = exp2f(s[j][2] - base_hi);
-            s[j][3] = exp2f(s[j][3] - base_hi);
+            s[j][0] = exp2f(fmaf(s[j][0], sl2, -base_lo));
+            s[j][1] = exp2f(fmaf(s[j][1], sl2, -base_lo));
+            s[j][2] = exp2f(fmaf(s[j][2], sl2, -base_hi));
+            s[j][3] = exp2f(fmaf(s[j][3], sl2, -base_hi));
             sum_lo += s[j][0] + s[j][1];
             sum_hi += s[j][2] + s[j][3];
         }
@@ -319,15 +338,15 @@ attention_mma_kernel(const AttnArgs a) {
     }
 }
 
-template <int D, bool DECODE>
-static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
+template <int D, bool DECODE, int STAGES>
+static int launch(const AttnArgs& a, dim3 grid, int page_shift, cudaStream_t stream) {
     constexpr int BM = DECODE ? 16 : 64;
-    size_t smem = (size_t)BM * D * 2 + 4 * (size_t)BN * D * 2;
+    size_t smem = (size_t)BM * D * 2 + 2 * (size_t)STAGES * BN * D * 2;
     if (DECODE) {
         const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
         if ((size_t)BM * D * 2 + merge > smem) smem = (size_t)BM * D * 2 + merge;
     }
-    auto kern = attention_mma_kernel<D, DECODE>;
+    auto kern = attention_mma_kernel<D, DECODE, STAGES>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -337,17 +356,24 @@ static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
         }
         configured = true;
     }
-    kern<<<grid, THREADS, smem, stream>>>(a);
+    kern<<<grid, THREADS, smem, stream>>>(a, page_shift);
     return 0;
 }
 
 template <bool DECODE>
 static int dispatch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
+    int page_shift = 0;
+    while ((1 << page_shift) < a.page_size) ++page_shift;
+    if ((1 << page_shift) != a.page_size) {
+        set_error("attention_mma: page_size %d is not a power of two", a.page_size);
+        return 1;
+    }
+    constexpr int ST = DECODE ? LILY_DECODE_STAGES : 2;
     switch (a.d) {
-        case 64: return launch<64, DECODE>(a, grid, stream);
-        case 128: return launch<128, DECODE>(a, grid, stream);
-        case 192: return launch<192, DECODE>(a, grid, stream);
-        case 256: return launch<256, DECODE>(a, grid, stream);
+        case 64: return launch<64, DECODE, ST>(a, grid, page_shift, stream);
+        case 128: return launch<128, DECODE, ST>(a, grid, page_shift, stream);
+        case 192: return launch<192, DECODE, DECODE ? 2 : 2>(a, grid, page_shift, stream);
+        case 256: return launch<256, DECODE, 2>(a, grid, page_shift, stream);
     }
     set_error("attention_mma: head_dim %d is not one of 64, 128, 192, 256", a.d);
     return 1;

@@ -23,9 +23,67 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+// Four consecutive elements at a time (the element index is a multiple of 4 and the base pointers
+// are 16-byte aligned, which the launchers check before they pick the VEC = 4 kernels).
+__device__ __forceinline__ float4 load4(const float* p, size_t i) { return *reinterpret_cast<const float4*>(p + i); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p, size_t i) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p + i);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store4(float* p, size_t i, float4 v) { *reinterpret_cast<float4*>(p + i) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, size_t i, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p + i) = raw;
+}
+
+__device__ __forceinline__ float2 load2(const float* p, size_t i) { return *reinterpret_cast<const float2*>(p + i); }
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p, size_t i) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + i));
+}
+__device__ __forceinline__ void store2(float* p, size_t i, float2 v) { *reinterpret_cast<float2*>(p + i) = v; }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, size_t i, float2 v) {
+    *reinterpret_cast<__nv_bfloat162*>(p + i) = __floats2bfloat162_rn(v.x, v.y);
+}
+
+// A kernel input that may arrive as `splits` float32 partial sums (the slices of a split-k
+// product, `stride` elements apart) to be added up in order while it is read.
+template <typename IN>
+struct Summed {
+    const IN* p;
+    int splits;
+    size_t stride;
+    __device__ __forceinline__ float operator()(size_t i) const {
+        float v = to_float(p[i]);
+        for (int s = 1; s < splits; ++s) v += to_float(p[i + (size_t)s * stride]);
+        return v;
+    }
+    __device__ __forceinline__ float4 four(size_t i) const {
+        float4 v = load4(p, i);
+        for (int s = 1; s < splits; ++s) {
+            const float4 t = load4(p, i + (size_t)s * stride);
+            v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+        }
+        return v;
+    }
+    __device__ __forceinline__ float2 two(size_t i) const {
+        float2 v = load2(p, i);
+        for (int s = 1; s < splits; ++s) {
+            const float2 t = load2(p, i + (size_t)s * stride);
+            v.x += t.x; v.y += t.y;
+        }
+        return v;
+    }
+    __device__ __forceinline__ explicit operator bool() const { return p != nullptr; }
+};
+
 // ---------------------------------------------------------------------------- embedding
 
-template <typename T>
+template <typename T, int VEC>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int hidden, int vocab) {
     const int n = blockIdx.x;
@@ -33,7 +91,11 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host has checked the range
     const T* src = table + (size_t)id * hidden;
     float* dst = out + (size_t)n * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) store4(dst, i, load4(src, i));
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
+    }
 }
 
 // ---------------------------------------------------------------------------- add + RMSNorm
@@ -41,49 +103,85 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 // One block per output row m.  src = rows ? rows[m] : m.
 //   v = resid[src] (+ delta[src]);  if write_residual: resid[src] = v
 //   out[m] = v * rsqrt(mean(v^2) + eps) * weight
-template <typename T, typename W>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+template <typename T, typename W, typename IN, int VEC>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const Summed<IN> delta,
                                    const W* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden, float eps, int write_residual,
                                    int stash) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     float* red = smem;             // 33 floats
     float* row = smem + 40;        // hidden floats when stash
     const int m = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[m] : m) * hidden;
     float ssq = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = resid[src + i];
-        if (delta) v += to_float(delta[src + i]);
-        if (write_residual && delta) resid[src + i] = v;
-        if (stash) row[i] = v;
-        ssq += v * v;
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float4 v = load4(resid, src + i);
+            if (delta) {
+                const float4 dl = delta.four(src + i);
+                v.x += dl.x; v.y += dl.y; v.z += dl.z; v.w += dl.w;
+                if (write_residual) store4(resid, src + i, v);
+            }
+            if (stash) store4(row, i, v);
+            ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = resid[src + i];
+            if (delta) v += delta(src + i);
+            if (write_residual && delta) resid[src + i] = v;
+            if (stash) row[i] = v;
+            ssq += v * v;
+        }
     }
     const float total = block_sum(ssq, red);
     const float inv = rsqrtf(total / (float)hidden + eps);
     T* dst = out + (size_t)m * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v;
-        if (stash) {
-            v = row[i];
-        } else {
-            v = resid[src + i];
-            if (delta && !write_residual) v += to_float(delta[src + i]);
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float4 v;
+            if (stash) {
+                v = load4(row, i);
+            } else {
+                v = load4(resid, src + i);
+                if (delta && !write_residual) {
+                    const float4 dl = delta.four(src + i);
+                    v.x += dl.x; v.y += dl.y; v.z += dl.z; v.w += dl.w;
+                }
+            }
+            const float4 g = load4(weight, i);
+            store4(dst, i, make_float4((v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w));
         }
-        dst[i] = from_float<T>((v * inv) * to_float(weight[i]));
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v;
+            if (stash) {
+                v = row[i];
+            } else {
+                v = resid[src + i];
+                if (delta && !write_residual) v += delta(src + i);
+            }
+            dst[i] = from_float<T>((v * inv) * to_float(weight[i]));
+        }
     }
 }
 
 // ---------------------------------------------------------------------------- SiLU * mul
 
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+__device__ __forceinline__ float silu_times(float g, float u) { return (g / (1.f + expf(-g))) * u; }
+
+template <typename T, typename IN, int VEC>
+__global__ void silu_mul_kernel(const Summed<IN> gate_up, T* __restrict__ out, int inter, size_t total) {
+    const size_t step = (size_t)gridDim.x * blockDim.x * VEC;
+    for (size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; idx < total; idx += step) {
         const size_t n = idx / inter;
         const int i = (int)(idx - n * inter);
-        const float g = to_float(gate_up[n * 2 * inter + i]);
-        const float u = to_float(gate_up[n * 2 * inter + inter + i]);
-        out[idx] = from_float<T>((g / (1.f + expf(-g))) * u);
+        if (VEC == 4) {
+            const float4 g = gate_up.four(n * 2 * inter + i), u = gate_up.four(n * 2 * inter + inter + i);
+            store4(out, idx, make_float4(silu_times(g.x, u.x), silu_times(g.y, u.y), silu_times(g.z, u.z), silu_times(g.w, u.w)));
+        } else {
+            out[idx] = from_float<T>(silu_times(gate_up(n * 2 * inter + i), gate_up(n * 2 * inter + inter + i)));
+        }
     }
 }
 
@@ -92,8 +190,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 // grid (tokens, ceil(heads / 4)), block (32, 4): one warp per (token, head) of the fused
 // projection [q heads | k heads | v heads].  q heads go to q_out, k and v heads into the
 // token's place in its page.
-template <typename T, typename W>
-__global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const W* __restrict__ q_gain,
+template <typename T, typename W, typename IN, int VEC>
+__global__ void qk_norm_rope_write_kernel(const Summed<IN> qkv, const W* __restrict__ q_gain,
                                           const W* __restrict__ k_gain, float eps,
                                           const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                           const int* __restrict__ positions, const int* __restrict__ token_req,
@@ -106,7 +204,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const W* __
     if (head >= nheads) return;
     const int lane = threadIdx.x;
     const int pos = positions[n];
-    const T* src = qkv + (size_t)n * (nq + 2 * nkv) * d + (size_t)head * d;
+    const size_t src = (size_t)n * (nq + 2 * nkv) * d + (size_t)head * d;
     T* dst;
     const W* gain = nullptr;
     bool rotate = true;
@@ -122,24 +220,65 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const W* __
         rotate = !is_v;
     }
     float inv = 1.f;
+    if (VEC == 2) {
+        // two neighbouring features per lane and step (d, the rotary width and its half are even)
+        if (gain) {
+            float ssq = 0.f;
+            for (int i = 2 * lane; i < d; i += 64) {
+                const float2 x = qkv.two(src + i);
+                ssq += x.x * x.x + x.y * x.y;
+            }
+            inv = rsqrtf(warp_sum(ssq) / (float)d + eps);
+        }
+        if (!rotate) {
+            for (int i = 2 * lane; i < d; i += 64) store2(dst, i, qkv.two(src + i));
+            return;
+        }
+        const int half = rd >> 1;
+        for (int i = 2 * lane; i < half; i += 64) {
+            float2 x1 = qkv.two(src + i), x2 = qkv.two(src + i + half);
+            if (gain) {
+                const float2 g1 = load2(gain, i), g2 = load2(gain, i + half);
+                x1 = make_float2((x1.x * inv) * g1.x, (x1.y * inv) * g1.y);
+                x2 = make_float2((x2.x * inv) * g2.x, (x2.y * inv) * g2.y);
+            }
+            float2 o1 = x1, o2 = x2;
+            if (cos_t) {
+                const float2 cc = load2(cos_t, (size_t)pos * half + i), ss = load2(sin_t, (size_t)pos * half + i);
+                o1 = make_float2(x1.x * cc.x - x2.x * ss.x, x1.y * cc.y - x2.y * ss.y);
+                o2 = make_float2(x2.x * cc.x + x1.x * ss.x, x2.y * cc.y + x1.y * ss.y);
+            }
+            store2(dst, i, o1);
+            store2(dst, i + half, o2);
+        }
+        for (int i = rd + 2 * lane; i < d; i += 64) {
+            float2 x = qkv.two(src + i);
+            if (gain) {
+                const float2 gg = load2(gain, i);
+                x = make_float2((x.x * inv) * gg.x, (x.y * inv) * gg.y);
+            }
+            store2(dst, i, x);
+        }
+        return;
+    }
     if (gain) {
         float ssq = 0.f;
         for (int i = lane; i < d; i += 32) {
-            const float x = to_float(src[i]);
+            const float x = qkv(src + i);
             ssq += x * x;
         }
         ssq = warp_sum(ssq);
         inv = rsqrtf(ssq / (float)d + eps);
     }
     if (!rotate) {
-        for (int i = lane; i < d; i += 32) dst[i] = src[i];
+        for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(qkv(src + i));
         return;
     }
     const int half = rd >> 1;
     const float* c = cos_t ? cos_t + (size_t)pos * half : nullptr;
     const float* s = sin_t ? sin_t + (size_t)pos * half : nullptr;
     for (int i = lane; i < half; i += 32) {
-        float x1 = to_float(src[i]), x2 = to_float(src[i + half]);
+        float x1 = qkv(src + i), x2 = qkv(src + i + half);
         if (gain) {
             x1 = (x1 * inv) * to_float(gain[i]);
             x2 = (x2 * inv) * to_float(gain[i + half]);
@@ -154,7 +293,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const W* __
         dst[i + half] = from_float<T>(o2);
     }
     for (int i = rd + lane; i < d; i += 32) {
-        float x = to_float(src[i]);
+        float x = qkv(src + i);
         if (gain) x = (x * inv) * to_float(gain[i]);
         dst[i] = from_float<T>(x);
     }
@@ -172,57 +311,88 @@ __global__ void cast_kernel(const A* __restrict__ in, B* __restrict__ out, size_
 
 using namespace lily;
 
+static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 LILY_API const char* lily_last_error() { return g_error; }
 
 LILY_API int lily_embed(const void* table, int table_dtype, const int* ids, float* out, int tokens, int hidden,
                         int vocab, cudaStream_t stream) {
     if (tokens == 0) return 0;
     LILY_REQUIRE(hidden > 0 && vocab > 0, "embed: bad sizes hidden=%d vocab=%d", hidden, vocab);
-    if (table_dtype == kBF16)
-        embed_kernel<<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
-    else
-        embed_kernel<<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+    const bool vec = hidden % 4 == 0 && aligned16(table) && aligned16(out);
+    if (table_dtype == kBF16) {
+        if (vec) embed_kernel<__nv_bfloat16, 4><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
+        else embed_kernel<__nv_bfloat16, 1><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
+    } else {
+        if (vec) embed_kernel<float, 4><<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+        else embed_kernel<float, 1><<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+    }
     LILY_CHECK_LAUNCH("embed");
     return 0;
 }
 
-template <typename T, typename W>
-static int launch_add_rmsnorm(float* resid, const void* delta, const void* weight, void* out, const int* rows,
-                              int out_rows, int hidden, float eps, int write_residual, cudaStream_t stream) {
+// `in_dtype` is the dtype of the summed input (delta, gate_up, qkv): the activation dtype with one
+// split, or float32 partial sums with `splits` slices `stride` elements apart.
+template <typename T, typename W, typename IN>
+static void launch_add_rmsnorm(float* resid, const void* delta, int splits, size_t stride, const void* weight, void* out,
+                               const int* rows, int out_rows, int hidden, float eps, int write_residual,
+                               cudaStream_t stream) {
     const int stash = hidden <= 11264;   // 40 + hidden floats stay within 48 KB
     const size_t smem = (40 + (stash ? hidden : 0)) * sizeof(float);
-    const int threads = hidden >= 2048 ? 512 : 256;
-    add_rmsnorm_kernel<T, W><<<out_rows, threads, smem, stream>>>(resid, (const T*)delta, (const W*)weight, (T*)out,
-                                                               rows, hidden, eps, write_residual, stash);
+    const bool vec = hidden % 4 == 0 && stride % 4 == 0 && aligned16(resid) && aligned16(delta) && aligned16(weight) && aligned16(out);
+    const int per = vec ? 4 : 1;
+    const int threads = hidden >= 2048 * per ? 512 : (hidden >= 1024 * per ? 256 : 128);
+    const Summed<IN> d{(const IN*)delta, splits, stride};
+    if (vec)
+        add_rmsnorm_kernel<T, W, IN, 4><<<out_rows, threads, smem, stream>>>(resid, d, (const W*)weight, (T*)out, rows, hidden, eps, write_residual, stash);
+    else
+        add_rmsnorm_kernel<T, W, IN, 1><<<out_rows, threads, smem, stream>>>(resid, d, (const W*)weight, (T*)out, rows, hidden, eps, write_residual, stash);
+}
+
+static int check_summed(const char* name, int act_dtype, int in_dtype, int splits) {
+    LILY_REQUIRE(splits >= 1, "%s: %d splits", name, splits);
+    LILY_REQUIRE(in_dtype == act_dtype || in_dtype == kF32, "%s: the input is the activation dtype or float32 partial sums", name);
+    LILY_REQUIRE(splits == 1 || in_dtype == kF32, "%s: only float32 partial sums come in several splits", name);
     return 0;
 }
 
 LILY_API int lily_add_rmsnorm(float* resid, const void* delta, const void* weight, void* out, const int* rows,
                               int out_rows, int hidden, float eps, int write_residual, int act_dtype,
-                              int weight_dtype, cudaStream_t stream) {
+                              int weight_dtype, int delta_dtype, int delta_splits, size_t delta_stride,
+                              cudaStream_t stream) {
     if (out_rows == 0) return 0;
     LILY_REQUIRE(hidden > 0, "add_rmsnorm: hidden=%d", hidden);
     LILY_REQUIRE(!(rows && write_residual && delta), "add_rmsnorm: gathered rows cannot write the residual back");
-    if (act_dtype == kBF16 && weight_dtype == kBF16)
-        launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, weight, out, rows, out_rows, hidden, eps, write_residual, stream);
-    else if (act_dtype == kBF16)
-        launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, weight, out, rows, out_rows, hidden, eps, write_residual, stream);
-    else if (weight_dtype == kBF16)
-        launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, weight, out, rows, out_rows, hidden, eps, write_residual, stream);
-    else
-        launch_add_rmsnorm<float, float>(resid, delta, weight, out, rows, out_rows, hidden, eps, write_residual, stream);
+    if (check_summed("add_rmsnorm", act_dtype, delta_dtype, delta_splits)) return 1;
+#define GO(T, W, IN) launch_add_rmsnorm<T, W, IN>(resid, delta, delta_splits, delta_stride, weight, out, rows, out_rows, hidden, eps, write_residual, stream)
+    const bool wb = weight_dtype == kBF16, ib = delta_dtype == kBF16;
+    if (act_dtype == kBF16) {
+        if (wb && ib) GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+        else if (wb) GO(__nv_bfloat16, __nv_bfloat16, float);
+        else if (ib) GO(__nv_bfloat16, float, __nv_bfloat16);
+        else GO(__nv_bfloat16, float, float);
+    } else {
+        if (wb) GO(float, __nv_bfloat16, float);
+        else GO(float, float, float);
+    }
+#undef GO
     LILY_CHECK_LAUNCH("add_rmsnorm");
     return 0;
 }
 
-LILY_API int lily_silu_mul(const void* gate_up, void* out, int tokens, int inter, int act_dtype, cudaStream_t stream) {
+LILY_API int lily_silu_mul(const void* gate_up, void* out, int tokens, int inter, int act_dtype, int in_dtype,
+                           int splits, size_t stride, cudaStream_t stream) {
     const size_t total = (size_t)tokens * inter;
     if (total == 0) return 0;
-    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (act_dtype == kBF16)
-        silu_mul_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
-    else
-        silu_mul_kernel<<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    if (check_summed("silu_mul", act_dtype, in_dtype, splits)) return 1;
+    const bool vec = inter % 4 == 0 && stride % 4 == 0 && aligned16(gate_up) && aligned16(out);
+    const size_t work = vec ? total / 4 : total;
+    const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
+#define GO(T, IN, V) silu_mul_kernel<T, IN, V><<<blocks, 256, 0, stream>>>(Summed<IN>{(const IN*)gate_up, splits, stride}, (T*)out, inter, total)
+    if (act_dtype == kBF16 && in_dtype == kBF16) { if (vec) GO(__nv_bfloat16, __nv_bfloat16, 4); else GO(__nv_bfloat16, __nv_bfloat16, 1); }
+    else if (act_dtype == kBF16) { if (vec) GO(__nv_bfloat16, float, 4); else GO(__nv_bfloat16, float, 1); }
+    else { if (vec) GO(float, float, 4); else GO(float, float, 1); }
+#undef GO
     LILY_CHECK_LAUNCH("silu_mul");
     return 0;
 }
@@ -231,22 +401,35 @@ LILY_API int lily_qk_norm_rope_write(const void* qkv, const void* q_gain, const 
                                      const float* cos_t, const float* sin_t, const int* positions,
                                      const int* token_req, const int* block_table, int bt_stride, void* kv_layer,
                                      void* q_out, int tokens, int nq, int nkv, int d, int rd, int page_size,
-                                     int write_kv, int act_dtype, int gain_dtype, cudaStream_t stream) {
+                                     int write_kv, int act_dtype, int gain_dtype, int in_dtype, int splits,
+                                     size_t stride, cudaStream_t stream) {
     if (tokens == 0) return 0;
     LILY_REQUIRE(d > 0 && rd >= 0 && rd <= d && rd % 2 == 0, "qk_norm_rope_write: rotary_dim %d does not fit head_dim %d", rd, d);
     LILY_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "qk_norm_rope_write: q and k gains come together");
     LILY_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "qk_norm_rope_write: cos and sin tables come together");
+    if (check_summed("qk_norm_rope_write", act_dtype, in_dtype, splits)) return 1;
     const int nheads = write_kv ? nq + 2 * nkv : nq;
     dim3 grid(tokens, (nheads + 3) / 4), block(32, 4);
-#define LAUNCH(T, W)                                                                                              \
-    qk_norm_rope_write_kernel<T, W><<<grid, block, 0, stream>>>((const T*)qkv, (const W*)q_gain, (const W*)k_gain, eps, \
-        cos_t, sin_t, positions, token_req, block_table, bt_stride, (T*)kv_layer, (T*)q_out, nq, nkv, d,          \
-        cos_t ? rd : 0, page_size, write_kv)
-    if (act_dtype == kBF16 && gain_dtype == kBF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
-    else if (act_dtype == kBF16) LAUNCH(__nv_bfloat16, float);
-    else if (gain_dtype == kBF16) LAUNCH(float, __nv_bfloat16);
-    else LAUNCH(float, float);
+    const int rot = cos_t ? rd : 0;
+    const bool vec = d % 2 == 0 && rot % 4 == 0 && stride % 2 == 0 && aligned16(qkv) && aligned16(kv_layer) &&
+                     aligned16(q_out) && aligned16(q_gain) && aligned16(k_gain) && aligned16(cos_t) && aligned16(sin_t);
+#define LAUNCH_V(T, W, IN, V)                                                                                     \
+    qk_norm_rope_write_kernel<T, W, IN, V><<<grid, block, 0, stream>>>(Summed<IN>{(const IN*)qkv, splits, stride}, \
+        (const W*)q_gain, (const W*)k_gain, eps, cos_t, sin_t, positions, token_req, block_table, bt_stride,      \
+        (T*)kv_layer, (T*)q_out, nq, nkv, d, rot, page_size, write_kv)
+#define LAUNCH(T, W, IN) do { if (vec) LAUNCH_V(T, W, IN, 2); else LAUNCH_V(T, W, IN, 1); } while (0)
+    const bool gb = gain_dtype == kBF16, ib = in_dtype == kBF16;
+    if (act_dtype == kBF16) {
+        if (gb && ib) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+        else if (gb) LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
+        else if (ib) LAUNCH(__nv_bfloat16, float, __nv_bfloat16);
+        else LAUNCH(__nv_bfloat16, float, float);
+    } else {
+        if (gb) LAUNCH(float, __nv_bfloat16, float);
+        else LAUNCH(float, float, float);
+    }
 #undef LAUNCH
+#undef LAUNCH_V
     LILY_CHECK_LAUNCH("qk_norm_rope_write");
     return 0;
 }

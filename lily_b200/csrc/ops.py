@@ -22,10 +22,11 @@ _vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_
 
 _SIGNATURES = {
     "lily_embed": [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
-    "lily_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _vp],
-    "lily_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
+    "lily_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _sz, _vp],
+    "lily_silu_mul": [_vp, _vp, _i, _i, _i, _i, _i, _sz, _vp],
     "lily_qk_norm_rope_write": [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                _i, _i, _i, _vp],
+                                _i, _i, _i, _i, _i, _sz, _vp],
+    "lily_skinny_gemm": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "lily_cast": [_vp, _i, _vp, _i, _sz, _vp],
     "lily_gemm_fp32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
@@ -55,6 +56,9 @@ def library():
             fn.argtypes = args
             fn.restype = _i
         lib.lily_attention_prefill_simt_rows.restype = _i
+        lib.lily_skinny_gemm_max_rows.restype = _i
+        lib.lily_skinny_gemm_splits.argtypes = [_i, _i, _i]
+        lib.lily_skinny_gemm_splits.restype = _i
         lib.lily_attention_prefill_mma_rows.restype = _i
         lib.lily_attention_mma_supports.argtypes = [_i]
         lib.lily_attention_mma_supports.restype = _i
@@ -119,11 +123,24 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = 
     return out
 
 
+def _summed(t: torch.Tensor, rows: int, cols: int, what: str):
+    """(splits, stride) of a kernel input that is either [rows, cols] in the activation dtype or
+    float32 partial sums [splits, rows, cols] of a split-k product."""
+    if t.dim() == 3:
+        if t.dtype != torch.float32 or tuple(t.shape[1:]) != (rows, cols):
+            raise KernelError(f"{what}: partial sums must be float32 [splits, {rows}, {cols}], got {t.dtype} {tuple(t.shape)}")
+        return t.shape[0], rows * cols
+    if tuple(t.shape) != (rows, cols):
+        raise KernelError(f"{what}: expected [{rows}, {cols}], got {tuple(t.shape)}")
+    return 1, 0
+
+
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, write_residual: bool = True,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``resid += delta`` (float32, in place when ``write_residual``), then RMSNorm with ``weight``.
-    With ``rows`` only those rows are normalised (and the residual is left as it is)."""
+    ``delta`` is [tokens, hidden] in the activation dtype or float32 partial sums [splits, tokens,
+    hidden].  With ``rows`` only those rows are normalised (and the residual is left as it is)."""
     _dev(resid, delta, weight, rows, out)
     if resid.dtype != torch.float32:
         raise KernelError("the residual stream is float32")
@@ -133,23 +150,27 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
         write_residual = False
     if out is None:
         out = torch.empty((m, hidden), dtype=out_dtype, device=resid.device)
-    if delta is not None and (delta.dtype != out.dtype or delta.shape != resid.shape):
-        raise KernelError(f"delta {delta.dtype} {tuple(delta.shape)} does not match out {out.dtype} / residual "
-                          f"{tuple(resid.shape)}")
+    splits, stride = (1, 0) if delta is None else _summed(delta, resid.shape[0], hidden, "add_rmsnorm delta")
+    if delta is not None and delta.dtype not in (out.dtype, torch.float32):
+        raise KernelError(f"delta {delta.dtype} does not match out {out.dtype}")
     if weight.numel() != hidden:
         raise KernelError(f"norm gain has {weight.numel()} entries, rows have {hidden}")
     _call("lily_add_rmsnorm", _p(resid), _p(delta), _p(weight), _p(out), _i32(rows, "rows"), m, hidden, float(eps),
-          int(write_residual), _dt(out), _dt(weight), _stream())
+          int(write_residual), _dt(out), _dt(weight), _dt(delta) if delta is not None else _dt(out), splits, stride,
+          _stream())
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+def silu_mul(gate_up: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate_up[:, :I]) * gate_up[:, I:]``; ``gate_up`` may be float32 partial sums
+    [splits, tokens, 2I], in which case ``out_dtype`` says what to write."""
     _dev(gate_up, out)
-    n, two_i = gate_up.shape
+    n, two_i = gate_up.shape[-2:]
+    splits, stride = _summed(gate_up, n, two_i, "silu_mul")
     if out is None:
-        out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
-    _call("lily_silu_mul", _p(gate_up), _p(out), n, two_i // 2, _dt(gate_up), _stream())
+        out = torch.empty((n, two_i // 2), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
+    _call("lily_silu_mul", _p(gate_up), _p(out), n, two_i // 2, _dt(out), _dt(gate_up), splits, stride, _stream())
     return out
 
 
@@ -159,12 +180,12 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain
                        kv_layer: torch.Tensor, nq: int, nkv: int, d: int, rotary_dim: int, page_size: int,
                        write_kv: bool = True, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Per-head RMSNorm of q and k (when gains are given), rotation by the tables, q to ``q_out``
-    [tokens, nq * d], k and v into the token's place in its page of ``kv_layer``."""
+    [tokens, nq * d], k and v into the token's place in its page of ``kv_layer``.  ``qkv`` is
+    [tokens, (nq + 2 nkv) d] in the cache's dtype or float32 partial sums [splits, tokens, ...]."""
     _dev(qkv, q_gain, k_gain, cos, sin, positions, token_req, block_table, kv_layer, q_out)
-    n = qkv.shape[0]
-    if qkv.shape[1] != (nq + 2 * nkv) * d:
-        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(nq + 2 * nkv) * d}")
-    if kv_layer.dtype != qkv.dtype:
+    n = qkv.shape[-2]
+    splits, stride = _summed(qkv, n, (nq + 2 * nkv) * d, "qk_norm_rope_write qkv")
+    if qkv.dtype not in (kv_layer.dtype, torch.float32):
         raise KernelError(f"cache dtype {kv_layer.dtype} differs from activations {qkv.dtype}")
     if tuple(kv_layer.shape[1:]) != (2, nkv, page_size, d):
         raise KernelError(f"cache layer shape {tuple(kv_layer.shape)} does not fit kv_heads={nkv} page={page_size} d={d}")
@@ -173,11 +194,11 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain
     if q_gain is not None and q_gain.dtype != k_gain.dtype:
         raise KernelError("q and k gains must share a dtype")
     if q_out is None:
-        q_out = torch.empty((n, nq * d), dtype=qkv.dtype, device=qkv.device)
+        q_out = torch.empty((n, nq * d), dtype=kv_layer.dtype, device=qkv.device)
     _call("lily_qk_norm_rope_write", _p(qkv), _p(q_gain), _p(k_gain), float(eps), _p(cos), _p(sin),
           _i32(positions, "positions"), _i32(token_req, "token_req"), _i32(block_table, "block_table"),
           block_table.shape[-1], _p(kv_layer), _p(q_out), n, nq, nkv, d, rotary_dim, page_size, int(write_kv),
-          _dt(qkv), _dt(q_gain) if q_gain is not None else _F32, _stream())
+          _dt(kv_layer), _dt(q_gain) if q_gain is not None else _F32, _dt(qkv), splits, stride, _stream())
     return q_out
 
 
@@ -216,6 +237,41 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if bias is not None:
         return torch.addmm(bias.to(x.dtype), x, weight.t())
     return torch.mm(x, weight.t())
+
+
+def linear_split(x: torch.Tensor, weight: torch.Tensor, splits: Optional[int] = None) -> Optional[torch.Tensor]:
+    """``x [M, K] . weight [N, K]^T`` for a few tokens (decode) by this package's weight-streaming
+    kernel, as float32 partial sums ``[splits, M, N]`` over slices of K that the consuming kernel
+    (``add_rmsnorm``, ``silu_mul``, ``qk_norm_rope_write``) adds up.  Without ``splits`` the kernel's
+    own rule decides, and None comes back for shapes it leaves to the library product (wide
+    outputs, more than 16 tokens) or cannot take (K not a multiple of 64, not bfloat16); the caller
+    then uses ``linear``.  With ``splits`` given the kernel runs whenever it can (up to 64 tokens)."""
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        return None
+    m, k = x.shape
+    n = weight.shape[0]
+    lib = library()
+    if m > lib.lily_skinny_gemm_max_rows() or m < 1 or weight.shape[1] != k or k % 64:
+        return None
+    if splits is None:
+        splits = int(lib.lily_skinny_gemm_splits(m, n, k))
+    if splits < 1:
+        return None
+    _dev(x, weight)
+    parts = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
+    _call("lily_skinny_gemm", _p(x), _p(weight), _p(parts), m, n, k, splits, _stream())
+    return parts
+
+
+def linear_auto(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The product in whichever form is fastest for the shape: float32 partial sums from
+    ``linear_split`` for a few tokens, else ``linear``'s [M, N].  For producers whose consumer is
+    one of the kernels that take either form."""
+    if bias is None:
+        parts = linear_split(x, weight)
+        if parts is not None:
+            return parts
+    return linear(x, weight, bias)
 
 
 # ------------------------------------------------------------------------------ attention

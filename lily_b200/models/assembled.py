@@ -129,4 +129,9 @@ class AssembledModel:
         if batch.logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
         x = self.final_norm.forward(residual, delta, rows=batch.logit_rows)
+        split = getattr(ops, "linear_split", None)
+        if split is not None:                     # a few rows: stream the head once, float32 out
+            parts = split(x, self.head)
+            if parts is not None and parts.shape[0] == 1:
+                return parts[0]
         return ops.linear(x, self.head, out_dtype=torch.float32)

@@ -104,13 +104,13 @@ class Attention(Mixer):
         s, ops = self.spec, self.ctx.ops
         page = cache.data.shape[3]
         table = batch.block_tables[cache.group]
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        qkv = getattr(ops, "linear_auto", ops.linear)(x, self.w_qkv, self.b_qkv)
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         q = ops.qk_norm_rope_write(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, batch.positions,
                                    batch.token_req, table, cache.data, s.num_heads, s.num_kv_heads, s.head_dim,
                                    rotary_dim, page, write_kv=write_cache)
-        out = torch.empty_like(q)
+        out = torch.empty_like(q)       # [tokens, heads * head_dim]
         nd = batch.num_decode
         if nd:
             splits = batch.decode_splits
@@ -122,4 +122,4 @@ class Attention(Mixer):
             tile_req, tile_start = batch.tiles(ops.prefill_tile_rows(q.dtype, s.head_dim))
             ops.attention_prefill(q, cache.data, table, batch.cu_seqlens, batch.prefix_lens, tile_req, tile_start,
                                   out, s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window)
-        return ops.linear(out, self.w_o, self.b_o)
+        return getattr(ops, "linear_auto", ops.linear)(out, self.w_o, self.b_o)

@@ -44,4 +44,5 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, batch):
         ops = self.ctx.ops
-        return ops.linear(ops.silu_mul(ops.linear(x, self.w_gate_up)), self.w_down)
+        product = getattr(ops, "linear_auto", ops.linear)        # partial sums for a few tokens, else [M, N]
+        return product(ops.silu_mul(product(x, self.w_gate_up), x.dtype), self.w_down)

@@ -39,7 +39,7 @@ def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_residual=
     return ((v * torch.rsqrt(var + eps)) * weight.float()).to(out_dtype)
 
 
-def silu_mul(gate_up, out=None):
+def silu_mul(gate_up, out_dtype=None, out=None):
     i = gate_up.shape[1] // 2
     g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
     return ((g / (1 + torch.exp(-g))) * u).to(gate_up.dtype)

@@ -93,6 +93,58 @@ def test_linear_bf16_and_fp32_logits():
     torch.testing.assert_close(ops().linear(x, w, b).float(), want + b.float(), atol=0.5, rtol=2e-2)
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (8, 6144, 4096), (8, 4096, 12288), (5, 331, 128), (16, 1000, 256),
+                                   (17, 136, 64), (33, 2000, 1024), (64, 4096, 1024), (3, 24576, 4096), (64, 24, 64)])
+def test_skinny_gemm_partial_sums(m, n, k):
+    g = torch.Generator(device=DEV).manual_seed(11)
+    x = torch.randn(m, k, device=DEV, generator=g).bfloat16()
+    w = torch.randn(n, k, device=DEV, generator=g).bfloat16()
+    parts = ops().linear_split(x, w, splits=max(1, min(5, k // 128)))
+    assert parts is not None and parts.dtype == torch.float32 and parts.shape[1:] == (m, n)
+    auto = ops().linear_split(x, w)                     # the kernel's own rule may leave the shape to the library
+    if auto is not None:
+        torch.testing.assert_close(auto.sum(0), parts.sum(0), atol=1e-3, rtol=1e-4)
+    want = x.double() @ w.double().t()
+    got = parts.double().sum(0)
+    assert float((got - want).abs().max()) < 2e-5 * (k ** 0.5) * 4      # float32 accumulation of exact products
+    # a token's result does not depend on the other tokens in the batch
+    alone = ops().linear_split(x[:1].contiguous(), w, splits=parts.shape[0])
+    assert torch.equal(alone[:, 0], parts[:, 0])
+    # shapes the kernel does not take are left to the library product
+    assert ops().linear_split(torch.zeros(65, k, device=DEV).bfloat16(), w) is None
+    assert ops().linear_split(torch.zeros(2, 72, device=DEV).bfloat16(), torch.zeros(8, 72, device=DEV).bfloat16()) is None
+    assert ops().linear_split(x.float(), w.float()) is None
+
+
+def test_kernels_add_up_partial_sums():
+    o = ops()
+    g = torch.Generator(device=DEV).manual_seed(12)
+    m, h, nq, nkv, d, page = 7, 136, 4, 2, 16, 16
+    parts = torch.randn(3, m, h, device=DEV, generator=g)
+    whole = (parts[0] + parts[1]) + parts[2]
+    w = (1 + 0.1 * torch.randn(h, device=DEV, generator=g)).bfloat16()
+    r1, r2 = torch.randn(m, h, device=DEV, generator=g), None
+    r2 = r1.clone()
+    a = o.add_rmsnorm(r1, parts, w, 1e-6, torch.bfloat16)
+    b = o.add_rmsnorm(r2, whole, w, 1e-6, torch.bfloat16)
+    assert torch.equal(a, b) and torch.equal(r1, r2)
+    gu = torch.randn(3, m, 2 * 200, device=DEV, generator=g)
+    assert torch.equal(o.silu_mul(gu, torch.bfloat16), o.silu_mul((gu[0] + gu[1]) + gu[2], torch.bfloat16))
+    torch.testing.assert_close(o.silu_mul(gu, torch.bfloat16).float(),
+                               ref.silu_mul(gu.sum(0)).float(), atol=2e-2, rtol=2e-2)
+    qkv = torch.randn(3, m, (nq + 2 * nkv) * d, device=DEV, generator=g)
+    pos = torch.arange(m, device=DEV, dtype=torch.int32) + 5
+    req = torch.zeros(m, device=DEV, dtype=torch.int32)
+    table = torch.tensor([[2, 1]], device=DEV, dtype=torch.int32)
+    cos, sin = torch.rand(32, d // 2, device=DEV, generator=g), torch.rand(32, d // 2, device=DEV, generator=g)
+    gain = torch.ones(d, device=DEV).bfloat16()
+    c1 = torch.zeros(3, 2, nkv, page, d, device=DEV).bfloat16()
+    c2 = c1.clone()
+    q1 = o.qk_norm_rope_write(qkv, gain, gain, 1e-6, cos, sin, pos, req, table, c1, nq, nkv, d, d, page)
+    q2 = o.qk_norm_rope_write((qkv[0] + qkv[1]) + qkv[2], gain, gain, 1e-6, cos, sin, pos, req, table, c2, nq, nkv, d, d, page)
+    assert q1.dtype == torch.bfloat16 and torch.equal(q1, q2) and torch.equal(c1, c2) and float(c1.abs().max()) > 0
+
+
 def _cache(pages, nkv, page_size, d, dtype, g):
     return (torch.randn(pages + 1, 2, nkv, page_size, d, device=DEV, generator=g)).to(dtype)
 
