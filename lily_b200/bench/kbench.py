@@ -9,6 +9,8 @@ from L2, results as achieved GB/s or TFLOP/s and as a fraction of the measured p
     python -m lily_b200.bench.kbench rope --tokens 2048
     python -m lily_b200.bench.kbench linear --tokens 8 --n 4096 --k 12288          (library product)
     python -m lily_b200.bench.kbench linear_split --tokens 8 --n 4096 --k 12288    (this package's decode product)
+    python -m lily_b200.bench.kbench gemm_tc --tokens 2048 --n 6144 --k 4096       (tcgen05 product)
+    python -m lily_b200.bench.kbench gemm_tc_silu --tokens 2048 --n 24576 --k 4096 (tcgen05 product + SiLU*mul)
 
 Sizes default to the Qwen3-8B layer (32 query heads, 8 kv heads, head size 128, width 4096,
 intermediate 12288); every size is a flag.  ``--reps 1 --copies 1`` gives a run small enough for a
@@ -80,7 +82,7 @@ def time_ms(fns, reps, warmup=3, graph=False):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attention_decode", "attention_prefill", "add_rmsnorm", "silu_mul", "rope", "linear", "linear_split"])
+    ap.add_argument("kernel", choices=["attention_decode", "attention_prefill", "add_rmsnorm", "silu_mul", "rope", "linear", "linear_split", "gemm_tc", "gemm_tc_silu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
@@ -184,8 +186,14 @@ def main() -> int:
         for _ in range(a.copies):
             x = torch.randn(a.tokens, a.k, device=dev, generator=g).to(dt)
             w = torch.randn(a.n, a.k, device=dev, generator=g).to(dt)
-            fns.append((lambda x=x, w=w: ops.linear_split(x, w)) if a.kernel == "linear_split" else
-                       (lambda x=x, w=w: ops.linear(x, w)))
+            if a.kernel == "linear_split":
+                fns.append(lambda x=x, w=w: ops.linear_split(x, w))
+            elif a.kernel == "gemm_tc":
+                fns.append(lambda x=x, w=w: ops.gemm_tc(x, w))
+            elif a.kernel == "gemm_tc_silu":
+                fns.append(lambda x=x, w=w: ops.gemm_tc(x, w, silu_mul_block=True))
+            else:
+                fns.append(lambda x=x, w=w: ops.linear(x, w))
         bytes_moved = (a.n * a.k + a.tokens * (a.n + a.k)) * item
         flops = 2.0 * a.tokens * a.n * a.k
         extra = {}

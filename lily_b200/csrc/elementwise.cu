@@ -170,17 +170,20 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const Summed<IN> d
 
 __device__ __forceinline__ float silu_times(float g, float u) { return (g / (1.f + expf(-g))) * u; }
 
+// The gate and up columns of one token alternate in runs of `block`: [gate block | up block | gate
+// block | ...]; block == inter is the plain [all gate | all up] order.
 template <typename T, typename IN, int VEC>
-__global__ void silu_mul_kernel(const Summed<IN> gate_up, T* __restrict__ out, int inter, size_t total) {
+__global__ void silu_mul_kernel(const Summed<IN> gate_up, T* __restrict__ out, int inter, int block, size_t total) {
     const size_t step = (size_t)gridDim.x * blockDim.x * VEC;
     for (size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; idx < total; idx += step) {
         const size_t n = idx / inter;
         const int i = (int)(idx - n * inter);
+        const size_t at = n * 2 * inter + (size_t)(i / block) * 2 * block + (i % block);
         if (VEC == 4) {
-            const float4 g = gate_up.four(n * 2 * inter + i), u = gate_up.four(n * 2 * inter + inter + i);
+            const float4 g = gate_up.four(at), u = gate_up.four(at + block);
             store4(out, idx, make_float4(silu_times(g.x, u.x), silu_times(g.y, u.y), silu_times(g.z, u.z), silu_times(g.w, u.w)));
         } else {
-            out[idx] = from_float<T>(silu_times(gate_up(n * 2 * inter + i), gate_up(n * 2 * inter + inter + i)));
+            out[idx] = from_float<T>(silu_times(gate_up(at), gate_up(at + block)));
         }
     }
 }
@@ -380,15 +383,16 @@ LILY_API int lily_add_rmsnorm(float* resid, const void* delta, const void* weigh
     return 0;
 }
 
-LILY_API int lily_silu_mul(const void* gate_up, void* out, int tokens, int inter, int act_dtype, int in_dtype,
-                           int splits, size_t stride, cudaStream_t stream) {
+LILY_API int lily_silu_mul(const void* gate_up, void* out, int tokens, int inter, int block, int act_dtype,
+                           int in_dtype, int splits, size_t stride, cudaStream_t stream) {
     const size_t total = (size_t)tokens * inter;
     if (total == 0) return 0;
+    LILY_REQUIRE(block > 0 && inter % block == 0, "silu_mul: gate/up runs of %d do not tile %d columns", block, inter);
     if (check_summed("silu_mul", act_dtype, in_dtype, splits)) return 1;
-    const bool vec = inter % 4 == 0 && stride % 4 == 0 && aligned16(gate_up) && aligned16(out);
+    const bool vec = block % 4 == 0 && stride % 4 == 0 && aligned16(gate_up) && aligned16(out);
     const size_t work = vec ? total / 4 : total;
     const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
-#define GO(T, IN, V) silu_mul_kernel<T, IN, V><<<blocks, 256, 0, stream>>>(Summed<IN>{(const IN*)gate_up, splits, stride}, (T*)out, inter, total)
+#define GO(T, IN, V) silu_mul_kernel<T, IN, V><<<blocks, 256, 0, stream>>>(Summed<IN>{(const IN*)gate_up, splits, stride}, (T*)out, inter, block, total)
     if (act_dtype == kBF16 && in_dtype == kBF16) { if (vec) GO(__nv_bfloat16, __nv_bfloat16, 4); else GO(__nv_bfloat16, __nv_bfloat16, 1); }
     else if (act_dtype == kBF16) { if (vec) GO(__nv_bfloat16, float, 4); else GO(__nv_bfloat16, float, 1); }
     else { if (vec) GO(float, float, 4); else GO(float, float, 1); }

@@ -23,7 +23,8 @@ _vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_
 _SIGNATURES = {
     "lily_embed": [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
     "lily_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _sz, _vp],
-    "lily_silu_mul": [_vp, _vp, _i, _i, _i, _i, _i, _sz, _vp],
+    "lily_silu_mul": [_vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _vp],
+    "lily_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "lily_qk_norm_rope_write": [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                 _i, _i, _i, _i, _i, _sz, _vp],
     "lily_skinny_gemm": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -161,16 +162,18 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-             out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``silu(gate_up[:, :I]) * gate_up[:, I:]``; ``gate_up`` may be float32 partial sums
-    [splits, tokens, 2I], in which case ``out_dtype`` says what to write."""
+def silu_mul(gate_up: torch.Tensor, out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
+             block: Optional[int] = None) -> torch.Tensor:
+    """``silu(gate) * up`` of ``gate_up`` [tokens, 2I] = [all gate | all up], or, with ``block``,
+    alternating runs of ``block`` gate and ``block`` up columns.  ``gate_up`` may be float32 partial
+    sums [splits, tokens, 2I], in which case ``out_dtype`` says what to write."""
     _dev(gate_up, out)
     n, two_i = gate_up.shape[-2:]
     splits, stride = _summed(gate_up, n, two_i, "silu_mul")
     if out is None:
         out = torch.empty((n, two_i // 2), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
-    _call("lily_silu_mul", _p(gate_up), _p(out), n, two_i // 2, _dt(out), _dt(gate_up), splits, stride, _stream())
+    _call("lily_silu_mul", _p(gate_up), _p(out), n, two_i // 2, int(block or two_i // 2), _dt(out), _dt(gate_up), splits,
+          stride, _stream())
     return out
 
 
@@ -237,6 +240,35 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if bias is not None:
         return torch.addmm(bias.to(x.dtype), x, weight.t())
     return torch.mm(x, weight.t())
+
+
+TC_MIN_ROWS = 65          # products of more rows than this go to the tcgen05 kernel when it takes the shape
+
+
+def gemm_tc_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            silu_mul_block: bool = False) -> torch.Tensor:
+    """``x [M, K] . weight [N, K]^T`` in bfloat16 on the tcgen05 tensor cores (TMA-fed, accumulator
+    in tensor memory).  With ``silu_mul_block`` the rows of ``weight`` alternate between 128 gate
+    rows and the 128 up rows of the same outputs and the result is ``silu(gate) * up`` [M, N / 2]."""
+    _dev(x, weight, bias)
+    m, k = x.shape
+    n = weight.shape[0]
+    if not gemm_tc_takes(x, weight) or weight.shape[1] != k:
+        raise KernelError(f"gemm_tc: x {tuple(x.shape)} {x.dtype} against weight {tuple(weight.shape)} {weight.dtype}")
+    out = torch.empty((m, n // 2 if silu_mul_block else n), dtype=torch.bfloat16, device=x.device)
+    _call("lily_gemm_tc", _p(x), _p(weight), _p(out), _p(bias), m, n, k, k, out.shape[1], 1 if silu_mul_block else 0,
+          _stream())
+    return out
+
+
+def gemm_tc_status() -> int:
+    """0, or a code from the first bounded wait that gave up in a tcgen05 kernel (synchronises)."""
+    return int(library().lily_gemm_tc_status())
 
 
 def linear_split(x: torch.Tensor, weight: torch.Tensor, splits: Optional[int] = None) -> Optional[torch.Tensor]:

@@ -82,7 +82,7 @@ class _DecodeGraph:
             cu_seqlens=parts[3], prefix_lens=parts[4], seq_lens=parts[5], slots=parts[6], logit_rows=parts[7],
             block_tables=[parts[8 + i].view(b, w) for i, w in enumerate(self.widths)],
             h_new_lens=[1] * b, h_prefix_lens=[0] * b, h_slots=[0] * b, max_seq_len=runner.context_len,
-            decode_splits=splits, workspace=runner.workspace)
+            decode_splits=splits, workspace=Workspace(runner.device))   # scratch of its own: the graph holds its address
         self.fill([], [], [[] for _ in self.widths])
         self.static.copy_(self.host)
         stream = torch.cuda.Stream(device=runner.device)

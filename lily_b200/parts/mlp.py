@@ -1,7 +1,11 @@
 """Dense SwiGLU feed-forward: ``down(silu(gate(x)) * up(x))``, no bias.
 
-gate and up are one matrix ``[2 * inter, hidden]`` (gate rows first) so that one product feeds the
-SiLU*mul kernel: lily/models/llama.py:31-47, stacking llama.py:164-165.
+gate and up are one matrix ``[2 * inter, hidden]`` so that one product feeds the SiLU*mul
+(lily/models/llama.py:31-47, stacking llama.py:164-165).  In bfloat16, when the intermediate size
+is a multiple of 128, the rows alternate between 128 gate rows and the 128 up rows of the same
+outputs: a 256-row tile of the product then holds both halves of 128 outputs, and for more than a
+few tokens the tcgen05 kernel applies SiLU*mul in its epilogue, so the ``[tokens, 2 * inter]``
+intermediate never reaches memory.  Otherwise gate rows come first, then up rows.
 """
 
 from __future__ import annotations
@@ -27,6 +31,7 @@ class SwiGLU(FeedForward):
         self.spec, self.prefix, self.ctx = spec, prefix, ctx
         self.w_gate_up = None
         self.w_down = None
+        self.block = None          # rows of gate / up alternate in runs of this many (None: all gate, then all up)
 
     def tensors(self) -> Dict[str, TensorSpec]:
         h, i, p = self.spec.hidden_size, self.spec.intermediate_size, self.prefix
@@ -36,13 +41,28 @@ class SwiGLU(FeedForward):
     def load(self, get) -> None:
         p, i = self.prefix, self.spec.intermediate_size
         gate = get(f"{p}.gate_proj.weight")
-        self.w_gate_up = torch.empty((2 * i, self.spec.hidden_size), dtype=gate.dtype, device=gate.device)
-        self.w_gate_up[:i].copy_(gate)
-        del gate
-        self.w_gate_up[i:].copy_(get(f"{p}.up_proj.weight"))
+        h = self.spec.hidden_size
+        self.w_gate_up = torch.empty((2 * i, h), dtype=gate.dtype, device=gate.device)
+        fused = gate.dtype == torch.bfloat16 and i % 128 == 0 and hasattr(self.ctx.ops, "gemm_tc")
+        if fused:
+            self.block = 128
+            runs = self.w_gate_up.view(i // 128, 2, 128, h)
+            runs[:, 0].copy_(gate.view(i // 128, 128, h))
+            del gate
+            runs[:, 1].copy_(get(f"{p}.up_proj.weight").view(i // 128, 128, h))
+        else:
+            self.w_gate_up[:i].copy_(gate)
+            del gate
+            self.w_gate_up[i:].copy_(get(f"{p}.up_proj.weight"))
         self.w_down = get(f"{p}.down_proj.weight").contiguous()
 
     def forward(self, x, batch):
         ops = self.ctx.ops
         product = getattr(ops, "linear_auto", ops.linear)        # partial sums for a few tokens, else [M, N]
-        return product(ops.silu_mul(product(x, self.w_gate_up), x.dtype), self.w_down)
+        if self.block and x.shape[0] >= ops.TC_MIN_ROWS and ops.gemm_tc_takes(x, self.w_gate_up):
+            act = ops.gemm_tc(x, self.w_gate_up, silu_mul_block=True)
+        elif self.block:
+            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, block=self.block)
+        else:
+            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype)
+        return product(act, self.w_down)

@@ -39,9 +39,13 @@ def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_residual=
     return ((v * torch.rsqrt(var + eps)) * weight.float()).to(out_dtype)
 
 
-def silu_mul(gate_up, out_dtype=None, out=None):
+def silu_mul(gate_up, out_dtype=None, out=None, block=None):
     i = gate_up.shape[1] // 2
-    g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
+    if block:
+        runs = gate_up.view(gate_up.shape[0], i // block, 2, block)
+        g, u = runs[:, :, 0].reshape(-1, i).float(), runs[:, :, 1].reshape(-1, i).float()
+    else:
+        g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
     return ((g / (1 + torch.exp(-g))) * u).to(gate_up.dtype)
 
 

@@ -116,6 +116,43 @@ def test_skinny_gemm_partial_sums(m, n, k):
     assert ops().linear_split(x.float(), w.float()) is None
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 6144, 4096), (300, 1000, 136), (65, 331, 200), (1, 24, 8),
+                                   (777, 512, 4096), (129, 257, 72)])
+def test_gemm_tcgen05(m, n, k):
+    o = ops()
+    g = torch.Generator(device=DEV).manual_seed(13)
+    x = torch.randn(m, k, device=DEV, generator=g).bfloat16()
+    w = torch.randn(n, k, device=DEV, generator=g).bfloat16()
+    b = torch.randn(n, device=DEV, generator=g).bfloat16()
+    want = x.float() @ w.float().t()
+    got = o.gemm_tc(x, w)
+    assert o.gemm_tc_status() == 0
+    # exact bfloat16 products summed in float32, rounded once to bfloat16
+    torch.testing.assert_close(got.float(), want, atol=2e-2 * (k ** 0.5), rtol=1e-2)
+    assert float((got.float() - want).abs().max()) <= float(want.abs().max()) * 2 ** -7
+    torch.testing.assert_close(o.gemm_tc(x, w, b).float(), want + b.float(), atol=2e-2 * (k ** 0.5) + 0.1, rtol=1e-2)
+    assert o.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (2048, 12288, 4096), (300, 384, 136), (70, 256, 4096)])
+def test_gemm_tcgen05_silu_mul_epilogue(m, inter, k):
+    o = ops()
+    g = torch.Generator(device=DEV).manual_seed(14)
+    x = (torch.randn(m, k, device=DEV, generator=g) * 0.5).bfloat16()
+    gate = (torch.randn(inter, k, device=DEV, generator=g) * (k ** -0.5)).bfloat16()
+    up = (torch.randn(inter, k, device=DEV, generator=g) * (k ** -0.5)).bfloat16()
+    mixed = torch.stack((gate.view(inter // 128, 128, k), up.view(inter // 128, 128, k)), dim=1).reshape(2 * inter, k).contiguous()
+    gt, ut = x.float() @ gate.float().t(), x.float() @ up.float().t()
+    want = torch.nn.functional.silu(gt) * ut
+    got = o.gemm_tc(x, mixed, silu_mul_block=True)
+    assert o.gemm_tc_status() == 0 and got.shape == (m, inter)
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+    # the same interleaved product through the unfused path: library product, then SiLU*mul in runs of 128
+    two = o.linear(x, mixed)
+    torch.testing.assert_close(o.silu_mul(two, block=128).float(), want, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(o.silu_mul(two, block=128).float(), ref.silu_mul(two, block=128).float(), atol=2e-2, rtol=2e-2)
+
+
 def test_kernels_add_up_partial_sums():
     o = ops()
     g = torch.Generator(device=DEV).manual_seed(12)
