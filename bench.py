@@ -245,11 +245,14 @@ def main() -> int:
     eng = Engine(EngineConfig("<random>", dtype="bfloat16", device="cuda:0", context_length=CONTEXT,
                               max_running_requests=max_batch,
                               server_args={"page_size": 64, "random_seed": 0, "chunked_prefill_size": 8192}), runner=runner)
-    e2e_prompt = CONTEXT - (steps + warmup) - 1
+    # requests admitted first decode a few tokens while the others' prompts go in: leave them room,
+    # so that all of the batch is still decoding when the timed steps end
+    slack = 2 * a.batch
+    e2e_prompt = CONTEXT - (steps + warmup) - slack
     prompts = [ids(e2e_prompt) for _ in range(a.batch)]
     sched = eng.new_scheduler()
     for i, p in enumerate(prompts):
-        sched.add_request(f"b{i}", p, SamplingParams(max_new_tokens=steps + warmup + 1, ignore_eos=True))
+        sched.add_request(f"b{i}", p, SamplingParams(max_new_tokens=steps + warmup + slack, ignore_eos=True))
     guard = 0
     while (sched.waiting_queue or len(sched.running) < a.batch) and guard < 10000:   # prompts in; first tokens sampled
         sched.step()
@@ -258,12 +261,16 @@ def main() -> int:
         sched.step()
     torch.cuda.synchronize()
     t_start = time.perf_counter()
-    done = 0
+    done, stamps, graph_before = 0, [], runner.graph_steps
     while done < steps and sched.running:
         sched.step()
         done += 1
+        stamps.append(time.perf_counter())
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t_start) * 1e3 / max(done, 1)
+    gaps = sorted((b - a) * 1e3 for a, b in zip([t_start] + stamps[:-1], stamps))
+    print(f"e2e: {done} steps, {runner.graph_steps - graph_before} through graphs, running {len(sched.running)}, "
+          f"per-step ms min {gaps[0]:.2f} median {gaps[len(gaps) // 2]:.2f} max {gaps[-1]:.2f}", file=sys.stderr)
     sched.run_to_completion()
     meta_ints = 3 * a.batch + 4 * a.batch + 1 + a.batch + a.batch * (CONTEXT // 64)
     e2e = {"value": round(a.batch / e2e_ms * 1e3, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_ints,

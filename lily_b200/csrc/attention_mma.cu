@@ -75,6 +75,8 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
     unsigned char* v_s = k_s + STAGES * BN * D * 2;                 // [STAGES][BN][D]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
+    pdl_wait();
+    pdl_launch_dependents();
     const __nv_bfloat16* q = (const __nv_bfloat16*)a.q;
     const __nv_bfloat16* kv = (const __nv_bfloat16*)a.kv;
     const int group = a.nq / a.nkv;
@@ -356,7 +358,7 @@ static int launch(const AttnArgs& a, dim3 grid, int page_shift, cudaStream_t str
         }
         configured = true;
     }
-    kern<<<grid, THREADS, smem, stream>>>(a, page_shift);
+    launch_pdl(kern, grid, dim3(THREADS), smem, stream, a, page_shift);
     return 0;
 }
 

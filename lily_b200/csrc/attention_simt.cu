@@ -210,6 +210,8 @@ attention_simt_kernel(const AttnArgs a) {
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          T* __restrict__ out, int nq, int d, int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t base = ((size_t)blockIdx.x * nq + blockIdx.y) * splits;
     float mx = -INFINITY;
     for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
@@ -296,9 +298,9 @@ LILY_API int lily_attention_combine(const float* scratch, void* out, int request
     const float* part_ml = scratch + (size_t)requests * nq * splits * d;
     dim3 cgrid(requests, nq);
     if (dtype == kBF16)
-        attention_combine_kernel<<<cgrid, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, nq, d, splits);
+        launch_pdl(attention_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, nq, d, splits);
     else
-        attention_combine_kernel<<<cgrid, 128, 0, stream>>>(part_o, part_ml, (float*)out, nq, d, splits);
+        launch_pdl(attention_combine_kernel<float>, cgrid, dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, (float*)out, nq, d, splits);
     LILY_CHECK_LAUNCH("attention_combine");
     return 0;
 }
@@ -333,9 +335,9 @@ LILY_API int lily_attention_decode_simt(const void* q, const void* kv, void* out
     if (splits > 1) {
         dim3 cgrid(requests, nq);
         if (dtype == kBF16)
-            attention_combine_kernel<<<cgrid, 128, 0, stream>>>(a.part_o, a.part_ml, (__nv_bfloat16*)out, nq, d, splits);
+            launch_pdl(attention_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (__nv_bfloat16*)out, nq, d, splits);
         else
-            attention_combine_kernel<<<cgrid, 128, 0, stream>>>(a.part_o, a.part_ml, (float*)out, nq, d, splits);
+            launch_pdl(attention_combine_kernel<float>, cgrid, dim3(128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (float*)out, nq, d, splits);
         LILY_CHECK_LAUNCH("attention_combine");
     }
     return 0;

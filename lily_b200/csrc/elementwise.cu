@@ -12,10 +12,19 @@
 #include "common.cuh"
 
 #include <cstdarg>
+#include <cstdlib>
 
 namespace lily {
 
 static thread_local char g_error[512] = "";
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("LILY_B200_PDL");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
 void set_error(const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -86,6 +95,8 @@ struct Summed {
 template <typename T, int VEC>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int hidden, int vocab) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int n = blockIdx.x;
     int id = ids[n];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host has checked the range
@@ -109,6 +120,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const Summed<IN> d
                                    const int* __restrict__ rows, int hidden, float eps, int write_residual,
                                    int stash) {
     extern __shared__ __align__(16) float smem[];
+    pdl_wait();
+    pdl_launch_dependents();
     float* red = smem;             // 33 floats
     float* row = smem + 40;        // hidden floats when stash
     const int m = blockIdx.x;
@@ -174,6 +187,8 @@ __device__ __forceinline__ float silu_times(float g, float u) { return (g / (1.f
 // block | ...]; block == inter is the plain [all gate | all up] order.
 template <typename T, typename IN, int VEC>
 __global__ void silu_mul_kernel(const Summed<IN> gate_up, T* __restrict__ out, int inter, int block, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t step = (size_t)gridDim.x * blockDim.x * VEC;
     for (size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; idx < total; idx += step) {
         const size_t n = idx / inter;
@@ -201,6 +216,8 @@ __global__ void qk_norm_rope_write_kernel(const Summed<IN> qkv, const W* __restr
                                           const int* __restrict__ block_table, int bt_stride,
                                           T* __restrict__ kv_layer, T* __restrict__ q_out,
                                           int nq, int nkv, int d, int rd, int page_size, int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int n = blockIdx.x;
     const int head = blockIdx.y * blockDim.y + threadIdx.y;
     const int nheads = write_kv ? nq + 2 * nkv : nq;
@@ -324,11 +341,11 @@ LILY_API int lily_embed(const void* table, int table_dtype, const int* ids, floa
     LILY_REQUIRE(hidden > 0 && vocab > 0, "embed: bad sizes hidden=%d vocab=%d", hidden, vocab);
     const bool vec = hidden % 4 == 0 && aligned16(table) && aligned16(out);
     if (table_dtype == kBF16) {
-        if (vec) embed_kernel<__nv_bfloat16, 4><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
-        else embed_kernel<__nv_bfloat16, 1><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
+        if (vec) launch_pdl(embed_kernel<__nv_bfloat16, 4>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
+        else launch_pdl(embed_kernel<__nv_bfloat16, 1>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
     } else {
-        if (vec) embed_kernel<float, 4><<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
-        else embed_kernel<float, 1><<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+        if (vec) launch_pdl(embed_kernel<float, 4>, dim3(tokens), dim3(256), 0, stream, (const float*)table, ids, out, hidden, vocab);
+        else launch_pdl(embed_kernel<float, 1>, dim3(tokens), dim3(256), 0, stream, (const float*)table, ids, out, hidden, vocab);
     }
     LILY_CHECK_LAUNCH("embed");
     return 0;
@@ -347,9 +364,9 @@ static void launch_add_rmsnorm(float* resid, const void* delta, int splits, size
     const int threads = hidden >= 2048 * per ? 512 : (hidden >= 1024 * per ? 256 : 128);
     const Summed<IN> d{(const IN*)delta, splits, stride};
     if (vec)
-        add_rmsnorm_kernel<T, W, IN, 4><<<out_rows, threads, smem, stream>>>(resid, d, (const W*)weight, (T*)out, rows, hidden, eps, write_residual, stash);
+        launch_pdl(add_rmsnorm_kernel<T, W, IN, 4>, dim3(out_rows), dim3(threads), smem, stream, resid, d, (const W*)weight, (T*)out, rows, hidden, eps, write_residual, stash);
     else
-        add_rmsnorm_kernel<T, W, IN, 1><<<out_rows, threads, smem, stream>>>(resid, d, (const W*)weight, (T*)out, rows, hidden, eps, write_residual, stash);
+        launch_pdl(add_rmsnorm_kernel<T, W, IN, 1>, dim3(out_rows), dim3(threads), smem, stream, resid, d, (const W*)weight, (T*)out, rows, hidden, eps, write_residual, stash);
 }
 
 static int check_summed(const char* name, int act_dtype, int in_dtype, int splits) {
@@ -392,7 +409,7 @@ LILY_API int lily_silu_mul(const void* gate_up, void* out, int tokens, int inter
     const bool vec = block % 4 == 0 && stride % 4 == 0 && aligned16(gate_up) && aligned16(out);
     const size_t work = vec ? total / 4 : total;
     const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
-#define GO(T, IN, V) silu_mul_kernel<T, IN, V><<<blocks, 256, 0, stream>>>(Summed<IN>{(const IN*)gate_up, splits, stride}, (T*)out, inter, block, total)
+#define GO(T, IN, V) launch_pdl(silu_mul_kernel<T, IN, V>, dim3(blocks), dim3(256), 0, stream, Summed<IN>{(const IN*)gate_up, splits, stride}, (T*)out, inter, block, total)
     if (act_dtype == kBF16 && in_dtype == kBF16) { if (vec) GO(__nv_bfloat16, __nv_bfloat16, 4); else GO(__nv_bfloat16, __nv_bfloat16, 1); }
     else if (act_dtype == kBF16) { if (vec) GO(__nv_bfloat16, float, 4); else GO(__nv_bfloat16, float, 1); }
     else { if (vec) GO(float, float, 4); else GO(float, float, 1); }
@@ -418,7 +435,7 @@ LILY_API int lily_qk_norm_rope_write(const void* qkv, const void* q_gain, const 
     const bool vec = d % 2 == 0 && rot % 4 == 0 && stride % 2 == 0 && aligned16(qkv) && aligned16(kv_layer) &&
                      aligned16(q_out) && aligned16(q_gain) && aligned16(k_gain) && aligned16(cos_t) && aligned16(sin_t);
 #define LAUNCH_V(T, W, IN, V)                                                                                     \
-    qk_norm_rope_write_kernel<T, W, IN, V><<<grid, block, 0, stream>>>(Summed<IN>{(const IN*)qkv, splits, stride}, \
+    launch_pdl(qk_norm_rope_write_kernel<T, W, IN, V>, grid, block, 0, stream, Summed<IN>{(const IN*)qkv, splits, stride}, \
         (const W*)q_gain, (const W*)k_gain, eps, cos_t, sin_t, positions, token_req, block_table, bt_stride,      \
         (T*)kv_layer, (T*)q_out, nq, nkv, d, rot, page_size, write_kv)
 #define LAUNCH(T, W, IN) do { if (vec) LAUNCH_V(T, W, IN, 2); else LAUNCH_V(T, W, IN, 1); } while (0)

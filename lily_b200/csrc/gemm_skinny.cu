@@ -77,6 +77,11 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         cp_async_commit();
     }
 
+    // x comes from the kernel before this one; the weights above do not, so their stream is
+    // already running while that kernel drains
+    pdl_wait();
+    pdl_launch_dependents();
+
     // stage this slice of x: rows beyond M are zero
     const int chunks = nkb * (KB / 8);
     for (int i = tid; i < NT * 8 * chunks; i += WARPS * 32) {
@@ -167,7 +172,7 @@ static int launch(const __nv_bfloat16* x, const __nv_bfloat16* w, float* parts, 
         granted = smem;
     }
     dim3 grid((N + WARPS * 16 * MT - 1) / (WARPS * 16 * MT), ksplit);
-    kern<<<grid, WARPS * 32, smem, stream>>>(x, w, parts, M, N, K, per);
+    launch_pdl(kern, grid, dim3(WARPS * 32), smem, stream, x, w, parts, M, N, K, per);
     return 0;
 }
 

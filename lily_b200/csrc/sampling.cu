@@ -63,6 +63,8 @@ __device__ ArgBest block_argmax(const float* row, int vocab, float tdiv, ArgBest
 __global__ void __launch_bounds__(STHREADS)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
     __shared__ ArgBest scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
     const ArgBest b = block_argmax(logits + (size_t)blockIdx.x * vocab, vocab, 1.f, scratch);
     if (threadIdx.x == 0) out[blockIdx.x] = b.i < vocab ? b.i : 0;
 }
@@ -255,7 +257,7 @@ using namespace lily;
 LILY_API int lily_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
     if (rows == 0) return 0;
     LILY_REQUIRE(vocab > 0, "argmax: vocab=%d", vocab);
-    argmax_kernel<<<rows, STHREADS, 0, stream>>>(logits, out, vocab);
+    launch_pdl(argmax_kernel, dim3(rows), dim3(STHREADS), 0, stream, logits, out, vocab);
     LILY_CHECK_LAUNCH("argmax");
     return 0;
 }

@@ -112,24 +112,19 @@ def order_entries(entries: Sequence[StepEntry]) -> List[int]:
 def choose_decode_splits(num_decode: int, kv_heads: int, max_seq_len: int, sm_count: int = 148,
                          blocks_per_sm: int = 3, min_keys: int = 256, max_splits: int = 32) -> int:
     """How many ranges the keys of a decode row are cut into.  One block works on one (request, kv
-    head, range); the device holds ``sm_count * blocks_per_sm`` blocks at a time.  With fewer blocks
-    than that, cut as finely as ``min_keys`` allows; with more, pick the count whose last wave of
-    blocks is fullest (a grid of 1.15 waves takes as long as one of 2).  The reference fixes 32
-    splits with a floor of 64 keys (lily/layers/attention/triton_backend.py:21,
-    decode_attention.py:68,172)."""
+    head, range); the device holds ``sm_count * blocks_per_sm`` blocks at a time.  Measured on a
+    B200 (head size 128, 4096 keys): the fastest grid is the single wave that comes closest to
+    filling the device (batch 8: 6 to 7 ranges; batch 16: 3); when the rows alone overfill it, about
+    four waves (batch 64: 4 ranges).  The reference fixes 32 splits with a floor of 64 keys
+    (lily/layers/attention/triton_backend.py:21, decode_attention.py:68,172)."""
     if num_decode == 0:
         return 1
     limit = max(1, min(max_splits, max_seq_len // min_keys))
     pairs, held = num_decode * kv_heads, sm_count * blocks_per_sm
-    if pairs * limit <= held:
-        return limit
-    best, best_fill = 1, 0.0
-    for s in range(1, limit + 1):
-        waves = pairs * s / held
-        fill = waves / -(-pairs * s // held)          # below one wave: the share of the device in use
-        if fill > best_fill + 0.02 or (fill >= best_fill - 0.02 and s > best and fill > 0.9):
-            best, best_fill = s, max(fill, best_fill)
-    return best
+    one_wave = min(limit, held // pairs)
+    if one_wave >= 1 and (pairs * one_wave >= 0.7 * held or one_wave == limit):
+        return one_wave
+    return max(1, min(limit, -(-4 * held // pairs)))
 
 
 def build_step_batch(entries: Sequence[StepEntry], prefix_lens: Sequence[int],
