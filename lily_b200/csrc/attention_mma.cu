@@ -63,16 +63,18 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 }
 
 template <int D, bool DECODE, int STAGES>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, D <= 128 ? 3 : 1)
 attention_mma_kernel(const AttnArgs a, const int page_shift) {
     constexpr int CH = D / 8;                  // 16-byte pieces per row
     constexpr int KSTEPS = D / 16;
     constexpr int BM = DECODE ? 16 : 64;
     constexpr int NT = DECODE ? 2 : 8;         // score n-tiles (8 keys each) per warp and key tile
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    unsigned char* q_s = smem_raw;                                  // [BM][D]
-    unsigned char* k_s = q_s + BM * D * 2;                          // [STAGES][BN][D]
+    unsigned char* k_s = smem_raw;                                  // [STAGES][BN][D]
     unsigned char* v_s = k_s + STAGES * BN * D * 2;                 // [STAGES][BN][D]
+    // the queries pass through the second key stage on their way to registers: that stage is first
+    // filled after the barrier of the first loop iteration, when every warp has its fragments
+    unsigned char* q_s = k_s + BN * D * 2;                          // [BM][D], BM <= BN
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
     pdl_wait();
@@ -342,11 +344,10 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
 
 template <int D, bool DECODE, int STAGES>
 static int launch(const AttnArgs& a, dim3 grid, int page_shift, cudaStream_t stream) {
-    constexpr int BM = DECODE ? 16 : 64;
-    size_t smem = (size_t)BM * D * 2 + 2 * (size_t)STAGES * BN * D * 2;
+    size_t smem = 2 * (size_t)STAGES * BN * D * 2;
     if (DECODE) {
         const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
-        if ((size_t)BM * D * 2 + merge > smem) smem = (size_t)BM * D * 2 + merge;
+        if (merge > smem) smem = merge;
     }
     auto kern = attention_mma_kernel<D, DECODE, STAGES>;
     static bool configured = false;

@@ -20,7 +20,7 @@
 namespace lily {
 namespace skinny {
 
-constexpr int KB = 64;            // k per tile (128 bytes of a row)
+constexpr int KB = 64;            // granule of k: K must be a multiple of it, slices are counted in it
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -39,37 +39,41 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// NT: 8-token tiles (M <= 8 * NT).  MT: 16-row tiles of w per warp.  WARPS per block.
-template <int NT, int MT, int WARPS, int STAGES>
+// NT: 8-token tiles (M <= 8 * NT).  MT: 16-row tiles of w per warp.  WARPS per block.  KT: k per
+// tile (64 or 256: 128 or 512 contiguous bytes of each row per copy round).
+template <int NT, int MT, int WARPS, int STAGES, int KT>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    float* __restrict__ parts, int M, int N, int K, int blocks_per_slice) {
     constexpr int ROWS = 16 * MT;                     // weight rows per warp
-    constexpr int TILE = ROWS * KB * 2;               // bytes of one warp tile
+    constexpr int PIECES = KT / 8;                    // 16-byte pieces per row of a tile
+    constexpr int PITCH = KT * 2;                     // bytes per row of a tile
+    constexpr int TILE = ROWS * PITCH;                // bytes of one warp tile
+    constexpr int COPIES = ROWS * PIECES / 32;        // cp.async per lane and tile
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
     unsigned char* ring = smem + (size_t)warp * STAGES * TILE;        // this warp's tiles
     unsigned char* xs = smem + (size_t)WARPS * STAGES * TILE;         // [NT * 8][slice k], 16-byte pieces swizzled
-    const int kblocks = K / KB;
+    const int kblocks = K / KT;                       // tiles along k (blocks_per_slice counts tiles too)
     const int kb0 = blockIdx.y * blocks_per_slice;
     const int nkb = max(0, min(blocks_per_slice, kblocks - kb0));
     const int row0 = (blockIdx.x * WARPS + warp) * ROWS;
 
-    // this lane copies piece (lane & 7) of rows (lane >> 3) + 4 i; rows beyond N repeat the last row
-    const int piece = lane & 7;
-    const __nv_bfloat16* src[ROWS / 4];
-    uint32_t dst[ROWS / 4];
+    // copy i of this lane moves piece (32 i + lane) % PIECES of row (32 i + lane) / PIECES: a warp-wide
+    // copy covers whole rows of the tile (4 rows of 128 bytes, or one row of 512); rows beyond N repeat the last row
+    const __nv_bfloat16* src[COPIES];
+    uint32_t dst[COPIES];
 #pragma unroll
-    for (int i = 0; i < ROWS / 4; ++i) {
-        const int r = (lane >> 3) + 4 * i;
-        src[i] = w + (size_t)min(row0 + r, N - 1) * K + (size_t)kb0 * KB + piece * 8;
-        dst[i] = (uint32_t)(r * 128 + ((piece ^ (r & 7)) << 4));
+    for (int i = 0; i < COPIES; ++i) {
+        const int r = (32 * i + lane) / PIECES, piece = (32 * i + lane) % PIECES;
+        src[i] = w + (size_t)min(row0 + r, N - 1) * K + (size_t)kb0 * KT + piece * 8;
+        dst[i] = (uint32_t)(r * PITCH + (((piece & ~7) | ((piece ^ r) & 7)) << 4));
     }
     auto issue = [&](int kb) {
         const uint32_t base = smem_u32(ring + (kb % STAGES) * TILE);
 #pragma unroll
-        for (int i = 0; i < ROWS / 4; ++i) cp_async16(base + dst[i], src[i] + (size_t)kb * KB);
+        for (int i = 0; i < COPIES; ++i) cp_async16(base + dst[i], src[i] + (size_t)kb * KT);
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {            // the weight stream starts before x is staged
@@ -83,11 +87,11 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     pdl_launch_dependents();
 
     // stage this slice of x: rows beyond M are zero
-    const int chunks = nkb * (KB / 8);
+    const int chunks = nkb * PIECES;
     for (int i = tid; i < NT * 8 * chunks; i += WARPS * 32) {
         const int r = i / chunks, ch = i % chunks;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < M) v = *reinterpret_cast<const uint4*>(x + (size_t)r * K + (size_t)kb0 * KB + ch * 8);
+        if (r < M) v = *reinterpret_cast<const uint4*>(x + (size_t)r * K + (size_t)kb0 * KT + ch * 8);
         *reinterpret_cast<uint4*>(xs + ((size_t)r * chunks + (ch ^ (r & 7))) * 16) = v;
     }
     __syncthreads();
@@ -105,19 +109,19 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         cp_async_commit();
         const uint32_t tile = smem_u32(ring + (kb % STAGES) * TILE);
 #pragma unroll
-        for (int kk = 0; kk < KB / 16; ++kk) {
+        for (int kk = 0; kk < KT / 16; ++kk) {
             uint32_t a[MT][4];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 const int r = mt * 16 + (lane & 15), ch = kk * 2 + (lane >> 4);
-                ldmatrix_x4(tile + r * 128 + ((ch ^ (r & 7)) << 4), a[mt][0], a[mt][1], a[mt][2], a[mt][3]);
+                ldmatrix_x4(tile + r * PITCH + (((ch & ~7) | ((ch ^ r) & 7)) << 4), a[mt][0], a[mt][1], a[mt][2], a[mt][3]);
             }
 #pragma unroll
             for (int np = 0; np < (NT + 1) / 2; ++np) {
                 // two token tiles at once: (tokens 0-7, k lo), (0-7, k hi), (8-15, k lo), (8-15, k hi)
                 uint32_t b0, b1, b2, b3;
                 const int r = np * 16 + (lane & 7) + ((lane >> 4) << 3);
-                const int ch = kb * 8 + kk * 2 + ((lane >> 3) & 1);
+                const int ch = kb * PIECES + kk * 2 + ((lane >> 3) & 1);
                 const int rr = NT == 1 ? (lane & 7) : r;              // one tile only: both halves read tokens 0-7
                 ldmatrix_x4(smem_u32(xs + ((size_t)rr * chunks + (ch ^ (rr & 7))) * 16), b0, b1, b2, b3);
 #pragma unroll
@@ -143,25 +147,32 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 struct Shape {
-    int nt, mt, warps, stages;
+    int nt, mt, warps, stages, kt;
 };
-static Shape shape_for(int M) {
-    if (M <= 8) return {1, 1, 8, 5};
-    if (M <= 16) return {2, 1, 8, 5};
-    if (M <= 32) return {4, 2, 4, 5};
-    return {8, 2, 4, 5};
+// Tiles of 256 k (512 contiguous bytes of a row per copy round) measured no faster than tiles of
+// 64 k with these ring sizes and cost shared memory that x's slice needs; they stay switched off.
+static Shape shape_for(int M, int K, int N = 0) {
+    // a wide product whose 256-row blocks fit the SMs in one wave runs one big block per SM, whole k
+    // (measured on 8 x 24576 x 4096: 41.9 us against the library's 35.6 us, so it stays switched off)
+    if (false && M <= 8 && N > 148 * 128 && N <= 148 * 256 && (size_t)8 * 5 * 32 * KB * 2 + (size_t)8 * K * 2 <= 224 * 1024)
+        return Shape{1, 2, 8, 5, 64};
+    const bool wide = false && K % 256 == 0;
+    if (M <= 8) return wide ? Shape{1, 1, 4, 3, 256} : Shape{1, 1, 8, 5, 64};
+    if (M <= 16) return wide ? Shape{2, 1, 4, 3, 256} : Shape{2, 1, 8, 5, 64};
+    if (M <= 32) return {4, 2, 4, 5, 64};
+    return {8, 2, 4, 5, 64};
 }
-static size_t smem_bytes(const Shape& s, int per) {
-    return (size_t)s.warps * s.stages * 16 * s.mt * KB * 2 + (size_t)s.nt * 8 * per * KB * 2;
+static size_t smem_bytes(const Shape& s, int tiles_per_slice) {
+    return (size_t)s.warps * s.stages * 16 * s.mt * s.kt * 2 + (size_t)s.nt * 8 * tiles_per_slice * s.kt * 2;
 }
 
-template <int NT, int MT, int WARPS, int STAGES>
+template <int NT, int MT, int WARPS, int STAGES, int KT>
 static int launch(const __nv_bfloat16* x, const __nv_bfloat16* w, float* parts, int M, int N, int K, int ksplit,
                   cudaStream_t stream) {
-    const int kblocks = K / KB;
-    const int per = (kblocks + ksplit - 1) / ksplit;
-    const size_t smem = smem_bytes(Shape{NT, MT, WARPS, STAGES}, per);
-    auto kern = skinny_gemm_kernel<NT, MT, WARPS, STAGES>;
+    const int tiles = K / KT;
+    const int per = (tiles + ksplit - 1) / ksplit;
+    const size_t smem = smem_bytes(Shape{NT, MT, WARPS, STAGES, KT}, per);
+    auto kern = skinny_gemm_kernel<NT, MT, WARPS, STAGES, KT>;
     static size_t granted = 48 * 1024;
     if (smem > granted) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -190,16 +201,17 @@ LILY_API int lily_skinny_gemm_max_rows() { return 64; }
 // products, which the library streams well without cutting k, and more than 16 tokens to it.
 LILY_API int lily_skinny_gemm_splits(int M, int N, int K) {
     if (K % skinny::KB != 0 || M < 1 || M > 16 || K < skinny::KB) return 0;
-    const skinny::Shape sh = skinny::shape_for(M);
+    const skinny::Shape sh = skinny::shape_for(M, K, N);
     const int rows_per_block = sh.warps * 16 * sh.mt;
     const int row_blocks = (N + rows_per_block - 1) / rows_per_block;
-    const int kblocks = K / skinny::KB;
+    const int tiles = K / sh.kt;
     const int held = 148 * 2;
+    if (sh.mt == 2 && M <= 8) return 1;                  // the one-block-per-SM shape: no split
     if (row_blocks > held / 2) return 0;
     int s = held / row_blocks;
-    const int longest = kblocks / 8 > 0 ? kblocks / 8 : 1;
+    const int longest = tiles * sh.kt / 512 > 0 ? tiles * sh.kt / 512 : 1;      // slices of at least 512 k
     s = s < 1 ? 1 : (s > longest ? longest : s);
-    while (s < kblocks && skinny::smem_bytes(sh, (kblocks + s - 1) / s) > 112 * 1024) ++s;
+    while (s < tiles && skinny::smem_bytes(sh, (tiles + s - 1) / s) > 112 * 1024) ++s;
     return row_blocks * s <= held ? s : 0;
 }
 
@@ -208,15 +220,19 @@ LILY_API int lily_skinny_gemm(const void* x, const void* w, float* parts, int M,
     if (M == 0 || N == 0) return 0;
     LILY_REQUIRE(M >= 1 && M <= 64, "skinny_gemm: %d tokens (takes 1..64)", M);
     LILY_REQUIRE(K > 0 && K % skinny::KB == 0, "skinny_gemm: K=%d is not a multiple of %d", K, skinny::KB);
-    LILY_REQUIRE(ksplit >= 1 && ksplit <= K / skinny::KB, "skinny_gemm: %d slices of K=%d", ksplit, K);
+    const skinny::Shape sh = skinny::shape_for(M, K, N);
+    LILY_REQUIRE(ksplit >= 1 && ksplit <= K / sh.kt, "skinny_gemm: %d slices of K=%d", ksplit, K);
     LILY_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "skinny_gemm: operands must be 16-byte aligned");
     const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
     int rc;
-    if (M <= 8) rc = skinny::launch<1, 1, 8, 5>(xp, wp, parts, M, N, K, ksplit, stream);
-    else if (M <= 16) rc = skinny::launch<2, 1, 8, 5>(xp, wp, parts, M, N, K, ksplit, stream);
-    else if (M <= 32) rc = skinny::launch<4, 2, 4, 5>(xp, wp, parts, M, N, K, ksplit, stream);
-    else rc = skinny::launch<8, 2, 4, 5>(xp, wp, parts, M, N, K, ksplit, stream);
+    if (M <= 8 && sh.mt == 2) rc = skinny::launch<1, 2, 8, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
+    else if (M <= 8) rc = sh.kt == 256 ? skinny::launch<1, 1, 4, 3, 256>(xp, wp, parts, M, N, K, ksplit, stream)
+                                  : skinny::launch<1, 1, 8, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
+    else if (M <= 16) rc = sh.kt == 256 ? skinny::launch<2, 1, 4, 3, 256>(xp, wp, parts, M, N, K, ksplit, stream)
+                                        : skinny::launch<2, 1, 8, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
+    else if (M <= 32) rc = skinny::launch<4, 2, 4, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
+    else rc = skinny::launch<8, 2, 4, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
     if (rc) return rc;
     LILY_CHECK_LAUNCH("skinny_gemm");
     return 0;

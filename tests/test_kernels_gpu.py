@@ -99,7 +99,7 @@ def test_skinny_gemm_partial_sums(m, n, k):
     g = torch.Generator(device=DEV).manual_seed(11)
     x = torch.randn(m, k, device=DEV, generator=g).bfloat16()
     w = torch.randn(n, k, device=DEV, generator=g).bfloat16()
-    parts = ops().linear_split(x, w, splits=max(1, min(5, k // 128)))
+    parts = ops().linear_split(x, w, splits=max(1, min(5, k // 512)))
     assert parts is not None and parts.dtype == torch.float32 and parts.shape[1:] == (m, n)
     auto = ops().linear_split(x, w)                     # the kernel's own rule may leave the shape to the library
     if auto is not None:
