@@ -41,6 +41,30 @@ def setup(request):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_head_size_128_paths_inside_the_engine(dtype):
+    """Head size 128, widths in multiples of 128, page size 64: tensor-core attention (prefill and
+    split-key decode through graphs), the tcgen05 gate/up kernel and the weight-streaming decode
+    product, all through the step function, against the plain implementation."""
+    cfg = tiny_models.MID_QWEN3
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 33, tmp)
+        v = cfg["vocab_size"]
+        ids = tiny_models.random_tokens(700, v, 4)
+        want = plain_impl.all_logits(cfg, rounded(weights, dtype), ids)
+        runner = make_runner(path, dtype=dtype, device="cuda", page_size=64, max_tokens=2048 + 512)
+        close(run_whole(runner, ids), want, dtype, "whole")
+        close(run_portions(runner, ids, [668] + [1] * 32), want, dtype, "last 32 one by one")
+        close(run_portions(runner, ids, [130, 2, 300, 65, 3, 129]), want, dtype, "portions")
+        reqs = {k: tiny_models.random_tokens(n, v, 50 + i) for i, (k, n) in enumerate({"a": 400, "b": 330, "c": 200, "d": 90}.items())}
+        plan = [{"a": 300, "b": 70}, {"a": 1, "b": 200, "c": 2}, {"a": 1, "b": 1, "c": 198, "d": 66}] + [{k: 1 for k in "abd"}] * 24
+        got = run_mixed(runner, reqs, plan)
+        for name, toks in reqs.items():
+            full = plain_impl.all_logits(cfg, rounded(weights, dtype), toks)
+            close(got[name], full[:got[name].shape[0]], dtype, name)
+        assert runner.graph_steps > 0 and runner.cache.held_pages() == [0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_whole_decode_and_portions(setup, dtype):
     cfg, weights, path = setup
     ids = tiny_models.random_tokens(150, cfg["vocab_size"], 3)

@@ -279,6 +279,46 @@ def test_attention_decode(dtype, splits, nq, nkv, d, page, window):
     torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page", [(4, 2, 16, 16), (8, 2, 128, 64), (6, 2, 48, 8)])
+def test_attention_window_edge_and_page_edge(dtype, nq, nkv, d, page):
+    """A key that dominates every score, placed first just inside and then just outside the window
+    of the last query (and on the last slot of a page): inside it owns the output, outside it must
+    not be seen at all.  Prefill and decode kernels, same cache."""
+    o = ops()
+    window, seq = 2 * page + 3, 5 * page + 2
+    g = torch.Generator(device=DEV).manual_seed(15)
+    width = -(-seq // page)
+    table = (torch.randperm(width, device=DEV, generator=g) + 1).view(1, width).to(torch.int32)
+    q = torch.randn(1, nq * d, device=DEV, generator=g).to(dtype)
+    qpos = seq - 1
+    for key_pos, inside in ((qpos - window + 1, True), (qpos - window, False), (3 * page - 1, True)):
+        cache = (torch.randn(width + 1, 2, nkv, page, d, device=DEV, generator=g) * 0.1).to(dtype)
+        pg, off = int(table[0, key_pos // page]), key_pos % page
+        for h in range(nkv):
+            cache[pg, 0, h, off] = (q.view(nq, d)[h * (nq // nkv)].float() * 8).to(dtype)
+            cache[pg, 1, h, off] = 7.0
+        for decode in (True, False):
+            got, want = torch.zeros_like(q), torch.zeros_like(q)
+            seq_t = torch.tensor([seq], device=DEV, dtype=torch.int32)
+            if decode:
+                scratch = torch.empty(max(1, o.decode_scratch_floats(1, nq, d, 2)), device=DEV)
+                o.attention_decode(q, cache, table, seq_t, got, scratch, 2, nq, nkv, d, page, d ** -0.5, window)
+                ref.attention_decode(q, cache, table, seq_t, want, None, 2, nq, nkv, d, page, d ** -0.5, window)
+            else:
+                cu = torch.tensor([0, 1], device=DEV, dtype=torch.int32)
+                pre = torch.tensor([seq - 1], device=DEV, dtype=torch.int32)
+                z = torch.zeros(1, device=DEV, dtype=torch.int32)
+                o.attention_prefill(q, cache, table, cu, pre, z, z, got, nq, nkv, d, page, d ** -0.5, window)
+                ref.attention_prefill(q, cache, table, cu, pre, z, z, want, nq, nkv, d, page, d ** -0.5, window)
+            torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+            first_head = got.view(nq, d)[0].float()
+            if inside:
+                assert float((first_head - 7.0).abs().max()) < 0.5, (key_pos, decode)
+            else:
+                assert float(first_head.abs().max()) < 1.0, (key_pos, decode)
+
+
 def test_attention_refuses_what_it_cannot_do():
     o = ops()
     q = torch.zeros(1, 2 * 272, device=DEV)

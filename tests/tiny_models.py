@@ -93,6 +93,26 @@ ODD_LLAMA = {
     "torch_dtype": "float32",
 }
 
+# Head size 128 and widths in multiples of 128, small enough for the CPU: the sizes at which the
+# tensor-core attention, the tcgen05 gate/up kernel and the weight-streaming decode product run
+# inside the engine (the tiny configurations above mostly take the CUDA-core kernels).
+MID_QWEN3 = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "model_type": "qwen3",
+    "num_hidden_layers": 2,
+    "hidden_size": 512,
+    "num_attention_heads": 8,
+    "num_key_value_heads": 2,
+    "head_dim": 128,
+    "intermediate_size": 1408,
+    "vocab_size": 2000,
+    "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 1024,
+    "torch_dtype": "float32",
+}
+
 CONFIGS = {"tiny_qwen3": TINY_QWEN3, "tiny_llama": TINY_LLAMA, "odd_qwen3": ODD_QWEN3, "odd_llama": ODD_LLAMA}
 
 
