@@ -11,8 +11,12 @@
 // lily/mem_cache/memory_pool.py:137-143, embedding lily/layers/vocab_embedding.py:37-39.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 #include <cstdarg>
 #include <cstdlib>
+
+namespace cg = cooperative_groups;
 
 namespace lily {
 
@@ -177,6 +181,40 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const Summed<IN> d
             dst[i] = from_float<T>((v * inv) * to_float(weight[i]));
         }
     }
+}
+
+// The same for a few rows (decode): a thread-block cluster of CL blocks shares one row, each block
+// takes hidden / CL columns (four per thread) and the blocks exchange their sums of squares
+// through distributed shared memory, so that 8 rows keep 64 SMs busy instead of 8.
+// grid (CL, rows), cluster (CL, 1, 1); hidden % (4 * CL) == 0; block = hidden / (4 * CL) threads.
+template <typename T, typename W, typename IN, int CL>
+__global__ void add_rmsnorm_cluster_kernel(float* __restrict__ resid, const Summed<IN> delta,
+                                           const W* __restrict__ weight, T* __restrict__ out,
+                                           const int* __restrict__ rows, int hidden, float eps, int write_residual) {
+    __shared__ float red[40];
+    __shared__ float share[1];
+    cg::cluster_group cluster = cg::this_cluster();
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.y;
+    const size_t src = (size_t)(rows ? rows[m] : m) * hidden;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;       // this thread's four columns
+    float4 v = load4(resid, src + i);
+    if (delta) {
+        const float4 dl = delta.four(src + i);
+        v.x += dl.x; v.y += dl.y; v.z += dl.z; v.w += dl.w;
+        if (write_residual) store4(resid, src + i, v);
+    }
+    const float mine = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
+    if (threadIdx.x == 0) share[0] = mine;
+    cluster.sync();
+    float total = 0.f;
+#pragma unroll
+    for (int r = 0; r < CL; ++r) total += *cluster.map_shared_rank(&share[0], r);    // same order in every block
+    cluster.sync();                                                  // nobody leaves while its sum may still be read
+    const float inv = rsqrtf(total / (float)hidden + eps);
+    const float4 g = load4(weight, i);
+    store4(out + (size_t)m * hidden, i, make_float4((v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w));
 }
 
 // ---------------------------------------------------------------------------- SiLU * mul
@@ -363,6 +401,25 @@ static void launch_add_rmsnorm(float* resid, const void* delta, int splits, size
     const int per = vec ? 4 : 1;
     const int threads = hidden >= 2048 * per ? 512 : (hidden >= 1024 * per ? 256 : 128);
     const Summed<IN> d{(const IN*)delta, splits, stride};
+    constexpr int CL = 8;
+    if (vec && out_rows <= 64 && hidden % (4 * CL) == 0 && hidden / (4 * CL) >= 32 && hidden / (4 * CL) <= 1024) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(CL, out_rows);
+        cfg.blockDim = dim3(hidden / (4 * CL));
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = CL;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
+        cudaLaunchKernelEx(&cfg, add_rmsnorm_cluster_kernel<T, W, IN, CL>, resid, d, (const W*)weight, (T*)out, rows, hidden, eps,
+                           write_residual);
+        return;
+    }
     if (vec)
         launch_pdl(add_rmsnorm_kernel<T, W, IN, 4>, dim3(out_rows), dim3(threads), smem, stream, resid, d, (const W*)weight, (T*)out, rows, hidden, eps, write_residual, stash);
     else

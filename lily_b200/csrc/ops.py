@@ -35,7 +35,7 @@ _SIGNATURES = {
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
-    "lily_argmax": [_vp, _vp, _i, _i, _vp],
+    "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_sample": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
 }
@@ -57,6 +57,8 @@ def library():
             fn.argtypes = args
             fn.restype = _i
         lib.lily_attention_prefill_simt_rows.restype = _i
+        lib.lily_argmax_chunks.argtypes = [_i, _i]
+        lib.lily_argmax_chunks.restype = _i
         lib.lily_skinny_gemm_max_rows.restype = _i
         lib.lily_skinny_gemm_splits.argtypes = [_i, _i, _i]
         lib.lily_skinny_gemm_splits.restype = _i
@@ -376,7 +378,13 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     rows, vocab = logits.shape
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    _call("lily_argmax", _p(logits), _i32(out, "out"), rows, vocab, _stream())
+    chunks = int(library().lily_argmax_chunks(rows, vocab))
+    pv = pi = None
+    if chunks > 1:          # a large vocabulary: many blocks per row, then a merge
+        pv = torch.empty((rows * chunks,), dtype=torch.float32, device=logits.device)
+        pi = torch.empty((rows * chunks,), dtype=torch.int32, device=logits.device)
+        launches["count"] += 1
+    _call("lily_argmax", _p(logits), _i32(out, "out"), _p(pv), _p(pi), rows, vocab, _stream())
     return out
 
 

@@ -69,6 +69,57 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
     if (threadIdx.x == 0) out[blockIdx.x] = b.i < vocab ? b.i : 0;
 }
 
+// Large vocabularies: a row is cut into `chunks` ranges, one block each, whose best (value, index)
+// go to `partial`; argmax_merge_kernel then picks the best of a row (ties go to the lower index).
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ partial_v, int* __restrict__ partial_i,
+                      int vocab, int chunks) {
+    __shared__ ArgBest scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row = blockIdx.x, c = blockIdx.y;
+    const int per = (vocab + chunks - 1) / chunks;
+    const int lo = c * per, hi = min(vocab, lo + per);
+    const float* src = logits + (size_t)row * vocab;
+    ArgBest best{-INFINITY, 0x7fffffff};
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) best = better(best, ArgBest{src[i], i});
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) scratch[warp] = best;
+    __syncthreads();
+    if (warp == 0) {
+        ArgBest t = lane < (int)(blockDim.x >> 5) ? scratch[lane] : ArgBest{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgBest other{__shfl_xor_sync(0xffffffffu, t.v, o), __shfl_xor_sync(0xffffffffu, t.i, o)};
+            t = better(t, other);
+        }
+        if (lane == 0) {
+            partial_v[row * chunks + c] = t.v;
+            partial_i[row * chunks + c] = t.i;
+        }
+    }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ partial_v, const int* __restrict__ partial_i,
+                                    int* __restrict__ out, int vocab, int chunks) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row = blockIdx.x, lane = threadIdx.x;
+    ArgBest best{-INFINITY, 0x7fffffff};
+    for (int c = lane; c < chunks; c += 32) best = better(best, ArgBest{partial_v[row * chunks + c], partial_i[row * chunks + c]});
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    if (lane == 0) out[row] = best.i < vocab ? best.i : 0;
+}
+
 // One entry per (row, token) that some request has seen or biases.
 __global__ void penalties_kernel(float* __restrict__ logits, const int* __restrict__ entry_row,
                                  const int* __restrict__ entry_token, const int* __restrict__ entry_count,
@@ -254,10 +305,27 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 
 using namespace lily;
 
-LILY_API int lily_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+// Ranges a row is cut into (1: the single-block kernel); the caller provides scratch of
+// rows * chunks floats and as many ints when it is more than 1.
+LILY_API int lily_argmax_chunks(int rows, int vocab) {
+    if (vocab < 16384) return 1;
+    int chunks = (148 * 4 + rows - 1) / (rows > 0 ? rows : 1);
+    const int most = vocab / 2048;
+    chunks = chunks > most ? most : chunks;
+    return chunks < 1 ? 1 : (chunks > 256 ? 256 : chunks);
+}
+
+LILY_API int lily_argmax(const float* logits, int* out, float* partial_v, int* partial_i, int rows, int vocab,
+                         cudaStream_t stream) {
     if (rows == 0) return 0;
     LILY_REQUIRE(vocab > 0, "argmax: vocab=%d", vocab);
-    launch_pdl(argmax_kernel, dim3(rows), dim3(STHREADS), 0, stream, logits, out, vocab);
+    const int chunks = lily_argmax_chunks(rows, vocab);
+    if (chunks <= 1 || partial_v == nullptr || partial_i == nullptr) {
+        launch_pdl(argmax_kernel, dim3(rows), dim3(STHREADS), 0, stream, logits, out, vocab);
+    } else {
+        launch_pdl(argmax_partial_kernel, dim3(rows, chunks), dim3(256), 0, stream, logits, partial_v, partial_i, vocab, chunks);
+        launch_pdl(argmax_merge_kernel, dim3(rows), dim3(32), 0, stream, (const float*)partial_v, (const int*)partial_i, out, vocab, chunks);
+    }
     LILY_CHECK_LAUNCH("argmax");
     return 0;
 }
