@@ -37,6 +37,10 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
 
+# extra compiler flags for experiments (e.g. -DLILY_DECODE_STAGES=3); they enter the binaries' names
+NVCC_FLAGS += os.environ.get("LILY_B200_NVCC_FLAGS", "").split()
+
+
 class BuildError(RuntimeError):
     pass
 

@@ -357,6 +357,102 @@ __global__ void qk_norm_rope_write_kernel(const Summed<IN> qkv, const W* __restr
     }
 }
 
+// The same work for bfloat16 in and out with 16-byte accesses, for many tokens: G = head_dim / 16
+// threads share a head (G a power of two, at most 32), each holding eight features of the first
+// half and the matching eight of the second, so the rotation needs no exchange and the norm's
+// sum of squares takes log2(G) shuffles.  The whole head is rotated (rotary width == head_dim).
+// grid (tokens, ceil(heads / (128 / G))), block 128.
+template <typename W>
+__global__ void qk_norm_rope_write_wide_kernel(const __nv_bfloat16* __restrict__ qkv, const W* __restrict__ q_gain,
+                                               const W* __restrict__ k_gain, float eps,
+                                               const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                               const int* __restrict__ positions, const int* __restrict__ token_req,
+                                               const int* __restrict__ block_table, int bt_stride,
+                                               __nv_bfloat16* __restrict__ kv_layer, __nv_bfloat16* __restrict__ q_out,
+                                               int nq, int nkv, int d, int group, int page_size, int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int n = blockIdx.x;
+    const int per_block = blockDim.x / group;
+    const int head = blockIdx.y * per_block + threadIdx.x / group;
+    const int j = threadIdx.x % group;
+    const int nheads = write_kv ? nq + 2 * nkv : nq;
+    const bool valid = head < nheads;
+    const int half = d >> 1;
+    const int pos = positions[n];
+    __nv_bfloat16* dst = nullptr;
+    const W* gain = nullptr;
+    bool rotate = true;
+    float a[8], b[8];
+    uint4 ra = make_uint4(0, 0, 0, 0), rb = ra;
+    if (valid) {
+        const __nv_bfloat16* src = qkv + ((size_t)n * (nq + 2 * nkv) + head) * d;
+        ra = *reinterpret_cast<const uint4*>(src + 8 * j);
+        rb = *reinterpret_cast<const uint4*>(src + half + 8 * j);
+        if (head < nq) {
+            dst = q_out + ((size_t)n * nq + head) * d;
+            gain = q_gain;
+        } else {
+            const int is_v = head >= nq + nkv;
+            const int kvh = head - nq - (is_v ? nkv : 0);
+            const int page = block_table[(size_t)token_req[n] * bt_stride + pos / page_size];
+            dst = kv_layer + ((((size_t)page * 2 + is_v) * nkv + kvh) * page_size + (pos % page_size)) * d;
+            gain = is_v ? nullptr : k_gain;
+            rotate = !is_v;
+        }
+    }
+    if (valid && !rotate) {
+        *reinterpret_cast<uint4*>(dst + 8 * j) = ra;
+        *reinterpret_cast<uint4*>(dst + half + 8 * j) = rb;
+    }
+    {
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&rb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
+            a[2 * i] = fa.x; a[2 * i + 1] = fa.y;
+            b[2 * i] = fb.x; b[2 * i + 1] = fb.y;
+        }
+    }
+    float ssq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ssq += a[i] * a[i] + b[i] * b[i];
+    for (int o = group >> 1; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+    if (!valid || !rotate) return;
+    if (gain) {
+        const float inv = rsqrtf(ssq / (float)d + eps);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            a[i] = (a[i] * inv) * to_float(gain[8 * j + i]);
+            b[i] = (b[i] * inv) * to_float(gain[half + 8 * j + i]);
+        }
+    }
+    if (cos_t) {
+        const float4* c4 = reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + 8 * j);
+        const float4* s4 = reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + 8 * j);
+        const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float x1 = a[i], x2 = b[i];
+            a[i] = x1 * c[i] - x2 * s[i];
+            b[i] = x2 * c[i] + x1 * s[i];
+        }
+    }
+    uint4 oa, ob;
+    __nv_bfloat162* qa = reinterpret_cast<__nv_bfloat162*>(&oa);
+    __nv_bfloat162* qb = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        qa[i] = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+        qb[i] = __floats2bfloat162_rn(b[2 * i], b[2 * i + 1]);
+    }
+    *reinterpret_cast<uint4*>(dst + 8 * j) = oa;
+    *reinterpret_cast<uint4*>(dst + half + 8 * j) = ob;
+}
+
 // ---------------------------------------------------------------------------- casts
 
 template <typename A, typename B>
@@ -497,6 +593,23 @@ LILY_API int lily_qk_norm_rope_write(const void* qkv, const void* q_gain, const 
         (T*)kv_layer, (T*)q_out, nq, nkv, d, rot, page_size, write_kv)
 #define LAUNCH(T, W, IN) do { if (vec) LAUNCH_V(T, W, IN, 2); else LAUNCH_V(T, W, IN, 1); } while (0)
     const bool gb = gain_dtype == kBF16, ib = in_dtype == kBF16;
+    const int group = d / 16;
+    if (act_dtype == kBF16 && ib && splits == 1 && d % 16 == 0 && group <= 32 && (group & (group - 1)) == 0 &&
+        (rot == d || rot == 0) && aligned16(qkv) && aligned16(kv_layer) && aligned16(q_out) && aligned16(q_gain) &&
+        aligned16(k_gain) && aligned16(cos_t) && aligned16(sin_t)) {
+        const int per_block = 128 / group;
+        dim3 wgrid(tokens, (nheads + per_block - 1) / per_block);
+        if (gb)
+            launch_pdl(qk_norm_rope_write_wide_kernel<__nv_bfloat16>, wgrid, dim3(128), 0, stream, (const __nv_bfloat16*)qkv,
+                       (const __nv_bfloat16*)q_gain, (const __nv_bfloat16*)k_gain, eps, cos_t, sin_t, positions, token_req,
+                       block_table, bt_stride, (__nv_bfloat16*)kv_layer, (__nv_bfloat16*)q_out, nq, nkv, d, group, page_size, write_kv);
+        else
+            launch_pdl(qk_norm_rope_write_wide_kernel<float>, wgrid, dim3(128), 0, stream, (const __nv_bfloat16*)qkv,
+                       (const float*)q_gain, (const float*)k_gain, eps, cos_t, sin_t, positions, token_req,
+                       block_table, bt_stride, (__nv_bfloat16*)kv_layer, (__nv_bfloat16*)q_out, nq, nkv, d, group, page_size, write_kv);
+        LILY_CHECK_LAUNCH("qk_norm_rope_write");
+        return 0;
+    }
     if (act_dtype == kBF16) {
         if (gb && ib) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
         else if (gb) LAUNCH(__nv_bfloat16, __nv_bfloat16, float);

@@ -188,7 +188,8 @@ def _cache(pages, nkv, page_size, d, dtype, g):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,rd,norm", [(4, 2, 16, 16, True), (8, 2, 32, 32, False), (6, 2, 48, 24, True),
-                                               (5, 1, 80, 80, False), (32, 8, 128, 128, True), (3, 3, 256, 64, True)])
+                                               (5, 1, 80, 80, False), (32, 8, 128, 128, True), (3, 3, 256, 64, True),
+                                               (7, 7, 64, 64, True), (2, 1, 256, 256, True), (9, 3, 128, 128, False)])
 def test_qk_norm_rope_write(dtype, nq, nkv, d, rd, norm):
     g = torch.Generator(device=DEV).manual_seed(5)
     page, n, reqs = 16, 50, 3
