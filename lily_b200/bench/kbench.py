@@ -100,6 +100,7 @@ def main() -> int:
     ap.add_argument("--reps", type=int, default=50)
     ap.add_argument("--copies", type=int, default=4)
     ap.add_argument("--no-graph", action="store_true", help="launch from the host each time instead of replaying a graph")
+    ap.add_argument("--rows64", action="store_true", help="attention_prefill: the mma.sync kernel (tiles of 64 rows) where the tcgen05 kernel would run")
     a = ap.parse_args()
 
     from lily_b200.csrc import ops
@@ -131,7 +132,7 @@ def main() -> int:
             else:
                 q = torch.randn(a.tokens, a.nq * a.d, device=dev, generator=g).to(dt)
                 out = torch.empty_like(q)
-                rows = ops.prefill_tile_rows(dt, a.d)
+                rows = ops.prefill_tile_rows(dt, a.d) if a.rows64 else ops.prefill_tile_rows(dt, a.d, a.page, a.tokens)
                 starts = list(range(0, a.tokens, rows))
                 treq = torch.zeros(len(starts), device=dev, dtype=torch.int32)
                 tstart = torch.tensor(starts, device=dev, dtype=torch.int32)
@@ -139,7 +140,7 @@ def main() -> int:
                 pre = torch.tensor([a.prefix], device=dev, dtype=torch.int32)
                 fns.append(lambda q=q, cache=cache, table=table, out=out, treq=treq, tstart=tstart, cu=cu, pre=pre:
                            ops.attention_prefill(q, cache, table, cu, pre, treq, tstart, out, a.nq, a.nkv, a.d, a.page,
-                                                 a.d ** -0.5))
+                                                 a.d ** -0.5, tile_rows=rows))
         if decode:
             bytes_moved = reqs * a.ctx * 2 * a.nkv * a.d * item + 2 * reqs * a.nq * a.d * item
             flops = 4.0 * reqs * a.nq * a.d * a.ctx
@@ -148,7 +149,7 @@ def main() -> int:
             pairs = a.tokens * a.prefix + a.tokens * (a.tokens + 1) / 2
             flops = 4.0 * a.nq * a.d * pairs
             bytes_moved = (a.prefix + a.tokens) * 2 * a.nkv * a.d * item + 2 * a.tokens * a.nq * a.d * item
-            extra = {}
+            extra = {"tile_rows": rows}
     elif a.kernel == "add_rmsnorm":
         for _ in range(a.copies):
             r = torch.randn(a.tokens, a.hidden, device=dev, generator=g)

@@ -1,0 +1,500 @@
+// Causal paged attention for prefill on the fifth-generation tensor cores (bfloat16, head size 128):
+// both products of a tile, S = Q K^T and O += P V, are tcgen05.mma instructions with their
+// accumulators in tensor memory, the operands arrive by TMA, and the softmax runs one thread per
+// query row straight out of tensor memory.  (The reference runs prefill attention through a
+// library: lily/layers/attention/flashinfer_backend.py:188-203.)
+//
+// One block works on 128 new tokens of one request and one query head, walking the keys in tiles
+// of 128 from the first the window allows to the last the causal rule allows.  Its six warps:
+//   warp 0   one thread issues the TMA loads: Q once (two [128 x 64] boxes, 128-byte swizzle), then
+//            for each tile K and V as [64 keys x 64 features] boxes taken from the request's pages
+//            (a box never crosses a page: the page size is a multiple of 64), into two stages each;
+//   warp 1   allocates tensor memory (S twice, 128 columns each, and O, 128 columns); one thread
+//            issues S_{j+1} = Q K_{j+1}^T (eight 128 x 128 x 16 products, both operands k-major)
+//            before it waits for P_j, then O += P_j V_j (V is read as it lies in the cache,
+//            [key][feature], which is the MN-major form of the B operand), so that the tensor cores
+//            work on the next scores while the softmax of the current ones runs;
+//   warps 2-5  one thread per query row: reads its row of S from tensor memory (tcgen05.ld), masks
+//            the tiles on the diagonal and at the window's edge, keeps the running maximum and sum
+//            in float32, writes P = exp2(s * scale - max) as bfloat16 into shared memory in the
+//            swizzled k-major layout that the second product reads, and at the end divides O by the
+//            sum and stores it.
+// The maximum that P is taken against only moves when the true maximum has grown by more than 2^8
+// since (then O and the sum are rescaled by the thread that owns the row, in tensor memory), so
+// the usual tile costs no pass over O; the result is the same quotient of sums either way.
+//
+// Keys past the request's length and rows past its new tokens are computed on whatever the pages
+// hold (the cache is finite everywhere: it starts as zeros) and masked: P is exactly 0 for the
+// former and the latter are not stored.  Every wait on an mbarrier is bounded; a wait that runs out
+// sets a status word (lily_attention_tc_status), the roles leave their loops and the block frees
+// its tensor memory.
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+
+namespace lily {
+namespace fa {
+
+constexpr int BQ = 128;                   // query rows per block
+constexpr int BKV = 128;                  // keys per tile
+constexpr int D = 128;                    // head size
+constexpr int STAGES = 2;                 // K stages, V stages, P buffers, S accumulators
+constexpr int SUB = 128 * 64 * 2;         // a [128 rows][64 elements] sub-tile with 128-byte rows: 16 KB
+constexpr int TILE = 2 * SUB;             // Q, one K stage, one V stage, one P buffer: 32 KB
+constexpr int BOX = 64 * 64 * 2;          // one TMA box of K or V: 8 KB
+constexpr int THREADS = 192;
+constexpr int SMEM = (1 + 3 * STAGES) * TILE + 1024;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+constexpr float GROW_LOG2 = 8.f;          // the reference maximum moves when the true one is 2^8 ahead
+
+__device__ int g_status = 0;              // 0 ok; else (code << 24 | block) of the first wait that gave up
+
+struct Params {
+    const int* block_table;
+    const int* cu_seqlens;
+    const int* prefix_lens;
+    const int* tile_req;
+    const int* tile_start;
+    __nv_bfloat16* out;
+    int bt_stride, tiles, nq, nkv, page_size, window;
+    float scale_log2;                     // softmax scale times log2(e)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_status, 0, (code << 24) | (int)((blockIdx.x + blockIdx.y * gridDim.x) & 0xFFFFFF));
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z, int w) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+// k-major operand tile with 128-byte swizzle: rows of 128 bytes, groups of eight rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// MN-major operand ([k][n] with n contiguous) with 128-byte swizzle: a row of 64 n per k, groups of
+// eight k 1024 bytes apart (stride field), the next 64 n `SUB` bytes further (leading field).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(SUB >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+// 32 consecutive columns of this thread's lane of tensor memory; follow with tmem_wait_ld().
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* r) {
+    uint32_t* u = reinterpret_cast<uint32_t*>(r);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+                   "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]),
+                   "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
+                   "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* r) {
+    const uint32_t* u = reinterpret_cast<const uint32_t*>(r);
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};\n"
+                 ::"r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
+                   "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]),
+                   "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]),
+                   "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31]),
+                   "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Params p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[1 + 7 * STAGES];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const uint32_t q_smem = smem_u32(smem);
+    const uint32_t k_smem = q_smem + TILE, v_smem = k_smem + STAGES * TILE, p_smem = v_smem + STAGES * TILE;
+    const uint32_t q_full = smem_u32(&bars[0]);
+    const uint32_t k_full = q_full + 8, k_empty = k_full + 8 * STAGES, v_full = k_empty + 8 * STAGES,
+                   v_empty = v_full + 8 * STAGES, s_full = v_empty + 8 * STAGES, p_full = s_full + 8 * STAGES,
+                   pv_done = p_full + 8 * STAGES;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(k_full + 8 * s, 1);
+            mbar_init(k_empty + 8 * s, 1);
+            mbar_init(v_full + 8 * s, 1);
+            mbar_init(v_empty + 8 * s, 1);
+            mbar_init(s_full + 8 * s, 1);
+            mbar_init(p_full + 8 * s, BQ);              // one arrival per softmax thread
+            mbar_init(pv_done + 8 * s, 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_s;
+    const uint32_t tmem_o = tmem + 2 * BKV;
+    volatile int* abort_flag = &abort_s;
+
+    // q and the cache come from the kernels before this one
+    pdl_wait();
+    pdl_launch_dependents();
+
+    // the tiles were listed in order of position: the last ones, which see the most keys, go first
+    const int tile = p.tiles - 1 - (int)blockIdx.y;
+    const int head = blockIdx.x;
+    const int req = p.tile_req[tile], start = p.tile_start[tile];
+    const int q_begin = p.cu_seqlens[req];
+    const int new_len = p.cu_seqlens[req + 1] - q_begin;
+    const int rows_valid = min(BQ, new_len - start);
+    const int pos0 = p.prefix_lens[req] + start;         // position of the tile's first row
+    const int kv_end = pos0 + rows_valid;                // keys the last row sees, exclusive
+    const int k_lo = (p.window > 0 && pos0 + 1 > p.window) ? pos0 + 1 - p.window : 0;
+    const int jt0 = k_lo / BKV;
+    const int n = (kv_end - 1) / BKV - jt0 + 1;          // key tiles of this block (>= 1)
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int kvh = head / (p.nq / p.nkv);
+            const int* table = p.block_table + (size_t)req * p.bt_stride;
+            mbar_expect_tx(q_full, TILE);
+            tma_load_3d(q_smem, &map_q, q_full, 0, head, q_begin + start);
+            tma_load_3d(q_smem + SUB, &map_q, q_full, 64, head, q_begin + start);
+            bool ok = true;
+            int issued_k = 0, issued_v = 0;
+            for (int j = 0; j < n && ok; ++j) {
+                const int s = j % STAGES;
+                const uint32_t par = (uint32_t)((j / STAGES) & 1);
+                int page[2], off[2];
+                for (int h = 0; h < 2; ++h) {            // the two 64-key boxes of the tile
+                    const int key = (jt0 + j) * BKV + 64 * h;
+                    const bool held = key < kv_end;
+                    page[h] = held ? table[key / p.page_size] : 0;
+                    off[h] = held ? key % p.page_size : 0;
+                }
+                ok = mbar_wait(k_empty + 8 * s, par ^ 1, abort_flag, 1);
+                if (!ok) break;
+                mbar_expect_tx(k_full + 8 * s, TILE);
+                for (int h = 0; h < 2; ++h)
+                    for (int dh = 0; dh < 2; ++dh)
+                        tma_load_4d(k_smem + s * TILE + dh * SUB + h * BOX, &map_kv, k_full + 8 * s, dh * 64, off[h], kvh, page[h]);
+                ++issued_k;
+                ok = mbar_wait(v_empty + 8 * s, par ^ 1, abort_flag, 2);
+                if (!ok) break;
+                mbar_expect_tx(v_full + 8 * s, TILE);
+                for (int h = 0; h < 2; ++h)
+                    for (int dh = 0; dh < 2; ++dh)
+                        tma_load_4d(v_smem + s * TILE + dh * SUB + h * BOX, &map_kv, v_full + 8 * s, dh * 64, off[h], p.nkv + kvh, page[h]);
+                ++issued_v;
+            }
+            if (*abort_flag) {
+                // copies already issued still land in this block's shared memory: give each a bounded wait
+                for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(q_full, 0); ++i) {}
+                for (int j = max(0, issued_k - STAGES); j < issued_k; ++j)
+                    for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(k_full + 8 * (j % STAGES), (j / STAGES) & 1); ++i) {}
+                for (int j = max(0, issued_v - STAGES); j < issued_v; ++j)
+                    for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(v_full + 8 * (j % STAGES), (j / STAGES) & 1); ++i) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // kind::f16: float32 accumulator, bfloat16 a and b, n = 128, m = 128; bit 16 makes b MN-major
+            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKV >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+            const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+            bool ok = mbar_wait(q_full, 0, abort_flag, 3);
+            auto scores = [&](int i) {                   // S_i = Q K_i^T into accumulator i % 2
+                const int s = i % STAGES;
+                if (!mbar_wait(k_full + 8 * s, (uint32_t)((i / STAGES) & 1), abort_flag, 4)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t inside = (uint32_t)((kk >> 2) * SUB + (kk & 3) * 32);
+                    umma(tmem + (uint32_t)(i & 1) * BKV, desc_k_major(q_smem + inside), desc_k_major(k_smem + s * TILE + inside),
+                         idesc_s, kk != 0 ? 1u : 0u);
+                }
+                umma_commit(k_empty + 8 * s);
+                umma_commit(s_full + 8 * (i & 1));
+                return true;
+            };
+            if (ok) ok = scores(0);
+            for (int j = 0; j < n && ok; ++j) {
+                const int s = j % STAGES, b = j & 1;
+                const uint32_t par = (uint32_t)((j / STAGES) & 1);
+                if (j + 1 < n) {
+                    ok = scores(j + 1);
+                    if (!ok) break;
+                }
+                ok = mbar_wait(p_full + 8 * b, par, abort_flag, 5) && mbar_wait(v_full + 8 * s, par, abort_flag, 6);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; ++kk) {
+                    const uint64_t da = desc_k_major(p_smem + b * TILE + (kk >> 2) * SUB + (kk & 3) * 32);
+                    const uint64_t db = desc_mn_major(v_smem + s * TILE + kk * 2048);
+                    umma(tmem_o, da, db, idesc_o, (j | kk) != 0 ? 1u : 0u);
+                }
+                umma_commit(v_empty + 8 * s);
+                umma_commit(pv_done + 8 * b);
+            }
+        }
+    } else {
+        const int row = (warp & 3) * 32 + lane;           // the lane of tensor memory this thread may read
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        const int pos = pos0 + row;
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n && ok; ++j) {
+            const int b = j & 1;
+            ok = mbar_wait(s_full + 8 * b, (uint32_t)((j >> 1) & 1), abort_flag, 7);
+            if (!ok) break;
+            tc_fence_after();
+            float s[BKV];
+#pragma unroll
+            for (int c = 0; c < BKV / 32; ++c) tmem_ld32(tmem + lane_addr + (uint32_t)(b * BKV + c * 32), s + c * 32);
+            tmem_wait_ld();
+            const int kb = (jt0 + j) * BKV;
+            const bool need_mask = kb + BKV - 1 > pos0 || (p.window > 0 && kb <= pos0 + BQ - 1 - p.window);
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < BKV; ++c) {
+                    const int key = kb + c;
+                    const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window);
+                    s[c] = seen ? s[c] : -INFINITY;
+                }
+            }
+            float mx = s[0];
+#pragma unroll
+            for (int c = 1; c < BKV; ++c) mx = fmaxf(mx, s[c]);
+            const float m_new = fmaxf(m_used, mx);
+            if (j == 0) {
+                m_used = m_new;
+            } else {
+                const bool grow = (m_new - m_used) * p.scale_log2 > GROW_LOG2;      // also when m_used is -inf
+                if (__any_sync(0xffffffffu, grow)) {
+                    // O must hold every product up to tile j - 1 before its rows are rescaled
+                    ok = mbar_wait(pv_done + 8 * ((j - 1) & 1), (uint32_t)(((j - 1) >> 1) & 1), abort_flag, 8);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const float alpha = grow ? ex2((m_used - m_new) * p.scale_log2) : 1.f;
+                    if (grow) m_used = m_new;
+                    l *= alpha;
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; ++c) {
+                        float o[32];
+                        tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] *= alpha;
+                        tmem_st32(tmem_o + lane_addr + (uint32_t)(c * 32), o);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            const float mb = (m_used == -INFINITY ? 0.f : m_used) * p.scale_log2;
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < BKV; ++c) {
+                s[c] = ex2(fmaf(s[c], p.scale_log2, -mb));
+                sum += s[c];
+            }
+            l += sum;
+            if (j >= 2) {                                  // the product that read this P buffer last is done
+                ok = mbar_wait(pv_done + 8 * b, (uint32_t)(((j - 2) >> 1) & 1), abort_flag, 9);
+                if (!ok) break;
+            }
+            unsigned char* prow = smem + (size_t)(1 + 2 * STAGES) * TILE + (size_t)b * TILE + (size_t)row * 128;
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float* v = s + t * 64 + c * 8;
+                    *reinterpret_cast<uint4*>(prow + t * SUB + ((c ^ (row & 7)) << 4)) =
+                        make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+                }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // the tensor cores read P through the async proxy
+            tc_fence_before();
+            mbar_arrive(p_full + 8 * b);
+        }
+        if (ok) ok = mbar_wait(pv_done + 8 * ((n - 1) & 1), (uint32_t)(((n - 1) >> 1) & 1), abort_flag, 10);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* dst = p.out + ((size_t)(q_begin + start + row) * p.nq + head) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                float o[32];
+                tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), o);
+                tmem_wait_ld();
+                if (row < rows_valid) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v)
+                        *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) =
+                            make_uint4(pack2(o[v * 8] * inv, o[v * 8 + 1] * inv), pack2(o[v * 8 + 2] * inv, o[v * 8 + 3] * inv),
+                                       pack2(o[v * 8 + 4] * inv, o[v * 8 + 5] * inv), pack2(o[v * 8 + 6] * inv, o[v * 8 + 7] * inv));
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)ptr;
+    });
+    return fn;
+}
+
+}  // namespace fa
+}  // namespace lily
+
+using namespace lily;
+
+LILY_API int lily_attention_prefill_tc_rows() { return fa::BQ; }
+
+// Whether the tcgen05 kernel takes this head size and page size (bfloat16 only).
+LILY_API int lily_attention_prefill_tc_takes(int d, int page_size) { return d == fa::D && page_size > 0 && page_size % 64 == 0; }
+
+// 0 while no wait has given up since the last call; else (code << 24 | block).  Codes: 1, 2 the
+// loader waiting for a free K or V stage; 3, 4, 6 the mma thread waiting for Q, K or V; 5 the mma
+// thread waiting for P; 7 the softmax waiting for scores; 8, 9, 10 the softmax waiting for a product
+// into O.  Synchronises the device.  Reading clears it.
+LILY_API int lily_attention_tc_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, fa::g_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(fa::g_status, &zero, sizeof(int));
+    return v;
+}
+
+// The arguments of lily_attention_prefill_mma with tiles of 128 rows, plus the number of pages of
+// the layer (`kv` is [num_pages, 2, nkv, page_size, d]) and of new tokens (`q` is [tokens, nq, d]).
+LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out, const int* block_table, int bt_stride,
+                                       const int* cu_seqlens, const int* prefix_lens, const int* tile_req,
+                                       const int* tile_start, int tiles, int nq, int nkv, int d, int page_size, int window,
+                                       float scale, int tokens, int num_pages, cudaStream_t stream) {
+    if (tiles == 0) return 0;
+    LILY_REQUIRE(lily_attention_prefill_tc_takes(d, page_size), "attention_prefill_tc: head size %d, page size %d (takes %d and multiples of 64)",
+                 d, page_size, fa::D);
+    LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill_tc: %d query heads over %d kv heads", nq, nkv);
+    LILY_REQUIRE(tiles <= 65535 && tokens > 0 && num_pages > 0, "attention_prefill_tc: tiles=%d tokens=%d pages=%d", tiles, tokens, num_pages);
+    LILY_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)kv % 16 == 0) && ((uintptr_t)out % 16 == 0), "attention_prefill_tc: operands must be 16-byte aligned");
+    fa::EncodeTiled enc = fa::encoder();
+    LILY_REQUIRE(enc != nullptr, "attention_prefill_tc: the driver does not offer cuTensorMapEncodeTiled");
+    CUtensorMap map_q, map_kv;
+    {
+        const cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)nq, (cuuint64_t)tokens};
+        const cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)nq * d * 2};
+        const cuuint32_t box[3] = {64, 1, (cuuint32_t)fa::BQ};
+        const cuuint32_t elem[3] = {1, 1, 1};
+        const CUresult rc = enc(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        LILY_REQUIRE(rc == CUDA_SUCCESS, "attention_prefill_tc: cuTensorMapEncodeTiled (q) failed with %d", (int)rc);
+    }
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)page_size, (cuuint64_t)2 * nkv, (cuuint64_t)num_pages};
+        const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)page_size * d * 2, (cuuint64_t)2 * nkv * page_size * d * 2};
+        const cuuint32_t box[4] = {64, 64, 1, 1};
+        const cuuint32_t elem[4] = {1, 1, 1, 1};
+        const CUresult rc = enc(&map_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(kv), dims, strides, box, elem,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        LILY_REQUIRE(rc == CUDA_SUCCESS, "attention_prefill_tc: cuTensorMapEncodeTiled (cache) failed with %d", (int)rc);
+    }
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(fa::attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::SMEM);
+        if (e != cudaSuccess) {
+            set_error("attention_prefill_tc: cannot get %d bytes of shared memory: %s", fa::SMEM, cudaGetErrorString(e));
+            return 2;
+        }
+        configured = true;
+    }
+    fa::Params p{};
+    p.block_table = block_table; p.cu_seqlens = cu_seqlens; p.prefix_lens = prefix_lens; p.tile_req = tile_req;
+    p.tile_start = tile_start; p.out = (__nv_bfloat16*)out; p.bt_stride = bt_stride; p.tiles = tiles; p.nq = nq; p.nkv = nkv;
+    p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    launch_pdl(fa::attention_prefill_tc_kernel, dim3(nq, tiles), dim3(fa::THREADS), (size_t)fa::SMEM, stream, map_q, map_kv, p);
+    LILY_CHECK_LAUNCH("attention_prefill_tc");
+    return 0;
+}

@@ -29,7 +29,7 @@ from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-SOURCES = ["elementwise.cu", "gemm_fp32.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "attention_simt.cu", "attention_mma.cu", "sampling.cu",
+SOURCES = ["elementwise.cu", "gemm_fp32.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "attention_simt.cu", "attention_mma.cu", "attention_tcgen05.cu", "sampling.cu",
            "attention_decode_static.cu"]
 HEADERS = ["common.cuh", "attention_args.cuh", "no_alloc.h"]
 

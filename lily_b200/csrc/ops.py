@@ -34,6 +34,7 @@ _SIGNATURES = {
     "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
     "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
     "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
@@ -63,6 +64,9 @@ def library():
         lib.lily_skinny_gemm_splits.argtypes = [_i, _i, _i]
         lib.lily_skinny_gemm_splits.restype = _i
         lib.lily_attention_prefill_mma_rows.restype = _i
+        lib.lily_attention_prefill_tc_rows.restype = _i
+        lib.lily_attention_prefill_tc_takes.argtypes = [_i, _i]
+        lib.lily_attention_prefill_tc_takes.restype = _i
         lib.lily_attention_mma_supports.argtypes = [_i]
         lib.lily_attention_mma_supports.restype = _i
         lib.lily_attention_decode_scratch_floats.argtypes = [_i, _i, _i, _i]
@@ -316,25 +320,57 @@ def uses_tensor_cores(dtype: torch.dtype, d: int) -> bool:
     return dtype == torch.bfloat16 and bool(library().lily_attention_mma_supports(int(d)))
 
 
-def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0) -> int:
-    """New tokens per tile of the prefill kernel that will take this precision and head size."""
+# A step with fewer new tokens than this in its prompt portions runs them through the mma.sync kernel
+# (tiles of 64 rows); from here on the tcgen05 kernel's tiles of 128 rows are worth filling.
+TC_ATTENTION_MIN_TOKENS = 128
+
+
+def uses_tcgen05_attention(dtype: torch.dtype, d: int, page_size: int, new_tokens: int) -> bool:
+    """Whether prefill attention of this precision, head size, page size and number of new tokens
+    runs on the tcgen05 kernel (bfloat16, head size 128, pages of a multiple of 64 positions)."""
+    return (dtype == torch.bfloat16 and new_tokens >= TC_ATTENTION_MIN_TOKENS
+            and bool(library().lily_attention_prefill_tc_takes(int(d), int(page_size))))
+
+
+def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size: int = 0, new_tokens: int = 0) -> int:
+    """New tokens per tile of the prefill kernel that will take this precision, head size, page
+    size and number of new tokens."""
     lib = library()
+    if uses_tcgen05_attention(dtype, d, page_size, new_tokens):
+        return int(lib.lily_attention_prefill_tc_rows())
     return int(lib.lily_attention_prefill_mma_rows() if uses_tensor_cores(dtype, d) else lib.lily_attention_prefill_simt_rows())
+
+
+def attention_tc_status() -> int:
+    """0, or a code from the first bounded wait that gave up in the tcgen05 attention kernel (synchronises)."""
+    return int(library().lily_attention_tc_status())
 
 
 def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
                       prefix_lens: torch.Tensor, tile_req: torch.Tensor, tile_start: torch.Tensor, out: torch.Tensor,
-                      nq: int, nkv: int, d: int, page_size: int, scale: float, window: Optional[int] = None) -> None:
+                      nq: int, nkv: int, d: int, page_size: int, scale: float, window: Optional[int] = None,
+                      tile_rows: Optional[int] = None) -> None:
     """Causal attention of each request's new tokens over its cached prefix and themselves.
     ``q`` and ``out`` are [tokens, nq * d] indexed by ``cu_seqlens``; tiles list (request, offset)
-    in steps of ``prefill_tile_rows(q.dtype, d)``."""
+    in steps of ``tile_rows`` (default: ``prefill_tile_rows(q.dtype, d)``), which also names the
+    kernel: the tcgen05 kernel takes tiles of its own size, the others theirs."""
     _dev(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out)
     if q.dtype != kv_layer.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, cache and out must share a dtype")
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
               _i32(cu_seqlens, "cu_seqlens"), _i32(prefix_lens, "prefix_lens"), _i32(tile_req, "tile_req"),
               _i32(tile_start, "tile_start"), tile_req.numel(), nq, nkv, d, page_size, int(window or 0), float(scale))
-    if uses_tensor_cores(q.dtype, d):
+    lib = library()
+    base_rows = int(lib.lily_attention_prefill_mma_rows() if uses_tensor_cores(q.dtype, d) else lib.lily_attention_prefill_simt_rows())
+    if tile_rows is not None and tile_rows != base_rows:
+        if not (tile_rows == int(lib.lily_attention_prefill_tc_rows()) and q.dtype == torch.bfloat16
+                and lib.lily_attention_prefill_tc_takes(int(d), int(page_size))):
+            raise KernelError(f"attention_prefill: no kernel with tiles of {tile_rows} rows for {q.dtype}, head size {d}, "
+                              f"page size {page_size}")
+        if not (q.is_contiguous() and out.is_contiguous() and kv_layer.is_contiguous()):
+            raise KernelError("attention_prefill: the tcgen05 kernel takes contiguous q, out and cache")
+        _call("lily_attention_prefill_tc", *common, q.shape[0], kv_layer.shape[0], _stream())
+    elif uses_tensor_cores(q.dtype, d):
         _call("lily_attention_prefill_mma", *common, _stream())
     else:
         _call("lily_attention_prefill_simt", *common, _dt(q), _stream())

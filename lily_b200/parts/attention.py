@@ -119,7 +119,8 @@ class Attention(Mixer):
             ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out[:nd], scratch, splits,
                                  s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window)
         if batch.num_requests > nd:
-            tile_req, tile_start = batch.tiles(ops.prefill_tile_rows(q.dtype, s.head_dim))
+            rows = ops.prefill_tile_rows(q.dtype, s.head_dim, page, batch.num_tokens - nd)
+            tile_req, tile_start = batch.tiles(rows)
             ops.attention_prefill(q, cache.data, table, batch.cu_seqlens, batch.prefix_lens, tile_req, tile_start,
-                                  out, s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window)
+                                  out, s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window, tile_rows=rows)
         return getattr(ops, "linear_auto", ops.linear)(out, self.w_o, self.b_o)

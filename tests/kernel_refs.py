@@ -91,7 +91,7 @@ def linear(x, weight, bias=None, out_dtype=None):
     return out.to(out_dtype or x.dtype)
 
 
-def prefill_tile_rows(dtype=None, d=0):
+def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0):
     return 32
 
 
@@ -121,7 +121,7 @@ def _attend(q, k, v, q_pos, scale, window):
 
 
 def attention_prefill(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out, nq, nkv, d,
-                      page_size, scale, window=None):
+                      page_size, scale, window=None, tile_rows=None):
     for r in sorted(set(tile_req.tolist())):
         t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
         prefix = int(prefix_lens[r])

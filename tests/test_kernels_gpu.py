@@ -261,6 +261,60 @@ def test_attention_prefill(dtype, nq, nkv, d, page, window):
     torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
 
 
+def _tiles_of(news, rows):
+    treq = [r for r, n in enumerate(news) for _ in range(0, n, rows)]
+    tstart = [s for r, n in enumerate(news) for s in range(0, n, rows)]
+    return (torch.tensor(treq, device=DEV, dtype=torch.int32), torch.tensor(tstart, device=DEV, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("nq,nkv,page,window", [(8, 2, 64, None), (4, 4, 128, None), (6, 1, 256, None), (4, 2, 64, 200),
+                                                 (2, 1, 64, 100), (4, 2, 128, 129)])
+def test_attention_prefill_tcgen05(nq, nkv, page, window):
+    """The tcgen05 kernel (tiles of 128 rows) against the plain statement: cached prefixes that end
+    inside a page and inside a key tile, portions shorter and longer than a tile, one token."""
+    o, d, dtype = ops(), 128, torch.bfloat16
+    rows = o.prefill_tile_rows(dtype, d, page, 10 ** 6)
+    assert rows == 128 and o.uses_tcgen05_attention(dtype, d, page, 4096) and not o.uses_tcgen05_attention(dtype, d, 16, 4096)
+    prefixes, news = [0, 17, 130, 5, 700, 64, 1000], [1, 70, 333, 200, 129, 2, 640]
+    cache, table, q, cu, pre = _attention_case(dtype, nq, nkv, d, page, prefixes, news, window, spike=True)
+    treq_t, tstart_t = _tiles_of(news, rows)
+    got, want = torch.zeros_like(q), torch.zeros_like(q)
+    o.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, got, nq, nkv, d, page, d ** -0.5, window, tile_rows=rows)
+    assert o.attention_tc_status() == 0
+    ref.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, want, nq, nkv, d, page, d ** -0.5, window)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    # the mma.sync kernel on the same case, cut into its own tiles, agrees too
+    base = o.prefill_tile_rows(dtype, d)
+    breq, bstart = _tiles_of(news, base)
+    other = torch.zeros_like(q)
+    o.attention_prefill(q, cache, table, cu, pre, breq, bstart, other, nq, nkv, d, page, d ** -0.5, window)
+    torch.testing.assert_close(got.float(), other.float(), **tol(dtype))
+
+
+def test_attention_prefill_tcgen05_rising_scores():
+    """Scores that grow by far more than 2^8 from one key tile to the next, for every row: the kernel
+    must rescale the output in tensor memory each time (the path that ordinary data rarely takes)."""
+    o, d, dtype, nq, nkv, page = ops(), 128, torch.bfloat16, 4, 2, 64
+    g = torch.Generator(device=DEV).manual_seed(21)
+    prefixes, news = [300, 0], [520, 700]
+    cache, table, q, cu, pre = _attention_case(dtype, nq, nkv, d, page, prefixes, news, None, seed=22)
+    u = torch.randn(d, device=DEV, generator=g)
+    q = (0.5 * q.float().view(-1, nq, d) + u).view(q.shape).to(dtype)
+    for r, (p, n) in enumerate(zip(prefixes, news)):
+        for pos, c in ((40, 0.25), (190, 0.5), (330, 1.0), (470, 1.5), (p + n - 90, 2.5), (p + n - 3, 4.0)):
+            pg, off = int(table[r, pos // page]), pos % page
+            cache[pg, 0, :, off] = (c * u).to(dtype)
+            cache[pg, 1, :, off] = c
+    rows = o.prefill_tile_rows(dtype, d, page, 10 ** 6)
+    treq_t, tstart_t = _tiles_of(news, rows)
+    got, want = torch.zeros_like(q), torch.zeros_like(q)
+    o.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, got, nq, nkv, d, page, d ** -0.5, None, tile_rows=rows)
+    assert o.attention_tc_status() == 0
+    ref.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, want, nq, nkv, d, page, d ** -0.5, None)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    assert float(want.float()[-1].view(nq, d)[0].mean()) > 3.5          # the last row sees the strongest key
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("splits", [1, 3, 8])
 @pytest.mark.parametrize("nq,nkv,d,page,window", [
