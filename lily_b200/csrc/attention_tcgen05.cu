@@ -1,11 +1,11 @@
 // Causal paged attention for prefill on the fifth-generation tensor cores (bfloat16, head size 128):
 // both products of a tile, S = Q K^T and O += P V, are tcgen05.mma instructions with their
-// accumulators in tensor memory, the operands arrive by TMA, and the softmax runs one thread per
+// accumulators in tensor memory, the operands arrive by TMA, and the softmax runs two threads per
 // query row straight out of tensor memory.  (The reference runs prefill attention through a
 // library: lily/layers/attention/flashinfer_backend.py:188-203.)
 //
 // One block works on 128 new tokens of one request and one query head, walking the keys in tiles
-// of 128 from the first the window allows to the last the causal rule allows.  Its six warps:
+// of 128 from the first the window allows to the last the causal rule allows.  Its ten warps:
 //   warp 0   one thread issues the TMA loads: Q once (two [128 x 64] boxes, 128-byte swizzle), then
 //            for each tile K and V as [64 keys x 64 features] boxes taken from the request's pages
 //            (a box never crosses a page: the page size is a multiple of 64), into two stages each;
@@ -14,13 +14,14 @@
 //            before it waits for P_j, then O += P_j V_j (V is read as it lies in the cache,
 //            [key][feature], which is the MN-major form of the B operand), so that the tensor cores
 //            work on the next scores while the softmax of the current ones runs;
-//   warps 2-5  one thread per query row: reads its row of S from tensor memory (tcgen05.ld), masks
-//            the tiles on the diagonal and at the window's edge, keeps the running maximum and sum
-//            in float32, writes P = exp2(s * scale - max) as bfloat16 into shared memory in the
-//            swizzled k-major layout that the second product reads, and at the end divides O by the
-//            sum and stores it.
+//   warps 2-9  two threads per query row, each with 64 of the tile's 128 keys: read their half of the
+//            row of S from tensor memory (tcgen05.ld), mask the tiles on the diagonal and at the
+//            window's edge, agree on the row's maximum, keep the running maximum and sum in float32,
+//            write P = exp2(s * scale - max) as bfloat16 into shared memory in the swizzled k-major
+//            layout that the second product reads, and at the end divide their half of O by the sum
+//            and store it.  (Two warps per scheduler hide each other's latencies; one does not.)
 // The maximum that P is taken against only moves when the true maximum has grown by more than 2^8
-// since (then O and the sum are rescaled by the thread that owns the row, in tensor memory), so
+// since (then O and the sum are rescaled by the threads that own the row, in tensor memory), so
 // the usual tile costs no pass over O; the result is the same quotient of sums either way.
 //
 // Keys past the request's length and rows past its new tokens are computed on whatever the pages
@@ -44,8 +45,15 @@ constexpr int STAGES = 2;                 // K stages, V stages, P buffers, S ac
 constexpr int SUB = 128 * 64 * 2;         // a [128 rows][64 elements] sub-tile with 128-byte rows: 16 KB
 constexpr int TILE = 2 * SUB;             // Q, one K stage, one V stage, one P buffer: 32 KB
 constexpr int BOX = 64 * 64 * 2;          // one TMA box of K or V: 8 KB
-constexpr int THREADS = 192;
-constexpr int SMEM = (1 + 3 * STAGES) * TILE + 1024;
+constexpr int SOFTMAX_THREADS = 256;     // two threads per query row, each with half of the row's keys
+constexpr int THREADS = 64 + SOFTMAX_THREADS;
+constexpr int NUM_BARS = 1 + 7 * STAGES;
+// shared memory, all of it dynamic and 1024-byte aligned: Q | K stages | V stages | P buffers | mbarriers |
+// tensor-memory base and abort flag | the row maxima and sums that the two threads of a row exchange
+constexpr int OFF_BARS = (1 + 3 * STAGES) * TILE;
+constexpr int OFF_MISC = OFF_BARS + 8 * NUM_BARS + 8;
+constexpr int OFF_XCH = OFF_MISC + 16;
+constexpr int SMEM = OFF_XCH + 2 * 2 * BQ * 4;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr float GROW_LOG2 = 8.f;          // the reference maximum moves when the true one is 2^8 ahead
 
@@ -160,12 +168,16 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Params p) {
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t bars[1 + 7 * STAGES];
-    __shared__ uint32_t tmem_base_s;
-    __shared__ int abort_s;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
+    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem + OFF_MISC);
+    int& abort_s = *reinterpret_cast<int*>(smem + OFF_MISC + 4);
+    float* xch = reinterpret_cast<float*>(smem + OFF_XCH);      // [tile parity][half][row]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if ((smem_u32(smem) & 1023u) != 0) {                        // the swizzled tiles need it; never seen, but checked
+        if (threadIdx.x == 0) atomicCAS(&g_status, 0, (11 << 24) | (int)((blockIdx.x + blockIdx.y * gridDim.x) & 0xFFFFFF));
+        return;
+    }
 
     const uint32_t q_smem = smem_u32(smem);
     const uint32_t k_smem = q_smem + TILE, v_smem = k_smem + STAGES * TILE, p_smem = v_smem + STAGES * TILE;
@@ -183,10 +195,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(v_full + 8 * s, 1);
             mbar_init(v_empty + 8 * s, 1);
             mbar_init(s_full + 8 * s, 1);
-            mbar_init(p_full + 8 * s, BQ);              // one arrival per softmax thread
+            mbar_init(p_full + 8 * s, SOFTMAX_THREADS); // one arrival per softmax thread
             mbar_init(pv_done + 8 * s, 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (threadIdx.x < 2 * BQ) {                                  // exchange slots start with the tag before their first
+        reinterpret_cast<uint32_t*>(xch)[threadIdx.x] = 3u;                       // parity 0: tags 1, 3, 1, ...
+        reinterpret_cast<uint32_t*>(xch)[2 * BQ + threadIdx.x] = 0u;              // parity 1: tags 2, 0, 2, ...
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(512) : "memory");
@@ -301,34 +317,66 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
         }
     } else {
-        const int row = (warp & 3) * 32 + lane;           // the lane of tensor memory this thread may read
-        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        // warps 2-5 take keys [0, 64) of each tile, warps 6-9 keys [64, 128); a warp reads the quarter
+        // of tensor memory (32 lanes = 32 query rows) that its index modulo 4 names
+        constexpr int HALF = BKV / 2;
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const int pos = pos0 + row;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
+        // The two threads of a row hand each other one float per tile (the maximum of their half; at
+        // the end their sum) through a word of shared memory whose two lowest mantissa bits carry a
+        // sequence tag, so the reader knows the word is this tile's without a barrier that an aborted
+        // partner would never reach.  Slots alternate with the tile's parity; both threads drop the
+        // same two bits of their own value, so they agree on the result.
+        volatile uint32_t* xw = reinterpret_cast<volatile uint32_t*>(xch);
+        auto exchange = [&](int seq, float mine, float& both_mine, float& other) {
+            const uint32_t tag = (uint32_t)(seq + 1) & 3u;
+            const uint32_t bits = __float_as_uint(mine) & ~3u;
+            xw[((seq & 1) * 2 + half) * BQ + row] = bits | tag;
+            both_mine = __uint_as_float(bits);
+            volatile uint32_t* from = xw + ((seq & 1) * 2 + (half ^ 1)) * BQ + row;
+            for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+                const uint32_t v = *from;
+                if ((v & 3u) == tag) {
+                    other = __uint_as_float(v & ~3u);
+                    return true;
+                }
+                if ((i & 1023u) == 1023u && *abort_flag) return false;
+            }
+            *abort_flag = 1;
+            atomicCAS(&g_status, 0, (12 << 24) | (int)((blockIdx.x + blockIdx.y * gridDim.x) & 0xFFFFFF));
+            return false;
+        };
         for (int j = 0; j < n && ok; ++j) {
             const int b = j & 1;
             ok = mbar_wait(s_full + 8 * b, (uint32_t)((j >> 1) & 1), abort_flag, 7);
             if (!ok) break;
             tc_fence_after();
-            float s[BKV];
+            float s[HALF];
 #pragma unroll
-            for (int c = 0; c < BKV / 32; ++c) tmem_ld32(tmem + lane_addr + (uint32_t)(b * BKV + c * 32), s + c * 32);
+            for (int c = 0; c < HALF / 32; ++c) tmem_ld32(tmem + lane_addr + (uint32_t)(b * BKV + half * HALF + c * 32), s + c * 32);
             tmem_wait_ld();
-            const int kb = (jt0 + j) * BKV;
-            const bool need_mask = kb + BKV - 1 > pos0 || (p.window > 0 && kb <= pos0 + BQ - 1 - p.window);
+            const int kb = (jt0 + j) * BKV + half * HALF;
+            const bool need_mask = kb + HALF - 1 > pos0 || (p.window > 0 && kb <= pos0 + BQ - 1 - p.window);
             if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < BKV; ++c) {
+                for (int c = 0; c < HALF; ++c) {
                     const int key = kb + c;
                     const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window);
                     s[c] = seen ? s[c] : -INFINITY;
                 }
             }
-            float mx = s[0];
+            float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-            for (int c = 1; c < BKV; ++c) mx = fmaxf(mx, s[c]);
-            const float m_new = fmaxf(m_used, mx);
+            for (int c = 4; c < HALF; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+            const float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            float mine_r, theirs;
+            ok = exchange(j, mine, mine_r, theirs);
+            if (!ok) break;
+            const float m_new = fmaxf(m_used, fmaxf(mine_r, theirs));
             if (j == 0) {
                 m_used = m_new;
             } else {
@@ -342,51 +390,58 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (grow) m_used = m_new;
                     l *= alpha;
 #pragma unroll 1
-                    for (int c = 0; c < D / 32; ++c) {
+                    for (int c = 0; c < D / 64; ++c) {         // this thread's half of the row of O
                         float o[32];
-                        tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), o);
+                        tmem_ld32(tmem_o + lane_addr + (uint32_t)(half * (D / 2) + c * 32), o);
                         tmem_wait_ld();
 #pragma unroll
                         for (int e = 0; e < 32; ++e) o[e] *= alpha;
-                        tmem_st32(tmem_o + lane_addr + (uint32_t)(c * 32), o);
+                        tmem_st32(tmem_o + lane_addr + (uint32_t)(half * (D / 2) + c * 32), o);
                     }
                     tmem_wait_st();
                 }
             }
             const float mb = (m_used == -INFINITY ? 0.f : m_used) * p.scale_log2;
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < BKV; ++c) {
+            for (int c = 0; c < HALF; ++c) {
                 s[c] = ex2(fmaf(s[c], p.scale_log2, -mb));
-                sum += s[c];
+                sum4[c & 3] += s[c];
             }
-            l += sum;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if (j >= 2) {                                  // the product that read this P buffer last is done
                 ok = mbar_wait(pv_done + 8 * b, (uint32_t)(((j - 2) >> 1) & 1), abort_flag, 9);
                 if (!ok) break;
             }
-            unsigned char* prow = smem + (size_t)(1 + 2 * STAGES) * TILE + (size_t)b * TILE + (size_t)row * 128;
+            // keys [64 half, 64 half + 64) of P are the sub-tile `half`: 128-byte rows, 16-byte pieces swizzled
+            unsigned char* prow = smem + (size_t)(1 + 2 * STAGES) * TILE + (size_t)b * TILE + (size_t)half * SUB + (size_t)row * 128;
 #pragma unroll
-            for (int t = 0; t < 2; ++t)
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const float* v = s + t * 64 + c * 8;
-                    *reinterpret_cast<uint4*>(prow + t * SUB + ((c ^ (row & 7)) << 4)) =
-                        make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
-                }
+            for (int c = 0; c < 8; ++c) {
+                const float* v = s + c * 8;
+                *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
+                    make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+            }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // the tensor cores read P through the async proxy
             tc_fence_before();
             mbar_arrive(p_full + 8 * b);
         }
-        if (ok) ok = mbar_wait(pv_done + 8 * ((n - 1) & 1), (uint32_t)(((n - 1) >> 1) & 1), abort_flag, 10);
+        // the two halves of a row add their sums (slots of the parity that the last tile did not use)
+        if (ok) {
+            float mine_r, theirs;
+            ok = exchange(n, l, mine_r, theirs);
+            l = mine_r + theirs;
+        }
+        if (ok) {
+            ok = mbar_wait(pv_done + 8 * ((n - 1) & 1), (uint32_t)(((n - 1) >> 1) & 1), abort_flag, 10);
+        }
         if (ok) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = p.out + ((size_t)(q_begin + start + row) * p.nq + head) * D;
+            __nv_bfloat16* dst = p.out + ((size_t)(q_begin + start + row) * p.nq + head) * D + half * (D / 2);
 #pragma unroll 1
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < D / 64; ++c) {
                 float o[32];
-                tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), o);
+                tmem_ld32(tmem_o + lane_addr + (uint32_t)(half * (D / 2) + c * 32), o);
                 tmem_wait_ld();
                 if (row < rows_valid) {
 #pragma unroll
