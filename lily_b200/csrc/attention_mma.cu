@@ -72,13 +72,18 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     unsigned char* k_s = smem_raw;                                  // [STAGES][BN][D]
     unsigned char* v_s = k_s + STAGES * BN * D * 2;                 // [STAGES][BN][D]
-    // the queries pass through the second key stage on their way to registers: that stage is first
+    // the queries pass through the last key stage on their way to registers: that stage is first
     // filled after the barrier of the first loop iteration, when every warp has its fragments
-    unsigned char* q_s = k_s + BN * D * 2;                          // [BM][D], BM <= BN
+    unsigned char* q_s = k_s + (STAGES - 1) * BN * D * 2;           // [BM][D], BM <= BN
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
-    pdl_wait();
-    pdl_launch_dependents();
+    // Prefill waits here for the kernel before it (which wrote q and this step's keys).  Decode
+    // waits further down: the block table, the lengths and every cached key but the one of this
+    // step were there before that kernel began, so the first key tiles stream in while it runs.
+    if (!DECODE) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
     const __nv_bfloat16* q = (const __nv_bfloat16*)a.q;
     const __nv_bfloat16* kv = (const __nv_bfloat16*)a.kv;
     const int group = a.nq / a.nkv;
@@ -114,6 +119,46 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         kbeg = (a.window > 0 && pos0 + 1 > a.window) ? pos0 + 1 - a.window : 0;
     }
 
+    const int* table = a.block_table + (size_t)req * a.bt_stride;
+    const size_t head_stride = (size_t)a.page_size * D;
+    const size_t page_stride = 2 * (size_t)a.nkv * head_stride;
+    const int ntiles = kend > kbeg ? (kend - kbeg + BN - 1) / BN : 0;
+
+    const __nv_bfloat16* kv_head = kv + (size_t)kvh * head_stride;
+    const int page_mask = (1 << page_shift) - 1;
+    auto load_tile = [&](int t, int buf) {
+        const int kb = kbeg + t * BN;
+        unsigned char* kd = k_s + buf * BN * D * 2;
+        unsigned char* vd = v_s + buf * BN * D * 2;
+#pragma unroll
+        for (int i = tid; i < BN * CH; i += THREADS) {
+            const int r = i / CH, ch = i % CH;
+            const int kpos = kb + r;
+            const bool ok = kpos < kend;
+            const int page = ok ? table[kpos >> page_shift] : 0;
+            const __nv_bfloat16* src = kv_head + (size_t)page * page_stride + (((ok ? kpos : 0) & page_mask) * D + ch * 8);
+            const uint32_t off = swz<D>(r, ch);
+            cp_async16(smem_u32(kd + off), src, ok);
+            cp_async16(smem_u32(vd + off), src + (size_t)a.nkv * head_stride, ok);
+        }
+    };
+
+    // the pipeline keeps STAGES - 1 tiles in flight; every iteration commits one group (maybe empty).
+    // Decode: the tiles that end before this step's own key are asked for ahead of the wait.
+    int early = 0;
+    if (DECODE) {
+#pragma unroll
+        for (int st = 0; st < STAGES - 1; ++st) {
+            if (st < ntiles && kbeg + (st + 1) * BN <= pos0 && early == st) {
+                load_tile(st, st);
+                cp_async_commit();
+                ++early;
+            }
+        }
+        pdl_wait();
+        pdl_launch_dependents();
+    }
+
     // ---- queries to shared memory (zero rows beyond nrows), then to A fragments -------------
     for (int i = tid; i < BM * CH; i += THREADS) {
         const int r = i / CH, ch = i % CH;
@@ -142,35 +187,12 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
-    const int* table = a.block_table + (size_t)req * a.bt_stride;
-    const size_t head_stride = (size_t)a.page_size * D;
-    const size_t page_stride = 2 * (size_t)a.nkv * head_stride;
-    const int ntiles = kend > kbeg ? (kend - kbeg + BN - 1) / BN : 0;
-
-    const __nv_bfloat16* kv_head = kv + (size_t)kvh * head_stride;
-    const int page_mask = (1 << page_shift) - 1;
-    auto load_tile = [&](int t, int buf) {
-        const int kb = kbeg + t * BN;
-        unsigned char* kd = k_s + buf * BN * D * 2;
-        unsigned char* vd = v_s + buf * BN * D * 2;
-#pragma unroll
-        for (int i = tid; i < BN * CH; i += THREADS) {
-            const int r = i / CH, ch = i % CH;
-            const int kpos = kb + r;
-            const bool ok = kpos < kend;
-            const int page = ok ? table[kpos >> page_shift] : 0;
-            const __nv_bfloat16* src = kv_head + (size_t)page * page_stride + (((ok ? kpos : 0) & page_mask) * D + ch * 8);
-            const uint32_t off = swz<D>(r, ch);
-            cp_async16(smem_u32(kd + off), src, ok);
-            cp_async16(smem_u32(vd + off), src + (size_t)a.nkv * head_stride, ok);
-        }
-    };
-
-    // the pipeline keeps STAGES - 1 tiles in flight; every iteration commits one group (maybe empty)
 #pragma unroll
     for (int st = 0; st < STAGES - 1; ++st) {
-        if (st < ntiles) load_tile(st, st);
-        cp_async_commit();
+        if (st >= early) {
+            if (st < ntiles) load_tile(st, st);
+            cp_async_commit();
+        }
     }
     const float sl2 = a.scale * 1.4426950408889634f;       // scores are kept in units of log2(e)
 

@@ -210,8 +210,7 @@ attention_simt_kernel(const AttnArgs a) {
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          T* __restrict__ out, int nq, int d, int splits) {
-    pdl_wait();
-    pdl_launch_dependents();
+    pdl_enter_small();
     const size_t base = ((size_t)blockIdx.x * nq + blockIdx.y) * splits;
     float mx = -INFINITY;
     for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);

@@ -44,6 +44,16 @@ void set_error(const char* fmt, ...);
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
+// How a short kernel between two long ones enters: the kernel after it may start at once, and
+// stream in what depends on no one (weights, cached keys of earlier steps), while this kernel still
+// waits for its own predecessor.  Every kernel waits before it reads or writes anything that
+// another kernel of the step writes, and a kernel only completes after its wait, so the order of
+// the step's writes is kept along the chain however early the launches are.
+__device__ __forceinline__ void pdl_enter_small() {
+    pdl_launch_dependents();
+    pdl_wait();
+}
+
 bool pdl_enabled();
 
 template <typename... KArgs, typename... Args>

@@ -99,8 +99,7 @@ struct Summed {
 template <typename T, int VEC>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int hidden, int vocab) {
-    pdl_wait();
-    pdl_launch_dependents();
+    pdl_enter_small();
     const int n = blockIdx.x;
     int id = ids[n];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host has checked the range
@@ -124,8 +123,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const Summed<IN> d
                                    const int* __restrict__ rows, int hidden, float eps, int write_residual,
                                    int stash) {
     extern __shared__ __align__(16) float smem[];
-    pdl_wait();
-    pdl_launch_dependents();
+    pdl_enter_small();
     float* red = smem;             // 33 floats
     float* row = smem + 40;        // hidden floats when stash
     const int m = blockIdx.x;
@@ -194,8 +192,7 @@ __global__ void add_rmsnorm_cluster_kernel(float* __restrict__ resid, const Summ
     __shared__ float red[40];
     __shared__ float share[1];
     cg::cluster_group cluster = cg::this_cluster();
-    pdl_wait();
-    pdl_launch_dependents();
+    pdl_enter_small();
     const int m = blockIdx.y;
     const size_t src = (size_t)(rows ? rows[m] : m) * hidden;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;       // this thread's four columns
@@ -225,8 +222,7 @@ __device__ __forceinline__ float silu_times(float g, float u) { return (g / (1.f
 // block | ...]; block == inter is the plain [all gate | all up] order.
 template <typename T, typename IN, int VEC>
 __global__ void silu_mul_kernel(const Summed<IN> gate_up, T* __restrict__ out, int inter, int block, size_t total) {
-    pdl_wait();
-    pdl_launch_dependents();
+    pdl_enter_small();
     const size_t step = (size_t)gridDim.x * blockDim.x * VEC;
     for (size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; idx < total; idx += step) {
         const size_t n = idx / inter;
@@ -254,8 +250,7 @@ __global__ void qk_norm_rope_write_kernel(const Summed<IN> qkv, const W* __restr
                                           const int* __restrict__ block_table, int bt_stride,
                                           T* __restrict__ kv_layer, T* __restrict__ q_out,
                                           int nq, int nkv, int d, int rd, int page_size, int write_kv) {
-    pdl_wait();
-    pdl_launch_dependents();
+    pdl_enter_small();
     const int n = blockIdx.x;
     const int head = blockIdx.y * blockDim.y + threadIdx.y;
     const int nheads = write_kv ? nq + 2 * nkv : nq;
@@ -370,8 +365,7 @@ __global__ void qk_norm_rope_write_wide_kernel(const __nv_bfloat16* __restrict__
                                                const int* __restrict__ block_table, int bt_stride,
                                                __nv_bfloat16* __restrict__ kv_layer, __nv_bfloat16* __restrict__ q_out,
                                                int nq, int nkv, int d, int group, int page_size, int write_kv) {
-    pdl_wait();
-    pdl_launch_dependents();
+    pdl_enter_small();
     const int n = blockIdx.x;
     const int per_block = blockDim.x / group;
     const int head = blockIdx.y * per_block + threadIdx.x / group;

@@ -42,9 +42,10 @@ def setup(request):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_head_size_128_paths_inside_the_engine(dtype):
-    """Head size 128, widths in multiples of 128, page size 64: tensor-core attention (prefill and
-    split-key decode through graphs), the tcgen05 gate/up kernel and the weight-streaming decode
-    product, all through the step function, against the plain implementation."""
+    """Head size 128, widths in multiples of 128, page size 64: tensor-core attention (tcgen05 for
+    portions of 128 tokens and more, mma.sync below that and for split-key decode through graphs),
+    the tcgen05 gate/up kernel and the weight-streaming decode product, all through the step
+    function, against the plain implementation."""
     cfg = tiny_models.MID_QWEN3
     with tempfile.TemporaryDirectory() as tmp:
         path, weights = model_dir(cfg, 33, tmp)
@@ -62,6 +63,10 @@ def test_head_size_128_paths_inside_the_engine(dtype):
             full = plain_impl.all_logits(cfg, rounded(weights, dtype), toks)
             close(got[name], full[:got[name].shape[0]], dtype, name)
         assert runner.graph_steps > 0 and runner.cache.held_pages() == [0]
+        if dtype == "bfloat16":
+            from lily_b200.csrc import ops
+            assert ops.uses_tcgen05_attention(torch.bfloat16, cfg["head_dim"], 64, 130)     # the portions of 130 tokens and more
+            assert ops.attention_tc_status() == 0 and ops.gemm_tc_status() == 0          # no bounded wait gave up
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -268,7 +268,7 @@ def _tiles_of(news, rows):
 
 
 @pytest.mark.parametrize("nq,nkv,page,window", [(8, 2, 64, None), (4, 4, 128, None), (6, 1, 256, None), (4, 2, 64, 200),
-                                                 (2, 1, 64, 100), (4, 2, 128, 129)])
+                                                 (2, 1, 64, 100), (4, 2, 128, 129), (6, 2, 64, None), (3, 3, 64, 70)])
 def test_attention_prefill_tcgen05(nq, nkv, page, window):
     """The tcgen05 kernel (tiles of 128 rows) against the plain statement: cached prefixes that end
     inside a page and inside a key tile, portions shorter and longer than a tile, one token."""
