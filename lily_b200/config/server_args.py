@@ -31,6 +31,7 @@ class ServerArgs:
 
     # Scheduling
     schedule_policy: str = "fcfs"
+    disable_overlap_schedule: bool = False    # read each step's tokens before the next step is launched
 
     # CUDA graphs (decode steps)
     disable_cuda_graph: bool = False

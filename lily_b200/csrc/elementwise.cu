@@ -96,13 +96,16 @@ struct Summed {
 
 // ---------------------------------------------------------------------------- embedding
 
+// An id below zero names a request slot: the token is the one the sampler stored for that slot
+// after the step before (`future`), so that a step can be launched before the host has seen it.
 template <typename T, int VEC>
-__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                             int hidden, int vocab) {
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ future,
+                             float* __restrict__ out, int hidden, int vocab) {
     pdl_enter_small();
     const int n = blockIdx.x;
     int id = ids[n];
-    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host has checked the range
+    if (id < 0 && future != nullptr) id = future[-id - 1];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host has checked the range of what it knew
     const T* src = table + (size_t)id * hidden;
     float* dst = out + (size_t)n * hidden;
     if (VEC == 4) {
@@ -110,6 +113,17 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     } else {
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
     }
+}
+
+// future[slot of row i] = tokens[i]: row i of the step's logits belongs to token logit_rows[i], that
+// token to request token_req[.], that request to slot slots[.].
+__global__ void scatter_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ logit_rows,
+                                      const int* __restrict__ token_req, const int* __restrict__ slots,
+                                      int* __restrict__ future, int n, int max_slots) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int slot = slots[token_req[logit_rows[i]]];
+    if (slot >= 0 && slot < max_slots) future[slot] = tokens[i];
 }
 
 // ---------------------------------------------------------------------------- add + RMSNorm
@@ -463,19 +477,28 @@ static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 LILY_API const char* lily_last_error() { return g_error; }
 
-LILY_API int lily_embed(const void* table, int table_dtype, const int* ids, float* out, int tokens, int hidden,
-                        int vocab, cudaStream_t stream) {
+LILY_API int lily_embed(const void* table, int table_dtype, const int* ids, const int* future, float* out, int tokens,
+                        int hidden, int vocab, cudaStream_t stream) {
     if (tokens == 0) return 0;
     LILY_REQUIRE(hidden > 0 && vocab > 0, "embed: bad sizes hidden=%d vocab=%d", hidden, vocab);
     const bool vec = hidden % 4 == 0 && aligned16(table) && aligned16(out);
     if (table_dtype == kBF16) {
-        if (vec) launch_pdl(embed_kernel<__nv_bfloat16, 4>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
-        else launch_pdl(embed_kernel<__nv_bfloat16, 1>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
+        if (vec) launch_pdl(embed_kernel<__nv_bfloat16, 4>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, future, out, hidden, vocab);
+        else launch_pdl(embed_kernel<__nv_bfloat16, 1>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, future, out, hidden, vocab);
     } else {
-        if (vec) launch_pdl(embed_kernel<float, 4>, dim3(tokens), dim3(256), 0, stream, (const float*)table, ids, out, hidden, vocab);
-        else launch_pdl(embed_kernel<float, 1>, dim3(tokens), dim3(256), 0, stream, (const float*)table, ids, out, hidden, vocab);
+        if (vec) launch_pdl(embed_kernel<float, 4>, dim3(tokens), dim3(256), 0, stream, (const float*)table, ids, future, out, hidden, vocab);
+        else launch_pdl(embed_kernel<float, 1>, dim3(tokens), dim3(256), 0, stream, (const float*)table, ids, future, out, hidden, vocab);
     }
     LILY_CHECK_LAUNCH("embed");
+    return 0;
+}
+
+LILY_API int lily_scatter_tokens(const int* tokens, const int* logit_rows, const int* token_req, const int* slots,
+                                 int* future, int n, int max_slots, cudaStream_t stream) {
+    if (n == 0) return 0;
+    LILY_REQUIRE(n > 0 && max_slots > 0, "scatter_tokens: n=%d max_slots=%d", n, max_slots);
+    scatter_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, logit_rows, token_req, slots, future, n, max_slots);
+    LILY_CHECK_LAUNCH("scatter_tokens");
     return 0;
 }
 

@@ -21,7 +21,8 @@ _F32, _BF16 = 0, 1
 _vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
 
 _SIGNATURES = {
-    "lily_embed": [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
+    "lily_embed": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "lily_scatter_tokens": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _sz, _vp],
     "lily_silu_mul": [_vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _vp],
     "lily_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
@@ -120,14 +121,30 @@ def _stream():
 
 # ------------------------------------------------------------------------------ elementwise
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Rows of ``table`` [vocab, hidden] at ``ids`` [tokens] as float32 (the residual stream)."""
-    _dev(table, ids, out)
+def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None,
+          future: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows of ``table`` [vocab, hidden] at ``ids`` [tokens] as float32 (the residual stream).  With
+    ``future`` (int32, one entry per request slot) an id ``-(slot + 1)`` stands for the token that
+    ``scatter_tokens`` stored for that slot."""
+    _dev(table, ids, out, future)
     n, (vocab, hidden) = ids.numel(), table.shape
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
-    _call("lily_embed", _p(table), _dt(table), _i32(ids, "ids"), _p(out), n, hidden, vocab, _stream())
+    _call("lily_embed", _p(table), _dt(table), _i32(ids, "ids"), _i32(future, "future") if future is not None else None,
+          _p(out), n, hidden, vocab, _stream())
     return out
+
+
+def scatter_tokens(tokens: torch.Tensor, logit_rows: torch.Tensor, token_req: torch.Tensor, slots: torch.Tensor,
+                   future: torch.Tensor) -> None:
+    """``future[slots[token_req[logit_rows[i]]]] = tokens[i]``: each sampled token goes to the entry
+    of its request's slot, where the next step's ``embed`` finds it."""
+    _dev(tokens, logit_rows, token_req, slots, future)
+    n = tokens.numel()
+    if logit_rows.numel() < n:
+        raise KernelError(f"scatter_tokens: {n} tokens for {logit_rows.numel()} logit rows")
+    _call("lily_scatter_tokens", _i32(tokens, "tokens"), _i32(logit_rows, "logit_rows"), _i32(token_req, "token_req"),
+          _i32(slots, "slots"), _i32(future, "future"), n, future.numel(), _stream())
 
 
 def _summed(t: torch.Tensor, rows: int, cols: int, what: str):

@@ -21,13 +21,27 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 
+# As the only token of an entry: the token sampled for this request by the step before, which the
+# host may not have seen yet.  It travels as -(slot + 1) and the embedding kernel looks it up in the
+# runner's table of future tokens (lily/scheduler/scheduler.py:194-216,488-492 of the reference
+# keeps such a table by request slot for its overlap schedule).
+FUTURE = -1
+
+
 @dataclass
 class StepEntry:
     """One request's share of a step."""
 
     slot: int                      # the request's slot in the cache manager
-    tokens: Sequence[int]          # its next tokens
+    tokens: Sequence[int]          # its next tokens (or [FUTURE])
     want: Sequence[int] = ()       # places among these tokens whose logits are asked for
+
+    @property
+    def wire_tokens(self) -> List[int]:
+        """The token ids as the device reads them."""
+        if len(self.tokens) == 1 and int(self.tokens[0]) == FUTURE:
+            return [-(int(self.slot) + 1)]
+        return [int(t) for t in self.tokens]
 
 
 class Workspace:
@@ -70,6 +84,7 @@ class StepBatch:
     max_seq_len: int
     decode_splits: int
     workspace: Optional[Workspace] = None
+    future_tokens: Optional[torch.Tensor] = None     # int32 [request slots]: what negative token ids stand for
     _tiles: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
 
     @property
@@ -167,7 +182,7 @@ def build_step_batch(entries: Sequence[StepEntry], prefix_lens: Sequence[int],
     host = pinned[:total] if pinned is not None and pinned.numel() >= total else torch.empty(total, dtype=torch.int32)
     flat: List[int] = []
     for e in entries:
-        flat.extend(int(t) for t in e.tokens)
+        flat.extend(e.wire_tokens)
     for p, ln in zip(prefix_lens, new_lens):
         flat.extend(range(p, p + ln))
     for i, ln in enumerate(new_lens):

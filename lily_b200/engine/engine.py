@@ -78,7 +78,8 @@ class Engine:
         a = self.server_args
         return Scheduler(self.runner, max_prefill_tokens=a.max_prefill_tokens,
                          chunked_prefill_size=a.chunked_prefill_size, max_running_requests=a.max_running_requests,
-                         eos_token_ids=self.eos_token_ids, random_seed=a.random_seed)
+                         eos_token_ids=self.eos_token_ids, random_seed=a.random_seed,
+                         overlap=not a.disable_overlap_schedule)
 
     @torch.inference_mode()
     def generate(self, prompts: Sequence[Sequence[int]],

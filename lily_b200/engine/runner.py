@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import logging
 import time
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -24,7 +24,7 @@ from lily_b200.cache.kv_cache import KVCacheManager, OutOfPages, bytes_per_token
 from lily_b200.config.model_config import read_model_dir
 from lily_b200.config.registry import resolve_architecture
 from lily_b200.config.server_args import ServerArgs
-from lily_b200.engine.batch import (StepBatch, StepEntry, Workspace, build_step_batch, choose_decode_splits,
+from lily_b200.engine.batch import (FUTURE, StepBatch, StepEntry, Workspace, build_step_batch, choose_decode_splits,
                                     order_entries)
 from lily_b200.models.assembled import AssembledModel
 from lily_b200.parts.base import BuildContext, ModelSpec
@@ -82,8 +82,9 @@ class _DecodeGraph:
             cu_seqlens=parts[3], prefix_lens=parts[4], seq_lens=parts[5], slots=parts[6], logit_rows=parts[7],
             block_tables=[parts[8 + i].view(b, w) for i, w in enumerate(self.widths)],
             h_new_lens=[1] * b, h_prefix_lens=[0] * b, h_slots=[0] * b, max_seq_len=runner.context_len,
-            decode_splits=splits, workspace=Workspace(runner.device))   # scratch of its own: the graph holds its address
-        self.fill([], [], [[] for _ in self.widths])
+            decode_splits=splits, workspace=Workspace(runner.device),   # scratch of its own: the graph holds its address
+            future_tokens=runner.future_tokens)
+        self.fill([], [], [[] for _ in self.widths], [])
         self.static.copy_(self.host)
         stream = torch.cuda.Stream(device=runner.device)
         stream.wait_stream(torch.cuda.current_stream())
@@ -100,7 +101,7 @@ class _DecodeGraph:
         self.kernels = (counter["count"] - before) if counter else 0     # this package's kernels in one replay
         self._counter = counter
 
-    def fill(self, tokens: Sequence[int], prefix: Sequence[int], tables) -> None:
+    def fill(self, tokens: Sequence[int], prefix: Sequence[int], tables, slots: Sequence[int]) -> None:
         """Writes a decode batch (padded to the bucket) into the pinned host copy."""
         b, n = self.bucket, len(tokens)
         pad = b - n
@@ -110,7 +111,7 @@ class _DecodeGraph:
         flat += list(range(b + 1))                            # cu_seqlens
         flat += list(prefix) + [0] * pad                      # prefix_lens
         flat += [p + 1 for p in prefix] + [1] * pad           # seq_lens
-        flat += [0] * b                                       # slots are not read by graph-safe mixers
+        flat += list(slots) + [0] * pad                       # slots: read when sampled tokens are stored by slot
         flat += list(range(b))                                # logit rows
         for g, w in zip(tables, self.widths):
             for t in g:
@@ -120,8 +121,8 @@ class _DecodeGraph:
             self.copied.synchronize()
         self.host.copy_(torch.tensor(flat, dtype=torch.int32))
 
-    def run(self, tokens, prefix, tables) -> torch.Tensor:
-        self.fill(tokens, prefix, tables)
+    def run(self, tokens, prefix, tables, slots) -> torch.Tensor:
+        self.fill(tokens, prefix, tables, slots)
         self.static.copy_(self.host, non_blocking=True)
         self.copied = torch.cuda.Event()
         self.copied.record()
@@ -176,6 +177,10 @@ class ModelRunner:
         logger.info("KV cache: %d pages of %d tokens (%.2f GB), %d request slots", pages, self.page_size,
                     pages * self.page_size * bytes_per_token(groups, self.dtype) / 1e9, self.max_requests)
         self.workspace = Workspace(self.device)
+        # the last token sampled for each request slot, on the device: a step may name it (FUTURE)
+        # instead of a token id that the host has not read yet
+        self.future_tokens = torch.zeros(self.max_requests + 1, dtype=torch.int32, device=self.device)
+        self._last_rows: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None
         self.seq_lens: Dict[int, int] = {}
         self._ring = _PinnedRing() if self.device.type == "cuda" else None
         self._kv_heads = max((need.kv_heads for need, _ in groups), default=1)
@@ -242,7 +247,7 @@ class ModelRunner:
             seen.add(e.slot)
             if len(e.tokens) == 0:
                 raise ValueError("an entry brings at least one token")
-            if any(not (0 <= int(t) < vocab) for t in e.tokens):
+            if not (len(e.tokens) == 1 and int(e.tokens[0]) == FUTURE) and any(not (0 <= int(t) < vocab) for t in e.tokens):
                 raise ValueError(f"token id outside [0, {vocab})")
             if self.seq_lens[e.slot] + len(e.tokens) > self.context_len:
                 raise ValueError(f"request would reach {self.seq_lens[e.slot] + len(e.tokens)} positions; "
@@ -274,7 +279,17 @@ class ModelRunner:
                                  workspace=self.workspace, pinned=pinned, logit_rows=rows)
         if self._ring is not None:
             self._ring.mark(ring_index)
+        batch.future_tokens = self.future_tokens
         return batch
+
+    def store_future(self, tokens: torch.Tensor) -> None:
+        """``tokens`` (int32, on the device) are what was sampled from the logits of the last step, row
+        by row: each goes to its request's entry of ``future_tokens``, where a later step that names
+        FUTURE for that request finds it."""
+        if self._last_rows is None:
+            raise RuntimeError("no step has run")
+        rows, token_req, slots = self._last_rows
+        self.model.ctx.ops.scatter_tokens(tokens, rows, token_req, slots, self.future_tokens)
 
     def _graph_bucket(self, entries: Sequence[StepEntry]) -> Optional[int]:
         if not self.use_graphs or len(entries) > self.graph_buckets[-1]:
@@ -290,7 +305,7 @@ class ModelRunner:
         for e in entries:
             if e.slot not in self.seq_lens:
                 raise KeyError(f"request slot {e.slot} is not open")
-            if not (0 <= int(e.tokens[0]) < vocab):
+            if int(e.tokens[0]) != FUTURE and not (0 <= int(e.tokens[0]) < vocab):
                 raise ValueError(f"token id outside [0, {vocab})")
             if self.seq_lens[e.slot] + 1 > self.context_len:
                 raise ValueError(f"request would pass the context length {self.context_len}")
@@ -306,7 +321,9 @@ class ModelRunner:
             graph = self._graphs[bucket] = _DecodeGraph(self, bucket)
         tables = [[self.cache.block_table(g, e.slot) for e in entries] for g in range(len(self.cache.groups))]
         self.graph_steps += 1
-        return graph.run([int(e.tokens[0]) for e in entries], [self.seq_lens[e.slot] for e in entries], tables)
+        self._last_rows = (graph.batch.logit_rows, graph.batch.token_req, graph.batch.slots)
+        return graph.run([e.wire_tokens[0] for e in entries], [self.seq_lens[e.slot] for e in entries], tables,
+                         [e.slot for e in entries])
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one step and returns float32 logits ``[sum(len(e.want)), vocab]`` on the device.
@@ -318,6 +335,7 @@ class ModelRunner:
             batch = None
         else:
             batch = self.prepare(entries)
+            self._last_rows = (batch.logit_rows, batch.token_req, batch.slots)
             with torch.no_grad():
                 logits = self.model.forward(batch, self.cache)
         for e in entries:

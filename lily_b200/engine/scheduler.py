@@ -18,6 +18,17 @@ Each ``step()``:
    context; a finished request gives back its pages and slot (lily/scheduler/schedule_batch.py:
    88-97, scheduler.py:629-650).
 
+With ``overlap`` the host does not wait for a step's tokens before it launches the next one
+(lily/scheduler/scheduler.py:463-551 does the same): a running request whose last token is still
+on the device brings ``FUTURE`` instead of a token id, the sampler's kernels leave each token in
+the runner's table by request slot where the next step's embedding finds it, and the host reads
+the tokens of step N (an asynchronous copy and an event) after it has queued step N + 1.  A request
+that is known to end with the token in flight (``max_new_tokens``, the context limit) is left out
+of the next step; one that turns out to have ended (a stop token) has the extra token dropped when
+it arrives.  What it held is given back at once: the device runs the steps in order, so whoever
+gets the pages next writes them after the step in flight has.  Steps that need the tokens on the
+host first are not overlapped: sampling with penalties, and a step that has to retract.
+
 When pages run out: decode retracts as above; a waiting request simply waits; a request that
 could never fit (prompt beyond the context or beyond the whole pool) is refused when it is added
 (``{"type": "abort"}``), and a lone running request that cannot grow even with the pool to itself
@@ -32,9 +43,9 @@ from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Optional, Sequence
 
 from lily_b200.cache.pages import pages_for
-from lily_b200.engine.batch import StepEntry
+from lily_b200.engine.batch import FUTURE, StepEntry
 from lily_b200.sampling.params import SamplingParams
-from lily_b200.sampling.sampler import SampleRow, Sampler
+from lily_b200.sampling.sampler import Sampled, SampleRow, Sampler
 
 logger = logging.getLogger(__name__)
 
@@ -54,6 +65,7 @@ class Req:
     is_chunked: bool = False
     finished_reason: Optional[dict] = None
     retractions: int = 0
+    pending: int = 0                    # tokens sampled for it that the host has not read yet
 
     @property
     def fill_ids(self) -> List[int]:
@@ -62,6 +74,12 @@ class Req:
     @property
     def finished(self) -> bool:
         return self.finished_reason is not None
+
+    def ends_with_pending(self, context_len: int) -> bool:
+        """Whether the tokens in flight are known to be its last (length or context limit)."""
+        n = len(self.output_ids) + self.pending
+        return self.pending > 0 and (n >= self.sampling_params.max_new_tokens
+                                     or len(self.origin_input_ids) + n >= context_len)
 
     def check_finished(self, context_len: int) -> Optional[dict]:
         """lily/scheduler/schedule_batch.py:88-97, plus the context limit."""
@@ -79,6 +97,14 @@ class Req:
 
 
 @dataclass
+class _Launched:
+    """A step whose sampled tokens are still on the device."""
+
+    sampled: List[Req]
+    result: Sampled
+
+
+@dataclass
 class SchedulerOutput:
     rid: str
     output_ids: List[int]
@@ -92,7 +118,7 @@ class SchedulerOutput:
 class Scheduler:
     def __init__(self, runner: Any, *, max_prefill_tokens: int = 16384, chunked_prefill_size: int = 8192,
                  max_running_requests: Optional[int] = None, eos_token_ids: Sequence[int] = (),
-                 random_seed: Optional[int] = None, sampler: Optional[Sampler] = None):
+                 random_seed: Optional[int] = None, sampler: Optional[Sampler] = None, overlap: bool = False):
         self.runner = runner
         self.max_prefill_tokens = max_prefill_tokens
         self.chunked_prefill_size = chunked_prefill_size
@@ -109,6 +135,11 @@ class Scheduler:
         self.decode_steps = 0
         self.retractions = 0
         self.last_batch: Dict[str, int] = {}
+        self.overlap = bool(overlap) and hasattr(runner, "store_future")
+        self.overlapped_steps = 0
+        self._inflight: Optional[_Launched] = None
+        self._pinned: List[Any] = []
+        self._pinned_turn = 0
 
     # ---- intake --------------------------------------------------------------------
 
@@ -149,7 +180,7 @@ class Scheduler:
                     self._publish(req)
 
     def has_work(self) -> bool:
-        return bool(self.waiting_queue or self.running)
+        return bool(self.waiting_queue or self.running or self._inflight is not None)
 
     # ---- bookkeeping ---------------------------------------------------------------
 
@@ -180,11 +211,17 @@ class Scheduler:
         cache = self.runner.cache
         return sum(cache.pages_needed(r.slot, r.seq_len + 1) for r in reqs)
 
+    def _decode_candidates(self) -> List[Req]:
+        """Running requests that take another step: all but those whose token in flight is their last."""
+        ctx = self.runner.context_len
+        return [r for r in self.running if not r.ends_with_pending(ctx)]
+
     def _plan_decode(self) -> List[Req]:
         """Running requests that decode this step, after retracting the youngest while the pool
-        cannot give every one of them its next position."""
+        cannot give every one of them its next position.  (Nothing is in flight when it retracts:
+        ``step`` reads the tokens first when the pages are short.)"""
         cache = self.runner.cache
-        while self.running and self._decode_pages(self.running) > cache.free_pages():
+        while self.running and self._decode_pages(self._decode_candidates()) > cache.free_pages():
             if len(self.running) == 1:
                 req = self.running.pop()
                 self._release(req)
@@ -192,7 +229,7 @@ class Scheduler:
                 self._publish(req)
                 break
             self._retract(self.running.pop())
-        return list(self.running)
+        return self._decode_candidates()
 
     def _plan_prefill(self, decoding: Sequence[Req]) -> List[Req]:
         cache = self.runner.cache
@@ -223,11 +260,25 @@ class Scheduler:
 
     # ---- one step ------------------------------------------------------------------
 
+    def _next_needs_host_tokens(self) -> bool:
+        """With a step in flight: whether the next one has to wait for its tokens (penalties read
+        the history; a retraction re-queues prompt + produced tokens)."""
+        candidates = self._decode_candidates()
+        if any(not r.sampling_params.plain for r in candidates):
+            return True
+        return self._decode_pages(candidates) > self.runner.cache.free_pages()
+
     def step(self) -> bool:
         """Runs one batch.  Returns False when there was nothing to run."""
-        decoding = self._plan_decode()
-        prefilling = self._plan_prefill(decoding)
-        if not decoding and not prefilling:
+        if self._inflight is not None and self._next_needs_host_tokens():
+            self._collect(self._take_inflight())
+        launched = self._launch()
+        previous = self._take_inflight()
+        if previous is not None:
+            self._collect(previous)
+        if launched is None:
+            if previous is not None:
+                return True
             if self.waiting_queue and not self.running:
                 # nothing runs and the head of the queue cannot start: it never will
                 req = self.waiting_queue.pop(0)
@@ -236,9 +287,40 @@ class Scheduler:
                 self._publish(req)
                 return True
             return False
+        if self.overlap and launched.result.tokens is not None:
+            if self.runner.device.type == "cuda":
+                launched.result.start_copy(*self._pinned_pair())
+            self._inflight = launched
+            self.overlapped_steps += 1
+        else:
+            self._collect(launched)
+        return True
+
+    def _take_inflight(self) -> Optional[_Launched]:
+        launched, self._inflight = self._inflight, None
+        return launched
+
+    def _pinned_pair(self):
+        """Two pairs of pinned buffers used in turn: a pair is read by ``_collect`` before the launch
+        after the next takes it again."""
+        if not self._pinned:
+            import torch
+            n = self.runner.max_requests + 1
+            self._pinned = [(torch.zeros(n, dtype=torch.int32, pin_memory=True),
+                             torch.zeros(n, dtype=torch.float32, pin_memory=True)) for _ in range(2)]
+        self._pinned_turn ^= 1
+        return self._pinned[self._pinned_turn]
+
+    def _launch(self) -> Optional[_Launched]:
+        """Plans a batch, queues it and its sampling on the device, and moves the requests on as if
+        every sampled token were an ordinary one; ``_collect`` corrects that when it reads them."""
+        decoding = self._plan_decode()
+        prefilling = self._plan_prefill(decoding)
+        if not decoding and not prefilling:
+            return None
         entries: List[StepEntry] = []
         for req in decoding:
-            entries.append(StepEntry(req.slot, [req.output_ids[-1]], [0]))
+            entries.append(StepEntry(req.slot, [FUTURE if req.pending else req.output_ids[-1]], [0]))
         for req in prefilling:
             if req.slot is None:
                 req.slot = self.runner.open_request()
@@ -252,17 +334,34 @@ class Scheduler:
         self.prefill_tokens_computed += self.last_batch["prefill_tokens"]
 
         sampled = [r for r in decoding] + [r for r in prefilling if not r.is_chunked]
-        rows = [SampleRow(r.sampling_params, r.seed, len(r.output_ids),
+        rows = [SampleRow(r.sampling_params, r.seed, len(r.output_ids) + r.pending,
                           r.fill_ids if not r.sampling_params.plain else ()) for r in sampled]
-        tokens, logprobs = self.sampler(logits, rows)
+        result = self.sampler.launch(logits, rows)
+        if self.overlap and result.tokens is not None:
+            self.runner.store_future(result.tokens)
 
         for req in decoding:
             req.seq_len += 1
+        requeue: List[Req] = []
         for req in prefilling:
             req.seq_len += req.extend_input_len
-        still_running: List[Req] = []
-        requeue: List[Req] = []
-        for i, req in enumerate(sampled):
+            if req.is_chunked:
+                req.is_chunked = False
+                requeue.append(req)
+            else:
+                self.running.append(req)
+        for req in sampled:
+            req.pending += 1
+        self.waiting_queue[:0] = requeue
+        return _Launched(sampled, result)
+
+    def _collect(self, launched: _Launched) -> None:
+        """Reads the tokens of a launched step and lets each request take its own."""
+        tokens, logprobs = launched.result.read()
+        for i, req in enumerate(launched.sampled):
+            req.pending -= 1
+            if req.finished:
+                continue                   # it ended a step ago (or was aborted): this token is one too many
             req.output_ids.append(int(tokens[i]))
             if req.output_logprobs is not None and logprobs is not None:
                 req.output_logprobs.append(float(logprobs[i]))
@@ -271,15 +370,8 @@ class Scheduler:
             if req.check_finished(self.runner.context_len):
                 self._release(req)
                 self._publish(req)
-            else:
-                still_running.append(req)
-        for req in prefilling:
-            if req.is_chunked:
-                req.is_chunked = False
-                requeue.append(req)
-        self.waiting_queue[:0] = requeue
-        self.running = still_running
-        return True
+                if req in self.running:
+                    self.running.remove(req)
 
     def run_to_completion(self, max_steps: int = 1 << 30) -> None:
         steps = 0

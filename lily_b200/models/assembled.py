@@ -118,7 +118,8 @@ class AssembledModel:
         """Runs the batch's tokens through the schedule and returns float32 logits
         ``[len(batch.logit_rows), vocab]``."""
         ops = self.ctx.ops
-        residual = ops.embed(self.embed, batch.token_ids)
+        future = getattr(batch, "future_tokens", None)
+        residual = ops.embed(self.embed, batch.token_ids) if future is None else ops.embed(self.embed, batch.token_ids, future=future)
         delta = None
         for pos, entry in enumerate(self.spec.schedule):
             ec, es = self.entry_cache[pos], self.entry_state[pos]

@@ -40,22 +40,56 @@ class SampleRow:
     seen: Sequence[int] = ()           # prompt + produced tokens (for the penalties)
 
 
+@dataclass
+class Sampled:
+    """What one call of the sampler left on the device, and how it reaches the host."""
+
+    tokens: Optional[torch.Tensor]                 # int32 [rows] on the device
+    logprobs: Optional[torch.Tensor] = None        # float32 [rows] on the device
+    host_tokens: Optional[torch.Tensor] = None     # where an asynchronous copy puts them
+    host_logprobs: Optional[torch.Tensor] = None
+    copied: Any = None                             # event after the copies
+
+    def start_copy(self, pinned_tokens: torch.Tensor, pinned_logprobs: Optional[torch.Tensor] = None) -> None:
+        """Starts the copy to pinned host memory behind the sampling kernels and records an event,
+        so that the host can read the tokens later without waiting for work queued after them."""
+        n = self.tokens.numel()
+        self.host_tokens = pinned_tokens[:n]
+        self.host_tokens.copy_(self.tokens, non_blocking=True)
+        if self.logprobs is not None and pinned_logprobs is not None:
+            self.host_logprobs = pinned_logprobs[:n]
+            self.host_logprobs.copy_(self.logprobs, non_blocking=True)
+        self.copied = torch.cuda.Event()
+        self.copied.record()
+
+    def read(self) -> Tuple[List[int], Optional[List[float]]]:
+        if self.tokens is None:
+            return [], None
+        if self.copied is not None:
+            self.copied.synchronize()
+            return (self.host_tokens.tolist(),
+                    self.host_logprobs.tolist() if self.host_logprobs is not None else
+                    (self.logprobs.tolist() if self.logprobs is not None else None))
+        return self.tokens.tolist(), (self.logprobs.tolist() if self.logprobs is not None else None)
+
+
 class Sampler:
     def __init__(self, ops: Any, device):
         self.ops, self.device = ops, device
 
-    def __call__(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> Tuple[List[int], Optional[List[float]]]:
+    def launch(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> Sampled:
         """``logits`` float32 [len(rows), vocab] on the device (modified in place by penalties).
-        Returns the tokens and, when any row asks for them, the chosen tokens' log-probabilities."""
+        Queues the sampling kernels and returns the tokens (and, when any row asks for them, the
+        chosen tokens' log-probabilities) as device tensors."""
         if len(rows) == 0:
-            return [], None
+            return Sampled(None)
         assert logits.shape[0] == len(rows), (logits.shape, len(rows))
         ops, dev = self.ops, self.device
         if any(not r.params.plain for r in rows):
             self._penalties(logits, rows)
         need_lp = any(r.params.logprobs for r in rows)
         if all(r.params.greedy for r in rows) and not need_lp:
-            return ops.argmax(logits).tolist(), None
+            return Sampled(ops.argmax(logits))
         f32 = dict(dtype=torch.float32, device=dev)
         temperature = torch.tensor([0.0 if r.params.greedy else r.params.temperature for r in rows], **f32)
         top_k = torch.tensor([r.params.top_k for r in rows], dtype=torch.int32, device=dev)
@@ -63,7 +97,11 @@ class Sampler:
         min_p = torch.tensor([r.params.min_p for r in rows], **f32)
         uniform = torch.tensor([uniform_for(r.seed, r.index) for r in rows], **f32)
         tokens, logprobs = ops.sample(logits, temperature, top_k, top_p, min_p, uniform, want_logprob=need_lp)
-        return tokens.tolist(), (logprobs.tolist() if logprobs is not None else None)
+        return Sampled(tokens, logprobs)
+
+    def __call__(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> Tuple[List[int], Optional[List[float]]]:
+        """``launch`` and read the result at once."""
+        return self.launch(logits, rows).read()
 
     def _penalties(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> None:
         e_row: List[int] = []

@@ -17,8 +17,16 @@ def library():
     return None
 
 
-def embed(table, ids, out=None):
-    return table[ids.long()].float()
+def embed(table, ids, out=None, future=None):
+    ids = ids.long()
+    if future is not None:
+        ids = torch.where(ids < 0, future.long()[(-ids - 1).clamp(min=0)], ids)
+    return table[ids].float()
+
+
+def scatter_tokens(tokens, logit_rows, token_req, slots, future):
+    n = tokens.numel()
+    future[slots.long()[token_req.long()[logit_rows.long()[:n]]]] = tokens.to(future.dtype)
 
 
 def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_residual=True, out=None):

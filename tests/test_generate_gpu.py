@@ -96,6 +96,33 @@ def test_temperature_generation_follows_the_plain_sampler():
                 ids.append(tok)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlap_schedule_on_the_gpu_changes_no_token(dtype):
+    """Steps launched before the tokens of the step before are read (graphs, the table of future
+    tokens on the device, asynchronous copies) give the tokens of steps that read first."""
+    cfg = tiny_models.TINY_LLAMA
+    from lily_b200 import SamplingParams
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 65, tmp)
+        prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], 120 + i) for i, n in enumerate([3, 17, 50, 100, 200])]
+        params = [SamplingParams(max_new_tokens=20 + i, temperature=0.9, seed=7 + i, ignore_eos=True) for i in range(5)]
+        plain = engine(path, dtype, page_size=16, chunked_prefill_size=128, disable_overlap_schedule=True)
+        first = plain.generate(prompts, params)
+        assert plain.last_scheduler.overlapped_steps == 0
+        # a token that appears in the middle of a run, to stop on: the extra token in flight is dropped
+        run = first[2]["output_ids"]
+        k = next(i for i in range(3, len(run)) if run[i] not in run[:i])
+        params[2] = SamplingParams(max_new_tokens=22, temperature=0.9, seed=9, stop_token_ids=[run[k]])
+        want = plain.generate(prompts, params)
+        assert want[2]["output_ids"] == run[:k + 1] and want[2]["finish_reason"]["type"] == "stop"
+        eng = engine(path, dtype, page_size=16, chunked_prefill_size=128)
+        got = eng.generate(prompts, params)
+        assert [g["output_ids"] for g in got] == [w["output_ids"] for w in want]
+        assert [g["finish_reason"] for g in got] == [w["finish_reason"] for w in want]
+        assert eng.last_scheduler.overlapped_steps > 15 and eng.runner.graph_steps > 15
+        assert eng.kv_available() == 2048
+
+
 def test_small_pool_retracts_on_the_gpu():
     cfg = tiny_models.TINY_QWEN3
     from lily_b200 import SamplingParams

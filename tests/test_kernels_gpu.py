@@ -30,6 +30,25 @@ def test_embed(dtype, hidden, vocab):
     table = torch.randn(vocab, hidden, device=DEV, generator=g).to(dtype)
     ids = torch.randint(0, vocab, (37,), device=DEV, generator=g, dtype=torch.int32)
     assert torch.equal(ops().embed(table, ids), ref.embed(table, ids))
+    # ids below zero name request slots whose token the sampler left on the device
+    future = torch.randint(0, vocab, (9,), device=DEV, generator=g, dtype=torch.int32)
+    mixed = ids.clone()
+    mixed[::3] = -(torch.arange(0, 13, device=DEV, dtype=torch.int32) % 9 + 1)
+    assert torch.equal(ops().embed(table, mixed, future=future), ref.embed(table, mixed, future=future))
+    assert torch.equal(ops().embed(table, mixed, future=future)[0], table[future[0].long()].float())
+
+
+def test_scatter_tokens():
+    g = torch.Generator(device=DEV).manual_seed(17)
+    tokens = torch.randint(0, 1000, (5,), device=DEV, generator=g, dtype=torch.int32)
+    logit_rows = torch.tensor([0, 1, 2, 9, 30], device=DEV, dtype=torch.int32)        # three decode tokens, two portions' ends
+    token_req = torch.tensor([0, 1, 2] + [3] * 7 + [4] * 21, device=DEV, dtype=torch.int32)
+    slots = torch.tensor([4, 1, 7, 2, 5], device=DEV, dtype=torch.int32)
+    a = torch.full((9,), -5, device=DEV, dtype=torch.int32)
+    b = a.clone()
+    ops().scatter_tokens(tokens, logit_rows, token_req, slots, a)
+    ref.scatter_tokens(tokens, logit_rows, token_req, slots, b)
+    assert torch.equal(a, b) and a[4] == tokens[0] and a[5] == tokens[4] and a[0] == -5
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -166,6 +166,61 @@ def test_temperature_seeds(setup):
         ids.append(tok)
 
 
+def test_overlap_schedule_changes_no_output(setup):
+    """Launching a step before the tokens of the one before are read: same tokens, finish reasons
+    and bookkeeping as reading them first, through mixed batches, chunked prompts, stop tokens
+    (whose extra token in flight is dropped), length limits (known ahead: no extra step), abort,
+    temperature with seeds and log-probabilities, penalties and retraction (both fall back to
+    reading first)."""
+    cfg, weights, path = setup
+    ps = prompts(cfg, [1, 7, 33, 64, 150, 20], seed=60)
+    # a seeded random run (greedy runs of this tiny model repeat one token) and a token that first
+    # appears in the middle of it, to stop on
+    drawn = dict(temperature=1.0, seed=11)
+    free_run = run(scheduler(path), [ps[2]], 14, **drawn)[0]
+    k = next(i for i in range(3, 14) if free_run[i] not in free_run[:i])
+
+    def scenario(overlap, **kw):
+        s = scheduler(path, overlap=overlap, chunked_prefill_size=64, eos_token_ids=[free_run[k]], **kw)
+        s.add_request("plain", ps[0], SamplingParams(max_new_tokens=9, ignore_eos=True))
+        s.add_request("one", ps[1], SamplingParams(max_new_tokens=1, ignore_eos=True))
+        s.add_request("eos", ps[2], SamplingParams(max_new_tokens=14, **drawn))
+        s.add_request("stop", ps[2], SamplingParams(max_new_tokens=14, stop_token_ids=[free_run[k - 1]], **drawn))
+        s.add_request("temp", ps[3], SamplingParams(max_new_tokens=11, temperature=0.8, top_p=0.9, seed=5, logprobs=True,
+                                                    ignore_eos=True))
+        s.add_request("long", ps[4], SamplingParams(max_new_tokens=6, ignore_eos=True))
+        for _ in range(3):
+            s.step()
+        s.add_request("late", ps[5], SamplingParams(max_new_tokens=12, ignore_eos=True))
+        s.add_request("gone", ps[5], SamplingParams(max_new_tokens=30, ignore_eos=True))
+        for _ in range(3):
+            s.step()
+        s.abort_request("gone")
+        s.add_request("pen", ps[1], SamplingParams(max_new_tokens=8, repetition_penalty=1.3, ignore_eos=True))
+        s.run_to_completion()
+        assert not s.has_work() and s.runner.cache.held_pages() == [0] and s.runner.cache.slots.available == 8
+        return s
+
+    a, b = scenario(False), scenario(True)
+    assert b.overlapped_steps > 10 and a.overlapped_steps == 0
+    for rid in ("plain", "one", "eos", "stop", "temp", "long", "late", "pen"):
+        ra, rb = a.results[rid], b.results[rid]
+        assert ra.output_ids == rb.output_ids and ra.finish_reason == rb.finish_reason, rid
+    assert a.results["temp"].logprobs == pytest.approx(b.results["temp"].logprobs)
+    assert b.results["eos"].output_ids == free_run[:k + 1] and b.results["eos"].finish_reason["type"] == "stop"
+    assert b.results["stop"].output_ids == free_run[:free_run.index(free_run[k - 1]) + 1]
+    assert b.results["gone"].finish_reason["type"] == "abort"
+    assert b.results["plain"].output_ids == plain_impl.greedy_generate(cfg, weights, ps[0], 9)
+    # only the requests that ended on a stop token (and the aborted one) got a step beyond their last token
+    assert a.decode_steps <= b.decode_steps <= a.decode_steps + 3
+    # retraction under overlap: tokens are read first whenever the pool runs short
+    ps2 = prompts(cfg, [20, 25, 18, 30, 22, 27, 19, 24], seed=20)
+    want = [plain_impl.greedy_generate(cfg, weights, p, 12) for p in ps2]
+    s = scheduler(path, max_tokens=13 * 16, page_size=16, overlap=True)
+    assert run(s, ps2, 12) == want and s.retractions > 0 and s.overlapped_steps > 0
+    assert s.runner.cache.held_pages() == [0] and s.runner.cache.slots.available == 8
+
+
 def test_sampling_params_checks():
     for kw in ({"max_new_tokens": 0}, {"temperature": -1}, {"top_p": 0}, {"top_k": 0}, {"min_p": 1.0},
                {"repetition_penalty": 0}, {"stop": "x"}, {"top_logprobs": 2}, {"n": 2}):
