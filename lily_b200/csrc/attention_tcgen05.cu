@@ -41,16 +41,26 @@ namespace fa {
 constexpr int BQ = 128;                   // query rows per block
 constexpr int BKV = 128;                  // keys per tile
 constexpr int D = 128;                    // head size
-constexpr int STAGES = 2;                 // K stages, V stages, P buffers, S accumulators
+// P (the second product's A operand) either goes through shared memory, or, packed as bfloat16
+// pairs, into the tensor-memory columns of the S tile it was computed from; the latter leaves
+// shared memory to K, V and Q alone (a third K/V stage fits) and spares the async-proxy fence.
+#ifdef LILY_FA_P_IN_SMEM
+constexpr bool P_TMEM = false;
+constexpr int STAGES = 2;                 // K stages, V stages
+#else
+constexpr bool P_TMEM = true;
+constexpr int STAGES = 3;
+#endif
+constexpr int SBUF = 2;                   // S accumulators (and P buffers)
 constexpr int SUB = 128 * 64 * 2;         // a [128 rows][64 elements] sub-tile with 128-byte rows: 16 KB
 constexpr int TILE = 2 * SUB;             // Q, one K stage, one V stage, one P buffer: 32 KB
 constexpr int BOX = 64 * 64 * 2;          // one TMA box of K or V: 8 KB
 constexpr int SOFTMAX_THREADS = 256;     // two threads per query row, each with half of the row's keys
 constexpr int THREADS = 64 + SOFTMAX_THREADS;
-constexpr int NUM_BARS = 1 + 7 * STAGES;
+constexpr int NUM_BARS = 1 + 4 * STAGES + 3 * SBUF;
 // shared memory, all of it dynamic and 1024-byte aligned: Q | K stages | V stages | P buffers | mbarriers |
 // tensor-memory base and abort flag | the row maxima and sums that the two threads of a row exchange
-constexpr int OFF_BARS = (1 + 3 * STAGES) * TILE;
+constexpr int OFF_BARS = (1 + 2 * STAGES + (P_TMEM ? 0 : SBUF)) * TILE;
 constexpr int OFF_MISC = OFF_BARS + 8 * NUM_BARS + 8;
 constexpr int OFF_XCH = OFF_MISC + 16;
 constexpr int SMEM = OFF_XCH + 2 * 2 * BQ * 4;
@@ -58,6 +68,17 @@ constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr float GROW_LOG2 = 8.f;          // the reference maximum moves when the true one is 2^8 ahead
 
 __device__ int g_status = 0;              // 0 ok; else (code << 24 | block) of the first wait that gave up
+
+// Built with -DLILY_FA_TIMING, block (0, 0) adds up the cycles its roles spend in each phase
+// (lily_attention_tc_timing reads them); without it the macros vanish.
+#ifdef LILY_FA_TIMING
+__device__ unsigned long long g_timing[32];
+#define FA_TIC() const long long tic__ = clock64()
+#define FA_TOC(slot, who) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (who)) g_timing[slot] += (unsigned long long)(clock64() - tic__); } while (0)
+#else
+#define FA_TIC() do {} while (0)
+#define FA_TOC(slot, who) do {} while (0)
+#endif
 
 struct Params {
     const int* block_table;
@@ -128,6 +149,12 @@ __device__ __forceinline__ void umma(uint32_t tmem_c, uint64_t desc_a, uint64_t 
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the A operand in tensor memory (128 lanes x k / 2 columns of bfloat16 pairs).
+__device__ __forceinline__ void umma_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(tmem_c), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
@@ -183,8 +210,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t k_smem = q_smem + TILE, v_smem = k_smem + STAGES * TILE, p_smem = v_smem + STAGES * TILE;
     const uint32_t q_full = smem_u32(&bars[0]);
     const uint32_t k_full = q_full + 8, k_empty = k_full + 8 * STAGES, v_full = k_empty + 8 * STAGES,
-                   v_empty = v_full + 8 * STAGES, s_full = v_empty + 8 * STAGES, p_full = s_full + 8 * STAGES,
-                   pv_done = p_full + 8 * STAGES;
+                   v_empty = v_full + 8 * STAGES, s_full = v_empty + 8 * STAGES, p_full = s_full + 8 * SBUF,
+                   pv_done = p_full + 8 * SBUF;
 
     if (threadIdx.x == 0) {
         abort_s = 0;
@@ -194,6 +221,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(k_empty + 8 * s, 1);
             mbar_init(v_full + 8 * s, 1);
             mbar_init(v_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < SBUF; ++s) {
             mbar_init(s_full + 8 * s, 1);
             mbar_init(p_full + 8 * s, SOFTMAX_THREADS); // one arrival per softmax thread
             mbar_init(pv_done + 8 * s, 1);
@@ -251,14 +280,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     page[h] = held ? table[key / p.page_size] : 0;
                     off[h] = held ? key % p.page_size : 0;
                 }
-                ok = mbar_wait(k_empty + 8 * s, par ^ 1, abort_flag, 1);
+                { FA_TIC(); ok = mbar_wait(k_empty + 8 * s, par ^ 1, abort_flag, 1); FA_TOC(0, true); }
                 if (!ok) break;
                 mbar_expect_tx(k_full + 8 * s, TILE);
                 for (int h = 0; h < 2; ++h)
                     for (int dh = 0; dh < 2; ++dh)
                         tma_load_4d(k_smem + s * TILE + dh * SUB + h * BOX, &map_kv, k_full + 8 * s, dh * 64, off[h], kvh, page[h]);
                 ++issued_k;
-                ok = mbar_wait(v_empty + 8 * s, par ^ 1, abort_flag, 2);
+                { FA_TIC(); ok = mbar_wait(v_empty + 8 * s, par ^ 1, abort_flag, 2); FA_TOC(1, true); }
                 if (!ok) break;
                 mbar_expect_tx(v_full + 8 * s, TILE);
                 for (int h = 0; h < 2; ++h)
@@ -283,7 +312,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             bool ok = mbar_wait(q_full, 0, abort_flag, 3);
             auto scores = [&](int i) {                   // S_i = Q K_i^T into accumulator i % 2
                 const int s = i % STAGES;
-                if (!mbar_wait(k_full + 8 * s, (uint32_t)((i / STAGES) & 1), abort_flag, 4)) return false;
+                {
+                    FA_TIC();
+                    const bool got = mbar_wait(k_full + 8 * s, (uint32_t)((i / STAGES) & 1), abort_flag, 4);
+                    FA_TOC(2, true);
+                    if (!got) return false;
+                }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -298,19 +332,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (ok) ok = scores(0);
             for (int j = 0; j < n && ok; ++j) {
                 const int s = j % STAGES, b = j & 1;
-                const uint32_t par = (uint32_t)((j / STAGES) & 1);
                 if (j + 1 < n) {
                     ok = scores(j + 1);
                     if (!ok) break;
                 }
-                ok = mbar_wait(p_full + 8 * b, par, abort_flag, 5) && mbar_wait(v_full + 8 * s, par, abort_flag, 6);
+                { FA_TIC(); ok = mbar_wait(p_full + 8 * b, (uint32_t)((j >> 1) & 1), abort_flag, 5); FA_TOC(4, true); }
+                if (ok) { FA_TIC(); ok = mbar_wait(v_full + 8 * s, (uint32_t)((j / STAGES) & 1), abort_flag, 6); FA_TOC(3, true); }
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; ++kk) {
-                    const uint64_t da = desc_k_major(p_smem + b * TILE + (kk >> 2) * SUB + (kk & 3) * 32);
                     const uint64_t db = desc_mn_major(v_smem + s * TILE + kk * 2048);
-                    umma(tmem_o, da, db, idesc_o, (j | kk) != 0 ? 1u : 0u);
+                    if (P_TMEM) {
+                        // A from tensor memory: 16 keys of P are 8 columns of bfloat16 pairs in S's buffer
+                        umma_ts(tmem_o, tmem + (uint32_t)(b * BKV + kk * 8), db, idesc_o, (j | kk) != 0 ? 1u : 0u);
+                    } else {
+                        const uint64_t da = desc_k_major(p_smem + b * TILE + (kk >> 2) * SUB + (kk & 3) * 32);
+                        umma(tmem_o, da, db, idesc_o, (j | kk) != 0 ? 1u : 0u);
+                    }
                 }
                 umma_commit(v_empty + 8 * s);
                 umma_commit(pv_done + 8 * b);
@@ -352,13 +391,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         };
         for (int j = 0; j < n && ok; ++j) {
             const int b = j & 1;
-            ok = mbar_wait(s_full + 8 * b, (uint32_t)((j >> 1) & 1), abort_flag, 7);
+            { FA_TIC(); ok = mbar_wait(s_full + 8 * b, (uint32_t)((j >> 1) & 1), abort_flag, 7); FA_TOC(8 + half, row == 0); }
             if (!ok) break;
+            FA_TIC();
             tc_fence_after();
             float s[HALF];
 #pragma unroll
             for (int c = 0; c < HALF / 32; ++c) tmem_ld32(tmem + lane_addr + (uint32_t)(b * BKV + half * HALF + c * 32), s + c * 32);
             tmem_wait_ld();
+            FA_TOC(10 + half, row == 0);
             const int kb = (jt0 + j) * BKV + half * HALF;
             const bool need_mask = kb + HALF - 1 > pos0 || (p.window > 0 && kb <= pos0 + BQ - 1 - p.window);
             if (need_mask) {
@@ -409,21 +450,37 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 sum4[c & 3] += s[c];
             }
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            if (j >= 2) {                                  // the product that read this P buffer last is done
-                ok = mbar_wait(pv_done + 8 * b, (uint32_t)(((j - 2) >> 1) & 1), abort_flag, 9);
-                if (!ok) break;
-            }
-            // keys [64 half, 64 half + 64) of P are the sub-tile `half`: 128-byte rows, 16-byte pieces swizzled
-            unsigned char* prow = smem + (size_t)(1 + 2 * STAGES) * TILE + (size_t)b * TILE + (size_t)half * SUB + (size_t)row * 128;
+            FA_TOC(12 + half, row == 0);
+            if (P_TMEM) {
+                // P over the first 64 columns of the S buffer it came from: this thread's 64 keys are 32
+                // columns of bfloat16 pairs.  The other thread of the row has read its scores (it posted
+                // its maximum after that), and the product that read this buffer's last P ran before the
+                // S product whose result was just read.
+                uint32_t packed[HALF / 2];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float* v = s + c * 8;
-                *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
-                    make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+                for (int c = 0; c < HALF / 2; ++c) packed[c] = pack2(s[2 * c], s[2 * c + 1]);
+                tmem_st32(tmem + lane_addr + (uint32_t)(b * BKV + half * (HALF / 2)), reinterpret_cast<const float*>(packed));
+                tmem_wait_st();
+            } else {
+                if (j >= 2) {                              // the product that read this P buffer last is done
+                    FA_TIC();
+                    ok = mbar_wait(pv_done + 8 * b, (uint32_t)(((j - 2) >> 1) & 1), abort_flag, 9);
+                    FA_TOC(14 + half, row == 0);
+                    if (!ok) break;
+                }
+                // keys [64 half, 64 half + 64) of P are the sub-tile `half`: 128-byte rows, 16-byte pieces swizzled
+                unsigned char* prow = smem + (size_t)(1 + 2 * STAGES) * TILE + (size_t)b * TILE + (size_t)half * SUB + (size_t)row * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float* v = s + c * 8;
+                    *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
+                        make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tensor cores read P through the async proxy
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // the tensor cores read P through the async proxy
             tc_fence_before();
             mbar_arrive(p_full + 8 * b);
+            FA_TOC(16 + half, row == 0);
         }
         // the two halves of a row add their sums (slots of the parity that the last tile did not use)
         if (ok) {
@@ -484,6 +541,18 @@ static EncodeTiled encoder() {
 }  // namespace lily
 
 using namespace lily;
+
+#ifdef LILY_FA_TIMING
+// Copies the 32 phase counters of block (0, 0) to `out` and clears them.  Slots: 0, 1 the loader waiting
+// for a K, V stage; 2, 3, 4 the mma thread waiting for K, V, P; for the softmax thread of row 0 with key half
+// h: 8 + h waiting for S, then measured from the start of the tile's work: 10 + h S read, 12 + h sums done,
+// 16 + h arrived on the P barrier; 14 + h the wait for the P buffer inside that.
+LILY_API int lily_attention_tc_timing(unsigned long long* out) {
+    unsigned long long zero[32] = {};
+    if (cudaMemcpyFromSymbol(out, fa::g_timing, sizeof(zero)) != cudaSuccess) return 1;
+    return cudaMemcpyToSymbol(fa::g_timing, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 LILY_API int lily_attention_prefill_tc_rows() { return fa::BQ; }
 
