@@ -69,6 +69,47 @@ def test_head_size_128_paths_inside_the_engine(dtype):
             assert ops.attention_tc_status() == 0 and ops.gemm_tc_status() == 0          # no bounded wait gave up
 
 
+def test_pages_whose_offset_passes_two_to_the_31_elements():
+    """A pool of 8.9 GB in which the request's pages lie past element 2^31 of a layer's cache (16 requests that only
+    hold pages fill the front of the pool): the same logits, bit for bit, as in a small pool, through the
+    tcgen05 and the mma.sync attention kernels, the cache write and the decode graphs.  A 32-bit offset
+    anywhere would read or write the wrong page."""
+    cfg = dict(tiny_models.MID_QWEN3, num_attention_heads=16, num_key_value_heads=8, hidden_size=512)
+    with tempfile.TemporaryDirectory() as tmp:
+        path, _ = model_dir(cfg, 34, tmp)
+        ids = tiny_models.random_tokens(700, cfg["vocab_size"], 5)
+
+        def logits_of(runner):
+            whole = run_whole(runner, ids[:600])[-3:]
+            cut = run_portions(runner, ids, [300, 130, 2, 200, 60] + [1] * 8)[-12:]
+            return torch.cat([whole, cut])
+
+        # the same context length in both, so that the decode graphs cut the keys into the same ranges
+        small = make_runner(path, dtype="bfloat16", device="cuda", page_size=64, max_tokens=4096, context_length=65536)
+        want = logits_of(small)
+        del small
+        torch.cuda.empty_cache()
+        pages = 17000
+        big = make_runner(path, dtype="bfloat16", device="cuda", page_size=64, max_tokens=pages * 64, max_requests=20,
+                          context_length=65536)
+        held = []
+        for _ in range(16):                                   # 16 x 1024 pages: the front of the pool
+            slot = big.cache.open_request()
+            big.cache.grow(slot, 65536)
+            held.append(slot)
+        probe = big.cache.open_request()
+        big.cache.grow(probe, 64)
+        first = big.cache.block_table(0, probe)[0]
+        big.cache.close_request(probe)
+        elements_per_page = 2 * cfg["num_key_value_heads"] * 64 * cfg["head_dim"]
+        assert first * elements_per_page > 2 ** 31, first
+        got = logits_of(big)
+        assert torch.equal(got, want)
+        for slot in held:
+            big.cache.close_request(slot)
+        assert big.cache.held_pages() == [0]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_whole_decode_and_portions(setup, dtype):
     cfg, weights, path = setup
