@@ -1,5 +1,6 @@
 // Sampling over float32 logits [rows, vocab]: penalties and bias, argmax, and temperature
-// sampling with top-k, top-p and min-p, one block per row, no sort.
+// sampling with top-k, top-p and min-p, one block (small vocabularies) or a cluster of eight blocks
+// per row, no sort.
 //
 // Order of operations as in lily/layers/sampler.py:1-12,64-116: (1) repetition, frequency and
 // presence penalties and the additive bias on the logits; (2) argmax for a greedy row;
@@ -14,6 +15,10 @@
 // bit pattern of x (4 passes of 8 bits); masses are summed in 2^-40 fixed point so that every
 // sum is independent of the order in which threads add.
 #include "common.cuh"
+
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace lily {
 
@@ -141,163 +146,270 @@ __global__ void penalties_kernel(float* __restrict__ logits, const int* __restri
     logits[(size_t)r * vocab + t] = v;
 }
 
-// Radix selection over ordered keys among elements with key >= floor_key.
+// ---- temperature sampling: a thread-block cluster per row -----------------------------------------
+//
+// A row of a large vocabulary is cut into CL contiguous slices, one block of the cluster each; what
+// the blocks find out about their slices (best value, histograms, masses) they leave in their own
+// shared memory, and after a cluster barrier every block reads all of them through distributed
+// shared memory and combines them in rank order, so all blocks reach the same decision without a
+// broadcast.  CL == 1 is the same code without a cluster (small vocabularies).
+
+template <int CL>
+struct RowShared {
+    ArgBest best[33];
+    float fsum[33];
+    ArgBest cbest;                      // this block's best, for the others to read
+    float csum;                         // ... its sum of exponentials (greedy log-probability)
+    unsigned long long ctotal;          // ... its mass of top-k survivors
+    unsigned cnt[2][256];               // histograms of the radix passes, double-buffered by pass
+    unsigned long long mass[2][256];
+    unsigned tcnt[256];                 // the cluster's totals of the current pass
+    unsigned long long tmass[256];
+    unsigned pick[4];
+    unsigned long long wsum[32];        // kept mass of each warp's segment
+    unsigned long long all_wsum[CL * 32];
+};
+
+template <int CL, typename T>
+__device__ __forceinline__ const T* peer(cg::cluster_group& cluster, const T* mine, int rank) {
+    if (CL == 1) return mine;
+    return cluster.map_shared_rank(const_cast<T*>(mine), rank);
+}
+template <int CL>
+__device__ __forceinline__ void cluster_barrier(cg::cluster_group& cluster) {
+    if (CL == 1) __syncthreads();
+    else cluster.sync();
+}
+
+// Radix selection over ordered keys among the row's elements with key >= floor_key.
 //   by count: the k-th largest key.
 //   by mass:  the smallest key whose mass of strictly larger keys is < limit.
-template <bool BY_MASS>
-__device__ unsigned radix_select(const float* row, int vocab, float tdiv, float mx, unsigned floor_key,
-                                 unsigned long long limit, unsigned* cnt, unsigned long long* mass,
-                                 unsigned* pick) {
+// `pass` counts the radix passes of the kernel so far (it picks the histogram buffer).
+template <int CL, bool BY_MASS>
+__device__ unsigned radix_select(cg::cluster_group& cluster, RowShared<CL>& sh, const float* row, int v0, int v1, float tdiv,
+                                 float mx, unsigned floor_key, unsigned long long limit, int& pass) {
     unsigned prefix = 0, prefix_mask = 0;
     unsigned long long above = 0;
-    for (int shift = 24; shift >= 0; shift -= 8) {
+    const int lane = threadIdx.x & 31;
+    for (int shift = 24; shift >= 0; shift -= 8, ++pass) {
+        unsigned* cnt = sh.cnt[pass & 1];
+        unsigned long long* mass = sh.mass[pass & 1];
         for (int b = threadIdx.x; b < 256; b += blockDim.x) {
             cnt[b] = 0;
             mass[b] = 0;
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const float x = row[i] / tdiv;
-            const unsigned key = ordered_key(x);
-            if (key < floor_key || (key & prefix_mask) != prefix) continue;
-            const unsigned bin = (key >> shift) & 255u;
-            atomicAdd(&cnt[bin], 1u);
-            if (BY_MASS) atomicAdd(&mass[bin], to_fixed(expf(x - mx)));
+        for (int base = v0; base < v1; base += blockDim.x) {
+            const int i = base + threadIdx.x;
+            bool act = false;
+            unsigned bin = 0;
+            unsigned long long m = 0;
+            if (i < v1) {
+                const float x = row[i] / tdiv;
+                const unsigned key = ordered_key(x);
+                if (key >= floor_key && (key & prefix_mask) == prefix) {
+                    act = true;
+                    bin = (key >> shift) & 255u;
+                    if (BY_MASS) m = to_fixed(expf(x - mx));
+                }
+            }
+            if (shift == 24) {
+                // On the first pass nearly every key falls into a handful of bins (sign and exponent): a
+                // warp adds up what its lanes bring for the same bin before it touches shared memory.
+                unsigned pending = __ballot_sync(0xffffffffu, act);
+                while (pending) {
+                    const int leader = __ffs(pending) - 1;
+                    const unsigned b0 = __shfl_sync(0xffffffffu, bin, leader);
+                    const bool mine = act && bin == b0;
+                    const unsigned same = __ballot_sync(0xffffffffu, mine);
+                    if (BY_MASS) {
+                        unsigned long long v = mine ? m : 0ull;
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                        if (lane == leader) atomicAdd(&mass[b0], v);
+                    }
+                    if (lane == leader) atomicAdd(&cnt[b0], (unsigned)__popc(same));
+                    pending &= ~same;
+                }
+            } else if (act) {
+                atomicAdd(&cnt[bin], 1u);
+                if (BY_MASS) atomicAdd(&mass[bin], m);
+            }
+        }
+        cluster_barrier<CL>(cluster);                   // every block's histogram of this pass is complete
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+            unsigned c = 0;
+            unsigned long long ms = 0;
+            for (int rk = 0; rk < CL; ++rk) {
+                c += peer<CL>(cluster, cnt, rk)[b];
+                if (BY_MASS) ms += peer<CL>(cluster, mass, rk)[b];
+            }
+            sh.tcnt[b] = c;
+            sh.tmass[b] = ms;
         }
         __syncthreads();
         if (threadIdx.x == 0) {
             unsigned long long run = above, chosen_above = above;
             int chosen = -1;
             for (int b = 255; b >= 0; --b) {
-                if (!cnt[b]) continue;
+                if (!sh.tcnt[b]) continue;
                 if (BY_MASS) {
                     // the lowest non-empty bin with less than `limit` of mass strictly above it
                     if (run >= limit && chosen >= 0) break;
                     chosen = b;
                     chosen_above = run;
-                    run += mass[b];
+                    run += sh.tmass[b];
                 } else {
                     // the bin that holds the limit-th largest key
                     chosen = b;
                     chosen_above = run;
-                    if (run + cnt[b] >= limit) break;
-                    run += cnt[b];
+                    if (run + sh.tcnt[b] >= limit) break;
+                    run += sh.tcnt[b];
                 }
             }
-            pick[1] = (unsigned)(chosen_above >> 32);
-            pick[2] = (unsigned)chosen_above;
-            pick[0] = (unsigned)(chosen < 0 ? 0 : chosen);
+            sh.pick[1] = (unsigned)(chosen_above >> 32);
+            sh.pick[2] = (unsigned)chosen_above;
+            sh.pick[0] = (unsigned)(chosen < 0 ? 0 : chosen);
         }
         __syncthreads();
-        prefix |= pick[0] << shift;
+        prefix |= sh.pick[0] << shift;
         prefix_mask |= 255u << shift;
-        above = ((unsigned long long)pick[1] << 32) | pick[2];
+        above = ((unsigned long long)sh.pick[1] << 32) | sh.pick[2];
         __syncthreads();
     }
     return prefix;
 }
 
+template <int CL>
 __global__ void __launch_bounds__(STHREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
               const float* __restrict__ uniform, int* __restrict__ out_token, float* __restrict__ out_logprob,
               int vocab) {
-    __shared__ ArgBest abest[33];
-    __shared__ float fred[33];
-    __shared__ unsigned cnt[256];
-    __shared__ unsigned long long mass[256];
-    __shared__ unsigned pick[4];
-    __shared__ unsigned long long chunk_sum[STHREADS];
-    __shared__ unsigned long long total_s;
-    __shared__ int last_kept_s;
-
-    const int r = blockIdx.x;
+    __shared__ RowShared<CL> sh;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = CL == 1 ? 0 : (int)cluster.block_rank();
+    const int r = blockIdx.y;
     const float* row = logits + (size_t)r * vocab;
+    const int slice = ((vocab + CL - 1) / CL + 31) / 32 * 32;
+    const int v0 = min(vocab, rank * slice), v1 = min(vocab, v0 + slice);
     const float temp = temperature[r];
     const int k = top_k[r];
     const bool greedy = temp == 0.f || k == 1;
+    const float tdiv = greedy ? 1.f : fmaxf(temp, 1e-5f);   // the divisor: x = logit / max(T, 1e-5)
+
+    // the row's best value (ties go to the lower index)
+    {
+        const ArgBest b = block_argmax(row + v0, v1 - v0, tdiv, sh.best);
+        if (threadIdx.x == 0) sh.cbest = ArgBest{b.v, b.i < v1 - v0 ? b.i + v0 : 0x7fffffff};
+    }
+    cluster_barrier<CL>(cluster);
+    ArgBest top{-INFINITY, 0x7fffffff};
+    for (int rk = 0; rk < CL; ++rk) top = better(top, *peer<CL>(cluster, &sh.cbest, rk));
+    const float mx = top.v;
 
     if (greedy) {
-        const ArgBest b = block_argmax(row, vocab, 1.f, abest);
         float s = 0.f;
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) s += expf(row[i] - b.v);
-        s = block_sum(s, fred);
-        if (threadIdx.x == 0) {
-            out_token[r] = b.i < vocab ? b.i : 0;
-            if (out_logprob) out_logprob[r] = -logf(s);
+        for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) s += expf(row[i] - mx);
+        s = block_sum(s, sh.fsum);
+        if (threadIdx.x == 0) sh.csum = s;
+        cluster_barrier<CL>(cluster);
+        if (rank == 0 && threadIdx.x == 0) {
+            float total = 0.f;
+            for (int rk = 0; rk < CL; ++rk) total += *peer<CL>(cluster, &sh.csum, rk);
+            out_token[r] = top.i < vocab ? top.i : 0;
+            if (out_logprob) out_logprob[r] = -logf(total);
         }
+        cluster_barrier<CL>(cluster);                   // nobody leaves while its shared memory may be read
         return;
     }
 
-    const float tdiv = fmaxf(temp, 1e-5f);   // the divisor: x = logit / max(T, 1e-5)
-    const ArgBest top = block_argmax(row, vocab, tdiv, abest);
-    const float mx = top.v;
-
+    int pass = 0;
     unsigned floor_key = 0;
     if (k > 0 && k < vocab)
-        floor_key = radix_select<false>(row, vocab, tdiv, mx, 0u, (unsigned long long)k, cnt, mass, pick);
+        floor_key = radix_select<CL, false>(cluster, sh, row, v0, v1, tdiv, mx, 0u, (unsigned long long)k, pass);
 
     const float p = top_p[r];
     if (p < 1.f) {
         // mass of the top-k survivors, then the cut
         unsigned long long z = 0;
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
             const float x = row[i] / tdiv;
             if (ordered_key(x) >= floor_key) z += to_fixed(expf(x - mx));
         }
-        if (threadIdx.x == 0) total_s = 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+        if (threadIdx.x == 0) sh.ctotal = 0;
         __syncthreads();
-        atomicAdd(&total_s, z);
-        __syncthreads();
-        const unsigned long long limit = (unsigned long long)((double)p * (double)total_s);
-        const unsigned cut = radix_select<true>(row, vocab, tdiv, mx, floor_key, limit > 0 ? limit : 1ull, cnt, mass, pick);
+        if ((threadIdx.x & 31) == 0) atomicAdd(&sh.ctotal, z);
+        cluster_barrier<CL>(cluster);
+        unsigned long long total = 0;
+        for (int rk = 0; rk < CL; ++rk) total += *peer<CL>(cluster, &sh.ctotal, rk);
+        const unsigned long long limit = (unsigned long long)((double)p * (double)total);
+        const unsigned cut = radix_select<CL, true>(cluster, sh, row, v0, v1, tdiv, mx, floor_key, limit > 0 ? limit : 1ull, pass);
         floor_key = max(floor_key, cut);
     }
     const float mp = min_p[r];
 
-    // kept mass per contiguous chunk of the vocabulary, then the draw in vocabulary order
-    const int chunk = (vocab + blockDim.x - 1) / blockDim.x;
-    const int lo = threadIdx.x * chunk, hi = min(vocab, lo + chunk);
+    // kept mass of each warp's contiguous segment of the slice (lanes interleaved, so the reads
+    // coalesce), then the draw in vocabulary order: the segment in which the running mass passes the
+    // target is walked by its warp 32 tokens at a time with a prefix sum over the lanes
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int seg = ((v1 - v0 + nwarp - 1) / nwarp + 31) / 32 * 32;
+    const int lo = min(v1, v0 + warp * seg), hi = min(v1, lo + seg);
     unsigned long long mine = 0;
-    int my_last = -1;
-    for (int i = lo; i < hi; ++i) {
+    for (int i = lo + lane; i < hi; i += 32) {
         const float x = row[i] / tdiv;
         const float e = expf(x - mx);
-        if (ordered_key(x) >= floor_key && e >= mp) {
-            mine += to_fixed(e);
-            my_last = i;
-        }
+        if (ordered_key(x) >= floor_key && e >= mp) mine += to_fixed(e);
     }
-    chunk_sum[threadIdx.x] = mine;
-    if (threadIdx.x == 0) { total_s = 0; last_kept_s = -1; }
-    __syncthreads();
-    atomicAdd(&total_s, mine);
-    atomicMax(&last_kept_s, my_last);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned long long total = total_s;
-        unsigned long long target = (unsigned long long)((double)uniform[r] * (double)total);
-        if (target >= total) target = total ? total - 1 : 0;
-        unsigned long long run = 0;
-        int t = 0;
-        for (; t < (int)blockDim.x - 1; ++t) {
-            if (run + chunk_sum[t] > target) break;
-            run += chunk_sum[t];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0) sh.wsum[warp] = mine;
+    cluster_barrier<CL>(cluster);
+    for (int i = threadIdx.x; i < CL * 32; i += blockDim.x) sh.all_wsum[i] = peer<CL>(cluster, sh.wsum, i / 32)[i % 32];
+    cluster_barrier<CL>(cluster);                       // the last read of another block's shared memory is behind us
+    unsigned long long total = 0, before = 0;
+    const int me = rank * 32 + warp;
+    for (int w = 0; w < CL * 32; ++w) {
+        if (w < me) before += sh.all_wsum[w];
+        total += sh.all_wsum[w];
+    }
+    if (total == 0) {
+        if (rank == 0 && threadIdx.x == 0) {    // nothing kept (cannot happen: the largest always is): the largest
+            out_token[r] = top.i < vocab ? top.i : 0;
+            if (out_logprob) out_logprob[r] = 0.f;
         }
-        int token = last_kept_s < 0 ? top.i : last_kept_s;
-        float chosen_e = 0.f;
-        const int clo = t * chunk, chi = min(vocab, clo + chunk);
-        for (int i = clo; i < chi; ++i) {
+        return;
+    }
+    unsigned long long target = (unsigned long long)((double)uniform[r] * (double)total);
+    if (target >= total) target = total - 1;
+    if (!(before <= target && target < before + mine)) return;       // the one warp whose segment holds the target stays
+    unsigned long long run = before;
+    for (int base = lo; base < hi; base += 32) {
+        const int i = base + lane;
+        float e = 0.f;
+        unsigned long long v = 0;
+        if (i < hi) {
             const float x = row[i] / tdiv;
-            const float e = expf(x - mx);
-            if (ordered_key(x) >= floor_key && e >= mp) {
-                run += to_fixed(e);
-                if (run > target) { token = i; chosen_e = e; break; }
-            }
+            e = expf(x - mx);
+            if (ordered_key(x) >= floor_key && e >= mp) v = to_fixed(e);
         }
-        if (chosen_e == 0.f) chosen_e = expf(row[token] / tdiv - mx);
-        out_token[r] = token;
-        if (out_logprob) out_logprob[r] = logf(chosen_e) - logf((float)((double)total / FIXED_ONE));
+        unsigned long long incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const unsigned hit = __ballot_sync(0xffffffffu, v != 0 && run + incl > target);
+        if (hit) {
+            if (lane == __ffs(hit) - 1) {
+                out_token[r] = i;
+                if (out_logprob) out_logprob[r] = logf(e) - logf((float)((double)total / FIXED_ONE));
+            }
+            return;
+        }
+        run += __shfl_sync(0xffffffffu, incl, 31);
     }
 }
 
@@ -346,8 +458,25 @@ LILY_API int lily_sample(const float* logits, const float* temperature, const in
                          int vocab, cudaStream_t stream) {
     if (rows == 0) return 0;
     LILY_REQUIRE(vocab > 0, "sample: vocab=%d", vocab);
-    sample_kernel<<<rows, STHREADS, 0, stream>>>(logits, temperature, top_k, top_p, min_p, uniform, out_token,
-                                                 out_logprob, vocab);
+    constexpr int CL = 8;
+    if (vocab >= CL * 4096) {
+        // a cluster of CL blocks per row
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(CL, rows);
+        cfg.blockDim = dim3(STHREADS);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = CL;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, sample_kernel<CL>, logits, temperature, top_k, top_p, min_p, uniform, out_token, out_logprob, vocab);
+    } else {
+        sample_kernel<1><<<dim3(1, rows), STHREADS, 0, stream>>>(logits, temperature, top_k, top_p, min_p, uniform, out_token,
+                                                                 out_logprob, vocab);
+    }
     LILY_CHECK_LAUNCH("sample");
     return 0;
 }
