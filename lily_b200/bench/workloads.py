@@ -48,6 +48,9 @@ def main() -> int:
     ap.add_argument("--requests", type=int, default=0)
     ap.add_argument("--new-tokens", type=int, default=0)
     ap.add_argument("--disable-overlap-schedule", action="store_true")
+    ap.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
+    ap.add_argument("--top-k", type=int, default=-1)
+    ap.add_argument("--top-p", type=float, default=1.0)
     a = ap.parse_args()
 
     import torch
@@ -90,7 +93,8 @@ def main() -> int:
     prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
     sched = eng.new_scheduler()
     for i, p in enumerate(prompts):
-        sched.add_request(f"w{i}", p, SamplingParams(max_new_tokens=new_tokens, ignore_eos=True))
+        sched.add_request(f"w{i}", p, SamplingParams(max_new_tokens=new_tokens, ignore_eos=True, temperature=a.temperature,
+                                                     top_k=a.top_k, top_p=a.top_p, seed=i))
     torch.cuda.synchronize()
     start = time.perf_counter()
     steps = decode_only_steps = 0
@@ -122,7 +126,7 @@ def main() -> int:
     if runner.free_tokens() != free_before or runner.cache.held_pages() != [0] * len(runner.cache.groups):
         problems.append("pages were not all given back")
     out = {
-        "workload": a.workload, "layers": cfg["num_hidden_layers"], "layers_of_model": full_layers, "requests": requests,
+        "workload": a.workload, "sampling": {"temperature": a.temperature, "top_k": a.top_k, "top_p": a.top_p}, "layers": cfg["num_hidden_layers"], "layers_of_model": full_layers, "requests": requests,
         "prompt_tokens": sum(lengths), "new_tokens": produced, "wall_s": round(wall, 3),
         "tokens_per_s_out": round(produced / wall, 1), "tokens_per_s_in_and_out": round((sum(lengths) + produced) / wall, 1),
         "steps": steps, "decode_only_steps": decode_only_steps,

@@ -185,8 +185,17 @@ __device__ __forceinline__ void cluster_barrier(cg::cluster_group& cluster) {
 //   by count: the k-th largest key.
 //   by mass:  the smallest key whose mass of strictly larger keys is < limit.
 // `pass` counts the radix passes of the kernel so far (it picks the histogram buffer).
+// x of element i of the row: from the block's copy in shared memory when the slice fits there.
+struct RowX {
+    const float* row;
+    const float* cached;    // x of [v0, v1), or null
+    int v0;
+    float tdiv;
+    __device__ __forceinline__ float operator()(int i) const { return cached ? cached[i - v0] : row[i] / tdiv; }
+};
+
 template <int CL, bool BY_MASS>
-__device__ unsigned radix_select(cg::cluster_group& cluster, RowShared<CL>& sh, const float* row, int v0, int v1, float tdiv,
+__device__ unsigned radix_select(cg::cluster_group& cluster, RowShared<CL>& sh, const RowX& xs, int v0, int v1,
                                  float mx, unsigned floor_key, unsigned long long limit, int& pass) {
     unsigned prefix = 0, prefix_mask = 0;
     unsigned long long above = 0;
@@ -205,7 +214,7 @@ __device__ unsigned radix_select(cg::cluster_group& cluster, RowShared<CL>& sh, 
             unsigned bin = 0;
             unsigned long long m = 0;
             if (i < v1) {
-                const float x = row[i] / tdiv;
+                const float x = xs(i);
                 const unsigned key = ordered_key(x);
                 if (key >= floor_key && (key & prefix_mask) == prefix) {
                     act = true;
@@ -248,28 +257,53 @@ __device__ unsigned radix_select(cg::cluster_group& cluster, RowShared<CL>& sh, 
             sh.tmass[b] = ms;
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned long long run = above, chosen_above = above;
-            int chosen = -1;
-            for (int b = 255; b >= 0; --b) {
-                if (!sh.tcnt[b]) continue;
-                if (BY_MASS) {
-                    // the lowest non-empty bin with less than `limit` of mass strictly above it
-                    if (run >= limit && chosen >= 0) break;
-                    chosen = b;
-                    chosen_above = run;
-                    run += sh.tmass[b];
-                } else {
-                    // the bin that holds the limit-th largest key
-                    chosen = b;
-                    chosen_above = run;
-                    if (run + sh.tcnt[b] >= limit) break;
-                    run += sh.tcnt[b];
-                }
+        if (threadIdx.x < 32) {
+            // Lane l owns bins [8 l, 8 l + 8).  w(b) = what bin b weighs (its count, or its mass); S(b) = above +
+            // the weight of all higher bins.  By count the answer is the bin with S < limit <= S + w; by
+            // mass the lowest non-empty bin with S < limit, or the highest non-empty bin when there is none.
+            unsigned long long w[8], mine = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                w[j] = BY_MASS ? sh.tmass[8 * lane + j] : (unsigned long long)sh.tcnt[8 * lane + j];
+                mine += w[j];
             }
-            sh.pick[1] = (unsigned)(chosen_above >> 32);
-            sh.pick[2] = (unsigned)chosen_above;
-            sh.pick[0] = (unsigned)(chosen < 0 ? 0 : chosen);
+            unsigned long long higher = mine;              // inclusive sum over lanes >= this one
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long up = __shfl_down_sync(0xffffffffu, higher, o);
+                if (lane + o < 32) higher += up;
+            }
+            unsigned long long s_above = above + higher - mine;     // S of this lane's highest bin
+            int found = -1, top_nonempty = -1;
+            unsigned long long found_above = 0, top_above = 0;
+#pragma unroll
+            for (int j = 7; j >= 0; --j) {
+                const int b = 8 * lane + j;
+                if (sh.tcnt[b]) {
+                    if (top_nonempty < 0) { top_nonempty = b; top_above = s_above; }
+                    const bool ok = BY_MASS ? s_above < limit : (s_above < limit && limit <= s_above + w[j]);
+                    if (ok && (BY_MASS || found < 0)) { found = b; found_above = s_above; }    // by mass: the lowest wins
+                }
+                s_above += w[j];
+            }
+            // across lanes: by mass the lowest found bin, by count the only one; else the highest non-empty bin
+            unsigned has = __ballot_sync(0xffffffffu, found >= 0);
+            int src;
+            if (has) {
+                src = BY_MASS ? __ffs(has) - 1 : 31 - __clz(has);
+            } else {
+                has = __ballot_sync(0xffffffffu, top_nonempty >= 0);
+                src = has ? 31 - __clz(has) : 0;
+                found = top_nonempty;
+                found_above = top_above;
+            }
+            const int chosen = __shfl_sync(0xffffffffu, found, src);
+            const unsigned long long chosen_above = __shfl_sync(0xffffffffu, found_above, src);
+            if (lane == 0) {
+                sh.pick[0] = (unsigned)(chosen < 0 ? 0 : chosen);
+                sh.pick[1] = (unsigned)((chosen < 0 ? above : chosen_above) >> 32);
+                sh.pick[2] = (unsigned)(chosen < 0 ? above : chosen_above);
+            }
         }
         __syncthreads();
         prefix |= sh.pick[0] << shift;
@@ -285,8 +319,9 @@ __global__ void __launch_bounds__(STHREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
               const float* __restrict__ uniform, int* __restrict__ out_token, float* __restrict__ out_logprob,
-              int vocab) {
+              int vocab, int cache_floats) {
     __shared__ RowShared<CL> sh;
+    extern __shared__ __align__(16) float x_cache[];     // x of this block's slice when `cache_floats` holds it
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = CL == 1 ? 0 : (int)cluster.block_rank();
     const int r = blockIdx.y;
@@ -298,9 +333,16 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     const bool greedy = temp == 0.f || k == 1;
     const float tdiv = greedy ? 1.f : fmaxf(temp, 1e-5f);   // the divisor: x = logit / max(T, 1e-5)
 
+    // x = logit / divisor of this block's slice, once, into shared memory: every later pass reads it there
+    const bool cached = v1 - v0 <= cache_floats;
+    if (cached)
+        for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) x_cache[i - v0] = row[i] / tdiv;
+    __syncthreads();
+    const RowX xs{row, cached ? x_cache : nullptr, v0, tdiv};
+
     // the row's best value (ties go to the lower index)
     {
-        const ArgBest b = block_argmax(row + v0, v1 - v0, tdiv, sh.best);
+        const ArgBest b = cached ? block_argmax(x_cache, v1 - v0, 1.f, sh.best) : block_argmax(row + v0, v1 - v0, tdiv, sh.best);
         if (threadIdx.x == 0) sh.cbest = ArgBest{b.v, b.i < v1 - v0 ? b.i + v0 : 0x7fffffff};
     }
     cluster_barrier<CL>(cluster);
@@ -310,7 +352,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 
     if (greedy) {
         float s = 0.f;
-        for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) s += expf(row[i] - mx);
+        for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) s += expf(xs(i) - mx);
         s = block_sum(s, sh.fsum);
         if (threadIdx.x == 0) sh.csum = s;
         cluster_barrier<CL>(cluster);
@@ -327,14 +369,14 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     int pass = 0;
     unsigned floor_key = 0;
     if (k > 0 && k < vocab)
-        floor_key = radix_select<CL, false>(cluster, sh, row, v0, v1, tdiv, mx, 0u, (unsigned long long)k, pass);
+        floor_key = radix_select<CL, false>(cluster, sh, xs, v0, v1, mx, 0u, (unsigned long long)k, pass);
 
     const float p = top_p[r];
     if (p < 1.f) {
         // mass of the top-k survivors, then the cut
         unsigned long long z = 0;
         for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
-            const float x = row[i] / tdiv;
+            const float x = xs(i);
             if (ordered_key(x) >= floor_key) z += to_fixed(expf(x - mx));
         }
 #pragma unroll
@@ -346,7 +388,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
         unsigned long long total = 0;
         for (int rk = 0; rk < CL; ++rk) total += *peer<CL>(cluster, &sh.ctotal, rk);
         const unsigned long long limit = (unsigned long long)((double)p * (double)total);
-        const unsigned cut = radix_select<CL, true>(cluster, sh, row, v0, v1, tdiv, mx, floor_key, limit > 0 ? limit : 1ull, pass);
+        const unsigned cut = radix_select<CL, true>(cluster, sh, xs, v0, v1, mx, floor_key, limit > 0 ? limit : 1ull, pass);
         floor_key = max(floor_key, cut);
     }
     const float mp = min_p[r];
@@ -359,7 +401,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     const int lo = min(v1, v0 + warp * seg), hi = min(v1, lo + seg);
     unsigned long long mine = 0;
     for (int i = lo + lane; i < hi; i += 32) {
-        const float x = row[i] / tdiv;
+        const float x = xs(i);
         const float e = expf(x - mx);
         if (ordered_key(x) >= floor_key && e >= mp) mine += to_fixed(e);
     }
@@ -391,7 +433,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
         float e = 0.f;
         unsigned long long v = 0;
         if (i < hi) {
-            const float x = row[i] / tdiv;
+            const float x = xs(i);
             e = expf(x - mx);
             if (ordered_key(x) >= floor_key && e >= mp) v = to_fixed(e);
         }
@@ -459,11 +501,28 @@ LILY_API int lily_sample(const float* logits, const float* temperature, const in
     if (rows == 0) return 0;
     LILY_REQUIRE(vocab > 0, "sample: vocab=%d", vocab);
     constexpr int CL = 8;
-    if (vocab >= CL * 4096) {
+    const bool clustered = vocab >= CL * 4096;
+    const int slice = clustered ? ((vocab + CL - 1) / CL + 31) / 32 * 32 : (vocab + 31) / 32 * 32;
+    // the slice's x values stay in shared memory when they fit beside the kernel's static 12 KB
+    int cache_floats = slice * 4 <= 160 * 1024 ? slice : 0;
+    static int granted[2] = {0, 0};
+    if (cache_floats * 4 > granted[clustered]) {
+        const cudaError_t e = clustered
+            ? cudaFuncSetAttribute(sample_kernel<CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, cache_floats * 4)
+            : cudaFuncSetAttribute(sample_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cache_floats * 4);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            cache_floats = 0;                           // the kernel reads the logits again in every pass instead
+        } else {
+            granted[clustered] = cache_floats * 4;
+        }
+    }
+    if (clustered) {
         // a cluster of CL blocks per row
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(CL, rows);
         cfg.blockDim = dim3(STHREADS);
+        cfg.dynamicSmemBytes = (size_t)cache_floats * 4;
         cfg.stream = stream;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -472,10 +531,11 @@ LILY_API int lily_sample(const float* logits, const float* temperature, const in
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaLaunchKernelEx(&cfg, sample_kernel<CL>, logits, temperature, top_k, top_p, min_p, uniform, out_token, out_logprob, vocab);
+        cudaLaunchKernelEx(&cfg, sample_kernel<CL>, logits, temperature, top_k, top_p, min_p, uniform, out_token, out_logprob, vocab,
+                           cache_floats);
     } else {
-        sample_kernel<1><<<dim3(1, rows), STHREADS, 0, stream>>>(logits, temperature, top_k, top_p, min_p, uniform, out_token,
-                                                                 out_logprob, vocab);
+        sample_kernel<1><<<dim3(1, rows), STHREADS, (size_t)cache_floats * 4, stream>>>(logits, temperature, top_k, top_p, min_p, uniform,
+                                                                                       out_token, out_logprob, vocab, cache_floats);
     }
     LILY_CHECK_LAUNCH("sample");
     return 0;

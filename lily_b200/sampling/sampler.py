@@ -73,9 +73,39 @@ class Sampled:
         return self.tokens.tolist(), (self.logprobs.tolist() if self.logprobs is not None else None)
 
 
+class _Staging:
+    """A few pinned int32 buffers used in turn for the per-step sampling parameters: one asynchronous
+    copy a step (a copy from pageable memory would hold the host until the device gets to it, which
+    is after the step it was queued behind).  A buffer is reused only after its copy has finished."""
+
+    def __init__(self, count: int = 4):
+        self.buffers: List[Optional[torch.Tensor]] = [None] * count
+        self.events: List[Any] = [None] * count
+        self.next = 0
+
+    def upload(self, columns: Sequence[torch.Tensor], device) -> List[torch.Tensor]:
+        """``columns``: equally long int32 / float32 host tensors.  Returns their copies on the device."""
+        n = columns[0].numel()
+        i = self.next
+        self.next = (i + 1) % len(self.buffers)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        if self.buffers[i] is None or self.buffers[i].numel() < len(columns) * n:
+            self.buffers[i] = torch.empty(max(len(columns) * n, 1024), dtype=torch.int32, pin_memory=True)
+        host = self.buffers[i][:len(columns) * n].view(len(columns), n)
+        for row, col in zip(host, columns):
+            row.copy_(col.view(torch.int32))
+        dev = host.to(device, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        return [dev[j].view(col.dtype) for j, col in enumerate(columns)]
+
+
 class Sampler:
     def __init__(self, ops: Any, device):
         self.ops, self.device = ops, device
+        self._staging = _Staging() if torch.device(device).type == "cuda" else None
 
     def launch(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> Sampled:
         """``logits`` float32 [len(rows), vocab] on the device (modified in place by penalties).
@@ -90,12 +120,15 @@ class Sampler:
         need_lp = any(r.params.logprobs for r in rows)
         if all(r.params.greedy for r in rows) and not need_lp:
             return Sampled(ops.argmax(logits))
-        f32 = dict(dtype=torch.float32, device=dev)
-        temperature = torch.tensor([0.0 if r.params.greedy else r.params.temperature for r in rows], **f32)
-        top_k = torch.tensor([r.params.top_k for r in rows], dtype=torch.int32, device=dev)
-        top_p = torch.tensor([r.params.top_p for r in rows], **f32)
-        min_p = torch.tensor([r.params.min_p for r in rows], **f32)
-        uniform = torch.tensor([uniform_for(r.seed, r.index) for r in rows], **f32)
+        columns = [torch.tensor([0.0 if r.params.greedy else r.params.temperature for r in rows], dtype=torch.float32),
+                   torch.tensor([r.params.top_k for r in rows], dtype=torch.int32),
+                   torch.tensor([r.params.top_p for r in rows], dtype=torch.float32),
+                   torch.tensor([r.params.min_p for r in rows], dtype=torch.float32),
+                   torch.tensor([uniform_for(r.seed, r.index) for r in rows], dtype=torch.float32)]
+        if self._staging is not None:
+            temperature, top_k, top_p, min_p, uniform = self._staging.upload(columns, dev)
+        else:
+            temperature, top_k, top_p, min_p, uniform = (c.to(dev) for c in columns)
         tokens, logprobs = ops.sample(logits, temperature, top_k, top_p, min_p, uniform, want_logprob=need_lp)
         return Sampled(tokens, logprobs)
 
