@@ -4,8 +4,9 @@
 // query row straight out of tensor memory.  (The reference runs prefill attention through a
 // library: lily/layers/attention/flashinfer_backend.py:188-203.)
 //
-// One block works on 128 new tokens of one request and one query head, walking the keys in tiles
-// of 128 from the first the window allows to the last the causal rule allows.  Its ten warps:
+// Two kernels.  The first: one block works on 128 new tokens of one request and one query head,
+// walking the keys in tiles of 128 from the first the window allows to the last the causal rule
+// allows.  Its ten warps:
 //   warp 0   one thread issues the TMA loads: Q once (two [128 x 64] boxes, 128-byte swizzle), then
 //            for each tile K and V as [64 keys x 64 features] boxes taken from the request's pages
 //            (a box never crosses a page: the page size is a multiple of 64), into two stages each;
@@ -17,9 +18,11 @@
 //   warps 2-9  two threads per query row, each with 64 of the tile's 128 keys: read their half of the
 //            row of S from tensor memory (tcgen05.ld), mask the tiles on the diagonal and at the
 //            window's edge, agree on the row's maximum, keep the running maximum and sum in float32,
-//            write P = exp2(s * scale - max) as bfloat16 into shared memory in the swizzled k-major
-//            layout that the second product reads, and at the end divide their half of O by the sum
-//            and store it.  (Two warps per scheduler hide each other's latencies; one does not.)
+//            write P = exp2(s * scale - max) as bfloat16 pairs over the tensor-memory columns of the S
+//            tile it came from, where the second product reads it as its A operand, and at the end
+//            divide their half of O by the sum and store it.
+// The second kernel (further down) gives a block two query heads of one kv head, a softmax group each,
+// and is the one that runs when the group size is even and the prompt long enough to fill the device.
 // The maximum that P is taken against only moves when the true maximum has grown by more than 2^8
 // since (then O and the sum are rescaled by the threads that own the row, in tensor memory), so
 // the usual tile costs no pass over O; the result is the same quotient of sums either way.
@@ -33,6 +36,7 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 namespace lily {
@@ -44,18 +48,22 @@ constexpr int D = 128;                    // head size
 // P (the second product's A operand) either goes through shared memory, or, packed as bfloat16
 // pairs, into the tensor-memory columns of the S tile it was computed from; the latter leaves
 // shared memory to K, V and Q alone (a third K/V stage fits) and spares the async-proxy fence.
+#ifndef LILY_FA_PARTS
+#define LILY_FA_PARTS 2
+#endif
+constexpr int PARTS = LILY_FA_PARTS;      // softmax threads per query row (2 or 4), each with 128 / PARTS of a tile's keys
 #ifdef LILY_FA_P_IN_SMEM
 constexpr bool P_TMEM = false;
 constexpr int STAGES = 2;                 // K stages, V stages
 #else
 constexpr bool P_TMEM = true;
-constexpr int STAGES = 3;
+constexpr int STAGES = PARTS == 2 ? 3 : 2;
 #endif
 constexpr int SBUF = 2;                   // S accumulators (and P buffers)
 constexpr int SUB = 128 * 64 * 2;         // a [128 rows][64 elements] sub-tile with 128-byte rows: 16 KB
 constexpr int TILE = 2 * SUB;             // Q, one K stage, one V stage, one P buffer: 32 KB
 constexpr int BOX = 64 * 64 * 2;          // one TMA box of K or V: 8 KB
-constexpr int SOFTMAX_THREADS = 256;     // two threads per query row, each with half of the row's keys
+constexpr int SOFTMAX_THREADS = PARTS * 128;
 constexpr int THREADS = 64 + SOFTMAX_THREADS;
 constexpr int NUM_BARS = 1 + 4 * STAGES + 3 * SBUF;
 // shared memory, all of it dynamic and 1024-byte aligned: Q | K stages | V stages | P buffers | mbarriers |
@@ -63,7 +71,7 @@ constexpr int NUM_BARS = 1 + 4 * STAGES + 3 * SBUF;
 constexpr int OFF_BARS = (1 + 2 * STAGES + (P_TMEM ? 0 : SBUF)) * TILE;
 constexpr int OFF_MISC = OFF_BARS + 8 * NUM_BARS + 8;
 constexpr int OFF_XCH = OFF_MISC + 16;
-constexpr int SMEM = OFF_XCH + 2 * 2 * BQ * 4;
+constexpr int SMEM = OFF_XCH + 2 * PARTS * BQ * 4;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr float GROW_LOG2 = 8.f;          // the reference maximum moves when the true one is 2^8 ahead
 
@@ -180,6 +188,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* r) {
                    "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31]),
                    "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* r) {
+    const uint32_t* u = reinterpret_cast<const uint32_t*>(r);
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};\n"
+                 ::"r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
+                   "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]),
+                   "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -229,9 +244,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (threadIdx.x < 2 * BQ) {                                  // exchange slots start with the tag before their first
-        reinterpret_cast<uint32_t*>(xch)[threadIdx.x] = 3u;                       // parity 0: tags 1, 3, 1, ...
-        reinterpret_cast<uint32_t*>(xch)[2 * BQ + threadIdx.x] = 0u;              // parity 1: tags 2, 0, 2, ...
+    for (int i = threadIdx.x; i < PARTS * BQ; i += THREADS) {    // exchange slots start with the tag before their first
+        reinterpret_cast<uint32_t*>(xch)[i] = 3u;                                 // parity 0: tags 1, 3, 1, ...
+        reinterpret_cast<uint32_t*>(xch)[PARTS * BQ + i] = 0u;                    // parity 1: tags 2, 0, 2, ...
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(512) : "memory");
@@ -319,11 +334,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (!got) return false;
                 }
                 tc_fence_after();
+                // the descriptors of the eight k steps differ from the tile's by constants (address field in 16-byte units)
+                const uint64_t dq = desc_k_major(q_smem), dk = desc_k_major(k_smem + s * TILE);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t inside = (uint32_t)((kk >> 2) * SUB + (kk & 3) * 32);
-                    umma(tmem + (uint32_t)(i & 1) * BKV, desc_k_major(q_smem + inside), desc_k_major(k_smem + s * TILE + inside),
-                         idesc_s, kk != 0 ? 1u : 0u);
+                    const uint64_t inside = (uint64_t)(((kk >> 2) * SUB + (kk & 3) * 32) >> 4);
+                    umma(tmem + (uint32_t)(i & 1) * BKV, dq + inside, dk + inside, idesc_s, kk != 0 ? 1u : 0u);
                 }
                 umma_commit(k_empty + 8 * s);
                 umma_commit(s_full + 8 * (i & 1));
@@ -340,15 +356,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (ok) { FA_TIC(); ok = mbar_wait(v_full + 8 * s, (uint32_t)((j / STAGES) & 1), abort_flag, 6); FA_TOC(3, true); }
                 if (!ok) break;
                 tc_fence_after();
+                const uint64_t dv = desc_mn_major(v_smem + s * TILE), dp = desc_k_major(p_smem + b * TILE);
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; ++kk) {
-                    const uint64_t db = desc_mn_major(v_smem + s * TILE + kk * 2048);
+                    const uint64_t db = dv + (uint64_t)(kk * 2048 >> 4);
                     if (P_TMEM) {
                         // A from tensor memory: 16 keys of P are 8 columns of bfloat16 pairs in S's buffer
                         umma_ts(tmem_o, tmem + (uint32_t)(b * BKV + kk * 8), db, idesc_o, (j | kk) != 0 ? 1u : 0u);
                     } else {
-                        const uint64_t da = desc_k_major(p_smem + b * TILE + (kk >> 2) * SUB + (kk & 3) * 32);
-                        umma(tmem_o, da, db, idesc_o, (j | kk) != 0 ? 1u : 0u);
+                        umma(tmem_o, dp + (uint64_t)(((kk >> 2) * SUB + (kk & 3) * 32) >> 4), db, idesc_o, (j | kk) != 0 ? 1u : 0u);
                     }
                 }
                 umma_commit(v_empty + 8 * s);
@@ -356,55 +372,69 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
         }
     } else {
-        // warps 2-5 take keys [0, 64) of each tile, warps 6-9 keys [64, 128); a warp reads the quarter
-        // of tensor memory (32 lanes = 32 query rows) that its index modulo 4 names
-        constexpr int HALF = BKV / 2;
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        // PARTS threads share a query row, each with COLS of a tile's keys (warps 2-5 the first COLS keys,
+        // the next four warps the next, ...); a warp reads the quarter of tensor memory (32 lanes = 32
+        // query rows) that its index modulo 4 names
+        constexpr int COLS = BKV / PARTS, OCOLS = D / PARTS;
+        const int quarter = warp & 3, part = (warp - 2) >> 2;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const int pos = pos0 + row;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
-        // The two threads of a row hand each other one float per tile (the maximum of their half; at
-        // the end their sum) through a word of shared memory whose two lowest mantissa bits carry a
-        // sequence tag, so the reader knows the word is this tile's without a barrier that an aborted
-        // partner would never reach.  Slots alternate with the tile's parity; both threads drop the
-        // same two bits of their own value, so they agree on the result.
+        // The threads of a row hand each other one float per tile (the maximum of their keys; at the end
+        // their sum) through words of shared memory whose two lowest mantissa bits carry a sequence
+        // tag, so a reader knows the word is this tile's without a barrier that an aborted partner
+        // would never reach.  Slots alternate with the tile's parity; every thread drops the same two
+        // bits of its own value, so all agree on the result.  `combine` folds the values in part order.
         volatile uint32_t* xw = reinterpret_cast<volatile uint32_t*>(xch);
-        auto exchange = [&](int seq, float mine, float& both_mine, float& other) {
+        auto exchange = [&](int seq, float mine, bool sum, float& result) {
             const uint32_t tag = (uint32_t)(seq + 1) & 3u;
             const uint32_t bits = __float_as_uint(mine) & ~3u;
-            xw[((seq & 1) * 2 + half) * BQ + row] = bits | tag;
-            both_mine = __uint_as_float(bits);
-            volatile uint32_t* from = xw + ((seq & 1) * 2 + (half ^ 1)) * BQ + row;
-            for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-                const uint32_t v = *from;
-                if ((v & 3u) == tag) {
-                    other = __uint_as_float(v & ~3u);
-                    return true;
+            xw[((seq & 1) * PARTS + part) * BQ + row] = bits | tag;
+            float acc = sum ? 0.f : -INFINITY;
+#pragma unroll
+            for (int q = 0; q < PARTS; ++q) {
+                float v = __uint_as_float(bits);
+                if (q != part) {
+                    volatile uint32_t* from = xw + ((seq & 1) * PARTS + q) * BQ + row;
+                    bool got = false;
+                    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+                        const uint32_t w = *from;
+                        if ((w & 3u) == tag) {
+                            v = __uint_as_float(w & ~3u);
+                            got = true;
+                            break;
+                        }
+                        if ((i & 1023u) == 1023u && *abort_flag) return false;
+                    }
+                    if (!got) {
+                        *abort_flag = 1;
+                        atomicCAS(&g_status, 0, (12 << 24) | (int)((blockIdx.x + blockIdx.y * gridDim.x) & 0xFFFFFF));
+                        return false;
+                    }
                 }
-                if ((i & 1023u) == 1023u && *abort_flag) return false;
+                acc = sum ? acc + v : fmaxf(acc, v);
             }
-            *abort_flag = 1;
-            atomicCAS(&g_status, 0, (12 << 24) | (int)((blockIdx.x + blockIdx.y * gridDim.x) & 0xFFFFFF));
-            return false;
+            result = acc;
+            return true;
         };
         for (int j = 0; j < n && ok; ++j) {
             const int b = j & 1;
-            { FA_TIC(); ok = mbar_wait(s_full + 8 * b, (uint32_t)((j >> 1) & 1), abort_flag, 7); FA_TOC(8 + half, row == 0); }
+            { FA_TIC(); ok = mbar_wait(s_full + 8 * b, (uint32_t)((j >> 1) & 1), abort_flag, 7); FA_TOC(8 + (part & 1), row == 0); }
             if (!ok) break;
             FA_TIC();
             tc_fence_after();
-            float s[HALF];
+            float s[COLS];
 #pragma unroll
-            for (int c = 0; c < HALF / 32; ++c) tmem_ld32(tmem + lane_addr + (uint32_t)(b * BKV + half * HALF + c * 32), s + c * 32);
+            for (int c = 0; c < COLS / 32; ++c) tmem_ld32(tmem + lane_addr + (uint32_t)(b * BKV + part * COLS + c * 32), s + c * 32);
             tmem_wait_ld();
-            FA_TOC(10 + half, row == 0);
-            const int kb = (jt0 + j) * BKV + half * HALF;
-            const bool need_mask = kb + HALF - 1 > pos0 || (p.window > 0 && kb <= pos0 + BQ - 1 - p.window);
+            FA_TOC(10 + (part & 1), row == 0);
+            const int kb = (jt0 + j) * BKV + part * COLS;
+            const bool need_mask = kb + COLS - 1 > pos0 || (p.window > 0 && kb <= pos0 + BQ - 1 - p.window);
             if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < HALF; ++c) {
+                for (int c = 0; c < COLS; ++c) {
                     const int key = kb + c;
                     const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window);
                     s[c] = seen ? s[c] : -INFINITY;
@@ -412,12 +442,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-            for (int c = 4; c < HALF; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+            for (int c = 4; c < COLS; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
             const float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            float mine_r, theirs;
-            ok = exchange(j, mine, mine_r, theirs);
+            FA_TOC(18 + (part & 1), row == 0);
+            float row_max;
+            ok = exchange(j, mine, false, row_max);
             if (!ok) break;
-            const float m_new = fmaxf(m_used, fmaxf(mine_r, theirs));
+            FA_TOC(20 + (part & 1), row == 0);
+            const float m_new = fmaxf(m_used, row_max);
             if (j == 0) {
                 m_used = m_new;
             } else {
@@ -431,62 +463,67 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (grow) m_used = m_new;
                     l *= alpha;
 #pragma unroll 1
-                    for (int c = 0; c < D / 64; ++c) {         // this thread's half of the row of O
+                    for (int c = 0; c < OCOLS / 32; ++c) {     // this thread's share of the row of O
                         float o[32];
-                        tmem_ld32(tmem_o + lane_addr + (uint32_t)(half * (D / 2) + c * 32), o);
+                        tmem_ld32(tmem_o + lane_addr + (uint32_t)(part * OCOLS + c * 32), o);
                         tmem_wait_ld();
 #pragma unroll
                         for (int e = 0; e < 32; ++e) o[e] *= alpha;
-                        tmem_st32(tmem_o + lane_addr + (uint32_t)(half * (D / 2) + c * 32), o);
+                        tmem_st32(tmem_o + lane_addr + (uint32_t)(part * OCOLS + c * 32), o);
                     }
                     tmem_wait_st();
                 }
             }
+            FA_TOC(22 + (part & 1), row == 0);
             const float mb = (m_used == -INFINITY ? 0.f : m_used) * p.scale_log2;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < HALF; ++c) {
+            for (int c = 0; c < COLS; ++c) {
                 s[c] = ex2(fmaf(s[c], p.scale_log2, -mb));
                 sum4[c & 3] += s[c];
             }
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            FA_TOC(12 + half, row == 0);
+            FA_TOC(12 + (part & 1), row == 0);
             if (P_TMEM) {
                 // P over the first 64 columns of the S buffer it came from: this thread's 64 keys are 32
                 // columns of bfloat16 pairs.  The other thread of the row has read its scores (it posted
                 // its maximum after that), and the product that read this buffer's last P ran before the
                 // S product whose result was just read.
-                uint32_t packed[HALF / 2];
+                uint32_t packed[COLS / 2];
 #pragma unroll
-                for (int c = 0; c < HALF / 2; ++c) packed[c] = pack2(s[2 * c], s[2 * c + 1]);
-                tmem_st32(tmem + lane_addr + (uint32_t)(b * BKV + half * (HALF / 2)), reinterpret_cast<const float*>(packed));
+                for (int c = 0; c < COLS / 2; ++c) packed[c] = pack2(s[2 * c], s[2 * c + 1]);
+                if (COLS == 64) tmem_st32(tmem + lane_addr + (uint32_t)(b * BKV + part * (COLS / 2)), reinterpret_cast<const float*>(packed));
+                else tmem_st16(tmem + lane_addr + (uint32_t)(b * BKV + part * (COLS / 2)), reinterpret_cast<const float*>(packed));
+                FA_TOC(24 + (part & 1), row == 0);
                 tmem_wait_st();
+                FA_TOC(26 + (part & 1), row == 0);
             } else {
                 if (j >= 2) {                              // the product that read this P buffer last is done
                     FA_TIC();
                     ok = mbar_wait(pv_done + 8 * b, (uint32_t)(((j - 2) >> 1) & 1), abort_flag, 9);
-                    FA_TOC(14 + half, row == 0);
+                    FA_TOC(14 + (part & 1), row == 0);
                     if (!ok) break;
                 }
-                // keys [64 half, 64 half + 64) of P are the sub-tile `half`: 128-byte rows, 16-byte pieces swizzled
-                unsigned char* prow = smem + (size_t)(1 + 2 * STAGES) * TILE + (size_t)b * TILE + (size_t)half * SUB + (size_t)row * 128;
+                // this thread's keys lie in sub-tile (part * COLS) / 64 of P: 128-byte rows, 16-byte pieces swizzled
+                unsigned char* prow = smem + (size_t)(1 + 2 * STAGES) * TILE + (size_t)b * TILE + (size_t)((part * COLS) / 64) * SUB + (size_t)row * 128;
+                const int c0 = ((part * COLS) % 64) / 8;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
+                for (int c = 0; c < COLS / 8; ++c) {
                     const float* v = s + c * 8;
-                    *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
+                    *reinterpret_cast<uint4*>(prow + (((c0 + c) ^ (row & 7)) << 4)) =
                         make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
                 }
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tensor cores read P through the async proxy
             }
             tc_fence_before();
             mbar_arrive(p_full + 8 * b);
-            FA_TOC(16 + half, row == 0);
+            FA_TOC(16 + (part & 1), row == 0);
         }
-        // the two halves of a row add their sums (slots of the parity that the last tile did not use)
+        // the threads of a row add their sums (slots of the parity that the last tile did not use)
         if (ok) {
-            float mine_r, theirs;
-            ok = exchange(n, l, mine_r, theirs);
-            l = mine_r + theirs;
+            float total;
+            ok = exchange(n, l, true, total);
+            l = total;
         }
         if (ok) {
             ok = mbar_wait(pv_done + 8 * ((n - 1) & 1), (uint32_t)(((n - 1) >> 1) & 1), abort_flag, 10);
@@ -494,11 +531,303 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = p.out + ((size_t)(q_begin + start + row) * p.nq + head) * D + half * (D / 2);
+            __nv_bfloat16* dst = p.out + ((size_t)(q_begin + start + row) * p.nq + head) * D + part * OCOLS;
 #pragma unroll 1
-            for (int c = 0; c < D / 64; ++c) {
+            for (int c = 0; c < OCOLS / 32; ++c) {
                 float o[32];
-                tmem_ld32(tmem_o + lane_addr + (uint32_t)(half * (D / 2) + c * 32), o);
+                tmem_ld32(tmem_o + lane_addr + (uint32_t)(part * OCOLS + c * 32), o);
+                tmem_wait_ld();
+                if (row < rows_valid) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v)
+                        *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) =
+                            make_uint4(pack2(o[v * 8] * inv, o[v * 8 + 1] * inv), pack2(o[v * 8 + 2] * inv, o[v * 8 + 3] * inv),
+                                       pack2(o[v * 8 + 4] * inv, o[v * 8 + 5] * inv), pack2(o[v * 8 + 6] * inv, o[v * 8 + 7] * inv));
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+// ---- two query heads a block ---------------------------------------------------------------------
+//
+// The same work for two query heads that share a kv head (an even group size): every K and V tile
+// that comes up from L2 feeds both heads, and the two heads' softmax groups (warps 2-5 and 6-9, one
+// thread per query row and no exchange between threads) work half a period apart, one in its
+// exponentials while the other finds its maximum or packs P, with the tensor cores busy on the other
+// head's products meanwhile.  S of each head has one accumulator (128 columns) whose first 64 columns
+// then hold P; O of each head another 128 columns: all 512.  The mma thread's order is
+//   S_0(0) S_1(0), then for every tile j:  PV_0(j) S_0(j+1) PV_1(j) S_1(j+1)
+// where PV_h(j) waits for P_h(j); S_h(j+1) follows PV_h(j) in issue order, which is what keeps it from
+// overwriting P_h(j) too early.  A softmax thread goes over its row twice in pieces of 32 columns (first
+// the maximum, then the exponentials), so that it never holds more than a piece in registers.
+
+constexpr int NH2 = 2;
+constexpr int KV2 = 2;                                   // K stages, V stages
+constexpr int THREADS2 = 64 + NH2 * BQ;
+constexpr int NUM_BARS2 = 1 + 4 * KV2 + 3 * NH2;
+constexpr int OFF2_K = NH2 * TILE;
+constexpr int OFF2_V = OFF2_K + KV2 * TILE;
+constexpr int OFF2_BARS = OFF2_V + KV2 * TILE;
+constexpr int OFF2_MISC = OFF2_BARS + 8 * NUM_BARS2 + 8;
+constexpr int SMEM2 = OFF2_MISC + 16;
+
+__global__ void __launch_bounds__(THREADS2, 1)
+attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Params p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF2_BARS);
+    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem + OFF2_MISC);
+    int& abort_s = *reinterpret_cast<int*>(smem + OFF2_MISC + 4);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicCAS(&g_status, 0, (11 << 24) | (int)((blockIdx.x + blockIdx.y * gridDim.x) & 0xFFFFFF));
+        return;
+    }
+    const uint32_t q_smem = smem_u32(smem), k_smem = q_smem + OFF2_K, v_smem = q_smem + OFF2_V;
+    const uint32_t q_full = smem_u32(&bars[0]);
+    const uint32_t k_full = q_full + 8, k_empty = k_full + 8 * KV2, v_full = k_empty + 8 * KV2, v_empty = v_full + 8 * KV2;
+    const uint32_t s_full = v_empty + 8 * KV2, p_full = s_full + 8 * NH2, pv_done = p_full + 8 * NH2;   // one per head
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < KV2; ++s) {
+            mbar_init(k_full + 8 * s, 1);
+            mbar_init(k_empty + 8 * s, 1);
+            mbar_init(v_full + 8 * s, 1);
+            mbar_init(v_empty + 8 * s, 1);
+        }
+        for (int h = 0; h < NH2; ++h) {
+            mbar_init(s_full + 8 * h, 1);
+            mbar_init(p_full + 8 * h, BQ);                      // one arrival per softmax thread of the head
+            mbar_init(pv_done + 8 * h, 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_s;                          // S (then P) of head h: columns 128 h
+    const uint32_t tmem_o = tmem + NH2 * BKV;                   // O of head h: columns 256 + 128 h
+    volatile int* abort_flag = &abort_s;
+
+    pdl_wait();
+    pdl_launch_dependents();
+
+    const int tile = p.tiles - 1 - (int)blockIdx.y;             // the last tiles, which see the most keys, go first
+    const int head0 = blockIdx.x * NH2;
+    const int req = p.tile_req[tile], start = p.tile_start[tile];
+    const int q_begin = p.cu_seqlens[req];
+    const int new_len = p.cu_seqlens[req + 1] - q_begin;
+    const int rows_valid = min(BQ, new_len - start);
+    const int pos0 = p.prefix_lens[req] + start;
+    const int kv_end = pos0 + rows_valid;
+    const int k_lo = (p.window > 0 && pos0 + 1 > p.window) ? pos0 + 1 - p.window : 0;
+    const int jt0 = k_lo / BKV;
+    const int n = (kv_end - 1) / BKV - jt0 + 1;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int kvh = head0 / (p.nq / p.nkv);
+            const int* table = p.block_table + (size_t)req * p.bt_stride;
+            mbar_expect_tx(q_full, NH2 * TILE);
+            for (int h = 0; h < NH2; ++h)
+                for (int dh = 0; dh < 2; ++dh)
+                    tma_load_3d(q_smem + h * TILE + dh * SUB, &map_q, q_full, dh * 64, head0 + h, q_begin + start);
+            bool ok = true;
+            int issued_k = 0, issued_v = 0;
+            for (int j = 0; j < n && ok; ++j) {
+                const int s = j % KV2;
+                const uint32_t par = (uint32_t)((j / KV2) & 1);
+                int page[2], off[2];
+                for (int h = 0; h < 2; ++h) {            // the two 64-key boxes of the tile
+                    const int key = (jt0 + j) * BKV + 64 * h;
+                    const bool held = key < kv_end;
+                    page[h] = held ? table[key / p.page_size] : 0;
+                    off[h] = held ? key % p.page_size : 0;
+                }
+                ok = mbar_wait(k_empty + 8 * s, par ^ 1, abort_flag, 1);
+                if (!ok) break;
+                mbar_expect_tx(k_full + 8 * s, TILE);
+                for (int h = 0; h < 2; ++h)
+                    for (int dh = 0; dh < 2; ++dh)
+                        tma_load_4d(k_smem + s * TILE + dh * SUB + h * BOX, &map_kv, k_full + 8 * s, dh * 64, off[h], kvh, page[h]);
+                ++issued_k;
+                ok = mbar_wait(v_empty + 8 * s, par ^ 1, abort_flag, 2);
+                if (!ok) break;
+                mbar_expect_tx(v_full + 8 * s, TILE);
+                for (int h = 0; h < 2; ++h)
+                    for (int dh = 0; dh < 2; ++dh)
+                        tma_load_4d(v_smem + s * TILE + dh * SUB + h * BOX, &map_kv, v_full + 8 * s, dh * 64, off[h], p.nkv + kvh, page[h]);
+                ++issued_v;
+            }
+            if (*abort_flag) {
+                for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(q_full, 0); ++i) {}
+                for (int j = max(0, issued_k - KV2); j < issued_k; ++j)
+                    for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(k_full + 8 * (j % KV2), (j / KV2) & 1); ++i) {}
+                for (int j = max(0, issued_v - KV2); j < issued_v; ++j)
+                    for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(v_full + 8 * (j % KV2), (j / KV2) & 1); ++i) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKV >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+            const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+            bool ok = mbar_wait(q_full, 0, abort_flag, 3);
+            auto scores = [&](int h, int i) {            // S_h(i) = Q_h K_i^T; the second head hands the K stage back
+                const int s = i % KV2;
+                const uint64_t dq = desc_k_major(q_smem + h * TILE), dk = desc_k_major(k_smem + s * TILE);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint64_t inside = (uint64_t)(((kk >> 2) * SUB + (kk & 3) * 32) >> 4);
+                    umma(tmem + (uint32_t)(h * BKV), dq + inside, dk + inside, idesc_s, kk != 0 ? 1u : 0u);
+                }
+                umma_commit(s_full + 8 * h);
+                if (h == NH2 - 1) umma_commit(k_empty + 8 * s);
+            };
+            if (ok) ok = mbar_wait(k_full, 0, abort_flag, 4);
+            if (ok) {
+                tc_fence_after();
+                scores(0, 0);
+                scores(1, 0);
+            }
+            for (int j = 0; j < n && ok; ++j) {
+                const int s = j % KV2;
+                ok = mbar_wait(v_full + 8 * s, (uint32_t)((j / KV2) & 1), abort_flag, 6);
+                for (int h = 0; h < NH2 && ok; ++h) {
+                    { FA_TIC(); ok = mbar_wait(p_full + 8 * h, (uint32_t)(j & 1), abort_flag, 5); FA_TOC(4 + h, true); }
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t dv = desc_mn_major(v_smem + s * TILE);
+#pragma unroll
+                    for (int kk = 0; kk < BKV / 16; ++kk)
+                        umma_ts(tmem_o + (uint32_t)(h * D), tmem + (uint32_t)(h * BKV + kk * 8), dv + (uint64_t)(kk * 2048 >> 4), idesc_o,
+                                (j | kk) != 0 ? 1u : 0u);
+                    umma_commit(pv_done + 8 * h);
+                    if (h == NH2 - 1) umma_commit(v_empty + 8 * s);
+                    if (j + 1 < n) {
+                        if (h == 0) {
+                            ok = mbar_wait(k_full + 8 * ((j + 1) % KV2), (uint32_t)(((j + 1) / KV2) & 1), abort_flag, 4);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
+                        scores(h, j + 1);
+                    }
+                }
+            }
+        }
+    } else {
+        const int h = (warp - 2) >> 2, quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint32_t my_s = tmem + lane_addr + (uint32_t)(h * BKV), my_o = tmem_o + lane_addr + (uint32_t)(h * D);
+        const int pos = pos0 + row;
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n && ok; ++j) {
+            { FA_TIC(); ok = mbar_wait(s_full + 8 * h, (uint32_t)(j & 1), abort_flag, 7); FA_TOC(8 + h, row == 0); }
+            if (!ok) break;
+            FA_TIC();
+            tc_fence_after();
+            const int kb = (jt0 + j) * BKV;
+            const bool need_mask = kb + BKV - 1 > pos0 || (p.window > 0 && kb <= pos0 + BQ - 1 - p.window);
+            // first pass: the row's maximum
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; ++c) {
+                float s[32];
+                tmem_ld32(my_s + (uint32_t)(c * 32), s);
+                tmem_wait_ld();
+                if (need_mask) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const int key = kb + c * 32 + e;
+                        const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window);
+                        s[e] = seen ? s[e] : -INFINITY;
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
+            }
+            const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            FA_TOC(10 + h, row == 0);
+            if (j == 0) {
+                m_used = m_new;
+            } else {
+                const bool grow = (m_new - m_used) * p.scale_log2 > GROW_LOG2;      // also when m_used is -inf
+                if (__any_sync(0xffffffffu, grow)) {
+                    // O must hold every product up to tile j - 1 before its rows are rescaled
+                    ok = mbar_wait(pv_done + 8 * h, (uint32_t)((j - 1) & 1), abort_flag, 8);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const float alpha = grow ? ex2((m_used - m_new) * p.scale_log2) : 1.f;
+                    if (grow) m_used = m_new;
+                    l *= alpha;
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; ++c) {
+                        float o[32];
+                        tmem_ld32(my_o + (uint32_t)(c * 32), o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] *= alpha;
+                        tmem_st32(my_o + (uint32_t)(c * 32), o);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            // second pass: P = exp2(s * scale - max) as bfloat16 pairs over the first 64 columns of S.  Piece c
+            // lands on columns [16 c, 16 c + 16), all of them in pieces that this pass has read already.
+            const float mb = (m_used == -INFINITY ? 0.f : m_used) * p.scale_log2;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; ++c) {
+                float s[32];
+                tmem_ld32(my_s + (uint32_t)(c * 32), s);
+                tmem_wait_ld();
+                if (need_mask) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const int key = kb + c * 32 + e;
+                        const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window);
+                        s[e] = seen ? s[e] : -INFINITY;
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    s[e] = ex2(fmaf(s[e], p.scale_log2, -mb));
+                    sum4[e & 3] += s[e];
+                }
+                uint32_t packed[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) packed[e] = pack2(s[2 * e], s[2 * e + 1]);
+                tmem_st16(my_s + (uint32_t)(c * 16), reinterpret_cast<const float*>(packed));
+            }
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            FA_TOC(12 + h, row == 0);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(p_full + 8 * h);
+            FA_TOC(16 + h, row == 0);
+        }
+        if (ok) ok = mbar_wait(pv_done + 8 * h, (uint32_t)((n - 1) & 1), abort_flag, 10);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* dst = p.out + ((size_t)(q_begin + start + row) * p.nq + head0 + h) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                float o[32];
+                tmem_ld32(my_o + (uint32_t)(c * 32), o);
                 tmem_wait_ld();
                 if (row < rows_valid) {
 #pragma unroll
@@ -608,6 +937,8 @@ LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out,
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fa::attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(fa::attention_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::SMEM2);
         if (e != cudaSuccess) {
             set_error("attention_prefill_tc: cannot get %d bytes of shared memory: %s", fa::SMEM, cudaGetErrorString(e));
             return 2;
@@ -618,7 +949,19 @@ LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out,
     p.block_table = block_table; p.cu_seqlens = cu_seqlens; p.prefix_lens = prefix_lens; p.tile_req = tile_req;
     p.tile_start = tile_start; p.out = (__nv_bfloat16*)out; p.bt_stride = bt_stride; p.tiles = tiles; p.nq = nq; p.nkv = nkv;
     p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
-    launch_pdl(fa::attention_prefill_tc_kernel, dim3(nq, tiles), dim3(fa::THREADS), (size_t)fa::SMEM, stream, map_q, map_kv, p);
+    static const bool single = [] {
+        const char* v = getenv("LILY_B200_FA_SINGLE");
+        return v && v[0] == '1';
+    }();
+    // two heads of a kv head a block, when that still leaves a block for every SM (short prompts
+    // fill the device better with a head a block)
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    if ((nq / nkv) % 2 == 0 && !single && (long)tiles * (nq / 2) >= sms)
+        launch_pdl(fa::attention_prefill_tc2_kernel, dim3(nq / 2, tiles), dim3(fa::THREADS2), (size_t)fa::SMEM2, stream, map_q, map_kv, p);
+    else
+        launch_pdl(fa::attention_prefill_tc_kernel, dim3(nq, tiles), dim3(fa::THREADS), (size_t)fa::SMEM, stream, map_q, map_kv, p);
     LILY_CHECK_LAUNCH("attention_prefill_tc");
     return 0;
 }
