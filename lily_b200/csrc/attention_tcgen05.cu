@@ -571,7 +571,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 constexpr int NH2 = 2;
 constexpr int KV2 = 2;                                   // K stages, V stages
 constexpr int THREADS2 = 64 + NH2 * BQ;
-constexpr int NUM_BARS2 = 1 + 4 * KV2 + 3 * NH2;
+constexpr int NUM_BARS2 = 1 + 4 * KV2 + 3 * NH2 + 1;   // the last one is the timing build's probe
 constexpr int OFF2_K = NH2 * TILE;
 constexpr int OFF2_V = OFF2_K + KV2 * TILE;
 constexpr int OFF2_BARS = OFF2_V + KV2 * TILE;
@@ -696,6 +696,36 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 if (h == NH2 - 1) umma_commit(k_empty + 8 * s);
             };
             if (ok) ok = mbar_wait(k_full, 0, abort_flag, 4);
+#ifdef LILY_FA_TIMING
+            if (ok && n >= 2) {
+                // how long 32 products of each kind take back to back, on tiles that are about to be overwritten:
+                // slot 28 S products (Q and K from shared memory), slot 29 the same issued as 8, slot 30 PV products
+                // (P from tensor memory, V from shared memory), slot 31 the empty commit-and-wait round trip
+                const uint32_t probe = pv_done + 8 * NH2;
+                mbar_init(probe, 1);
+                asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+                ok = mbar_wait(v_full, 0, abort_flag, 6);
+                tc_fence_after();
+                uint32_t phase = 0;
+                const uint64_t dq = desc_k_major(q_smem), dk = desc_k_major(k_smem), dv = desc_mn_major(v_smem);
+                for (int kind = 0; kind < 4 && ok; ++kind) {
+                    FA_TIC();
+                    const int reps = kind == 0 ? 4 : (kind == 3 ? 0 : (kind == 1 ? 1 : 4));
+                    for (int r = 0; r < reps; ++r)
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk) {
+                            const uint64_t inside = (uint64_t)(((kk >> 2) * SUB + (kk & 3) * 32) >> 4);
+                            if (kind <= 1) umma(tmem, dq + inside, dk + inside, idesc_s, 1u);
+                            else umma_ts(tmem_o, tmem + (uint32_t)(kk * 8), dv + (uint64_t)(kk * 2048 >> 4), idesc_o, 1u);
+                        }
+                    umma_commit(probe);
+                    ok = mbar_wait(probe, phase, abort_flag, 13);
+                    phase ^= 1;
+                    FA_TOC(28 + (kind == 0 ? 0 : kind == 1 ? 1 : kind == 2 ? 2 : 3), true);
+                }
+                tc_fence_after();
+            }
+#endif
             if (ok) {
                 tc_fence_after();
                 scores(0, 0);
