@@ -28,6 +28,7 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -279,6 +280,172 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---- the same product over pairs of blocks ---------------------------------------------------------
+//
+// Two blocks of a cluster (two SMs) work on one 256 x 256 output tile with `tcgen05.mma.cta_group::2`:
+// each block loads its own 128 rows of A and its own 128 of the tile's 256 rows of B, the even
+// block's mma thread issues 256 x 256 x 16 products that read A from both blocks (128 rows each) and B
+// from both (one half each), and each block ends up with its 128 rows of the tile in its own tensor
+// memory.  Per block and k step that is 32 KB of operands for twice the arithmetic of the one-block
+// kernel's 48 KB, and the tensor cores run at their full rate, which one-block products do not reach.
+//   * the `full` barrier of a stage lives in the even block; both blocks' TMA loads complete their
+//     bytes on it (`cp.async.bulk.tensor ... cta_group::2`) and the even block's loader announces the
+//     sum of both;
+//   * `empty` and `ready` are in each block and the mma thread's commits reach both at once
+//     (`tcgen05.commit ... multicast::cluster`);
+//   * `drained` lives in the even block; the epilogue warps of both blocks arrive there.
+// Every wait is bounded as in the one-block kernel; both blocks meet at a cluster barrier before
+// they free tensor memory.
+
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_B_BYTES = 128 * BK * 2;                 // this block's half of the B tile
+constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// The address, in the cluster's shared window, of the same variable in block `rank` of the cluster.
+__device__ __forceinline__ uint32_t in_block(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_in_even_block, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar_in_even_block), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives, when the products issued so far are done, on the barrier at this offset in both blocks.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_in_cluster) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(bar_in_cluster) : "memory");
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * PAIR_STAGES + 4];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                      // 0: the block whose mma thread issues for both
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int num_kb = (K + BK - 1) / BK;
+    const int m_blocks = (M + 2 * BM - 1) / (2 * BM), n_blocks = (N + BN - 1) / BN, tiles = m_blocks * n_blocks;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[PAIR_STAGES]);
+    const uint32_t ready0 = smem_u32(&bars[2 * PAIR_STAGES]), drained0 = smem_u32(&bars[2 * PAIR_STAGES + 2]);
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);                       // waited on in the even block only
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(ready0 + 8 * a, 1);
+            mbar_init(drained0 + 8 * a, 16);                   // the eight epilogue warps of each block (even block's copy)
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                        // both blocks' barriers exist before anyone signals the other's
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = tmem_base_s;
+    volatile int* abort_flag = &abort_s;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < tiles && ok; tile += pairs) {
+                const int m0 = (tile % m_blocks) * 2 * BM + (int)rank * BM, n0 = (tile / m_blocks) * BN + (int)rank * 128;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    ok = mbar_wait(empty0 + 8 * s, ((it / PAIR_STAGES) & 1) ^ 1, abort_flag, 1);
+                    if (!ok) break;
+                    const uint32_t full_even = in_block(full0 + 8 * s, 0);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);     // this block's bytes and the other's
+                    const uint32_t a_dst = smem_u32(smem + s * PAIR_STAGE_BYTES);
+                    tma_load_2d_pair(a_dst, &map_a, full_even, kb * BK, m0);
+                    tma_load_2d_pair(a_dst + A_BYTES, &map_b, full_even, kb * BK, n0);
+                }
+            }
+            if (*abort_flag && rank == 0) {
+                for (int j = max(0, it - PAIR_STAGES); j < it; ++j)
+                    for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(full0 + 8 * (j % PAIR_STAGES), (j / PAIR_STAGES) & 1); ++i) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // kind::f16, bfloat16 a and b (k-major), float32 d, n = 256, m = 256 over the two blocks
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            int it = 0, local = 0;
+            bool ok = true;
+            for (int tile = pair; tile < tiles && ok; tile += pairs, ++local) {
+                const int acc = local & 1;
+                ok = mbar_wait(drained0 + 8 * acc, ((local >> 1) & 1) ^ 1, abort_flag, 4);   // both blocks' epilogues have emptied it
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t tacc = tmem + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    ok = mbar_wait(full0 + 8 * s, (it / PAIR_STAGES) & 1, abort_flag, 2);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint64_t da = smem_desc(smem_u32(smem + s * PAIR_STAGE_BYTES));
+                    const uint64_t db = smem_desc(smem_u32(smem + s * PAIR_STAGE_BYTES + A_BYTES));
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk)
+                        umma_pair(tacc, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb | kk) != 0 ? 1u : 0u);
+                    umma_commit_pair(empty0 + 8 * s);          // the stage is free in both blocks once these have read it
+                }
+                umma_commit_pair(ready0 + 8 * acc);            // both blocks' epilogues may read their half
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+            const int acc = local & 1;
+            const int m0 = (tile % m_blocks) * 2 * BM + (int)rank * BM, n0 = (tile / m_blocks) * BN;
+            if (!mbar_wait(ready0 + 8 * acc, (local >> 1) & 1, abort_flag, 3)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int row = m0 + quarter * 32 + lane;
+            epilogue_tile<EPI>(tmem + acc * BN + ((uint32_t)(quarter * 32) << 16), C, bias, row, row < M, n0, N, ldc, (warp - 2) >> 2);
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(in_block(drained0 + 8 * acc, 0));
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                        // nobody frees tensor memory or leaves while the other block works
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(2 * BN) : "memory");
+    }
+}
+
 // ---- host side: tensor maps -----------------------------------------------------------------
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -313,9 +480,62 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld,
     return 0;
 }
 
+static int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
+// LILY_B200_GEMM_PAIR=0 keeps every product on the one-block kernel.
+static bool pair_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("LILY_B200_GEMM_PAIR");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
 template <int EPI>
 static int launch(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldc,
                   cudaStream_t stream) {
+    const int sms = sm_count();
+    if (pair_enabled() && M > BM) {
+        // pairs of blocks on 256 x 256 tiles
+        CUtensorMap ma, mb;
+        if (make_map(&ma, A, M, K, lda, BM)) return 1;
+        if (make_map(&mb, B, N, K, K, 128)) return 1;
+        const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
+        auto kern = gemm_tc_pair_kernel<EPI>;
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) {
+                set_error("gemm_tc: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+                return 2;
+            }
+            configured = true;
+        }
+        const long tiles = (long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
+        const long pairs = tiles < sms / 2 ? tiles : sms / 2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(2 * pairs));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, kern, ma, mb, (__nv_bfloat16*)C, (const __nv_bfloat16*)bias, M, N, K, ldc);
+        return 0;
+    }
     CUtensorMap ma, mb;
     if (make_map(&ma, A, M, K, lda, BM)) return 1;
     if (make_map(&mb, B, N, K, K, BN)) return 1;
@@ -331,12 +551,6 @@ static int launch(const void* A, const void* B, void* C, const void* bias, int M
         configured = true;
     }
     const long tiles = (long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     kern<<<grid, THREADS, smem, stream>>>(ma, mb, (__nv_bfloat16*)C, (const __nv_bfloat16*)bias, M, N, K, ldc);
     return 0;
