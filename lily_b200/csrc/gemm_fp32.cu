@@ -1,13 +1,16 @@
 // True float32 matrix product for the 32-bit path: C[M,N] = A[M,K] . W[N,K]^T (+ bias[N]).
 //
-// FFMA only (no tensor cores, no TF32).  Each output element is summed over k = 0..K-1 in
-// that order whatever M and N are, so a row's result does not depend on what else is in the
-// batch.  Takes the place of F.linear in float32 (lily/layers/quantization/base.py:69-72).
+// FFMA only (no tensor cores, no TF32).  Each output element is summed over k in a fixed order
+// whatever M and N are (runs of 256 products, each run summed left to right, the runs' sums added
+// left to right), so a row's result does not depend on what else is in the batch; summing in runs
+// keeps the rounding error of a sum over 12,288 products near that of one over a few hundred.
+// Takes the place of F.linear in float32 (lily/layers/quantization/base.py:69-72).
 #include "common.cuh"
 
 namespace lily {
 
 constexpr int BM = 64, BN = 64, BK = 16;
+constexpr int RUN = 256;               // products per run (a multiple of BK)
 
 __global__ void __launch_bounds__(256)
 gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
@@ -17,8 +20,17 @@ gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, const
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int lr = threadIdx.x >> 2, lc = (threadIdx.x & 3) * 4;   // loader: row 0..63, k offset 0,4,8,12
-    float acc[4][4] = {};
+    float acc[4][4] = {}, total[4][4] = {};
     for (int k0 = 0; k0 < K; k0 += BK) {
+        if (k0 != 0 && k0 % RUN == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    total[i][j] += acc[i][j];
+                    acc[i][j] = 0.f;
+                }
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int k = k0 + lc + j;
@@ -48,7 +60,7 @@ gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, const
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
-            if (n < N) C[(size_t)m * ldc + n] = acc[i][j] + (bias ? bias[n] : 0.f);
+            if (n < N) C[(size_t)m * ldc + n] = (total[i][j] + acc[i][j]) + (bias ? bias[n] : 0.f);
         }
     }
 }

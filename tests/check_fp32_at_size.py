@@ -1,0 +1,153 @@
+"""The float32 path at full model sizes against the plain implementation, in every way of cutting.
+
+Not a pytest file (it holds tens of GB on the device for a minute): run it by hand on a B200,
+
+    python tests/check_fp32_at_size.py qwen3_8b
+    python tests/check_fp32_at_size.py llama31_8b
+    python tests/check_fp32_at_size.py qwen3_32b --layers 16      # 64 layers in float32 twice do not fit
+
+It draws seeded random float32 weights of the named sizes on the device (the engine's own
+random-weights mode), hands the same tensors to ``tests/plain_impl.py`` (whole sequences, no cache,
+plain PyTorch in float32 on the device, TF32 off) and compares the logits of ``ModelRunner.step``
+for a prompt taken whole, in portions of changing size, with the last 32 tokens one by one (decode
+graphs), and mixed with three other requests over a pool so small that pages are used again.  Prints
+one JSON line with the largest absolute difference of each cutting.  With ``--float64`` the plain
+implementation also runs in float64 and both float32 results are compared with it: at these sizes
+(32 to 36 layers, sums over 4,096 to 14,336 products, logits up to 7) the plain float32
+implementation itself ends 1.4e-4 to 2.0e-4 from the exact logits, so that is how far a correct
+float32 engine can be from it.  Exit code 0: every cutting within 1e-4 of the plain float32 result,
+or, with ``--float64``, the engine within 1e-4 of the exact logits and the cuttings within 1e-4 of
+one another.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+sys.path.insert(0, HERE)
+
+SIZES = {
+    "qwen3_8b": {
+        "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 36, "hidden_size": 4096,
+        "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+        "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+        "max_position_embeddings": 4096, "hidden_act": "silu", "torch_dtype": "float32"},
+    "llama31_8b": {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 32, "hidden_size": 4096,
+        "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336,
+        "vocab_size": 128256, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 8192},
+        "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 8192, "hidden_act": "silu",
+        "torch_dtype": "float32"},
+    "qwen3_32b": {
+        "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 64, "hidden_size": 5120,
+        "num_attention_heads": 64, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 25600,
+        "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+        "max_position_embeddings": 16384, "hidden_act": "silu", "torch_dtype": "float32"},
+}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("size", choices=sorted(SIZES))
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the size has (reported)")
+    ap.add_argument("--tokens", type=int, default=200)
+    ap.add_argument("--float64", action="store_true", help="also compare both float32 results with the plain implementation in float64")
+    a = ap.parse_args()
+
+    import torch
+
+    import plain_impl
+    from harness import run_mixed, run_portions, run_whole
+    from lily_b200.config.registry import resolve_architecture
+    from lily_b200.config.server_args import ServerArgs
+    from lily_b200.engine.runner import ModelRunner
+    from lily_b200.weights.random_init import RandomSource, expected_tensors
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    cfg = dict(SIZES[a.size])
+    full_layers = cfg["num_hidden_layers"]
+    if a.layers:
+        cfg["num_hidden_layers"] = a.layers
+    vocab = cfg["vocab_size"]
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, vocab, (a.tokens,), generator=g).tolist()
+    others = {k: torch.randint(0, vocab, (m,), generator=g).tolist() for k, m in (("b", 90), ("c", 70), ("d", 100))}
+
+    # pages of 64: the prompt's 4 pages and the other requests' 2 + 2 + 2 fit a pool of 8 only because
+    # the last request gets the pages that the first to end gives back
+    args = ServerArgs(dtype="float32", device="cuda:0", context_length=1024, page_size=64, max_total_tokens=8 * 64,
+                      max_running_requests=4, random_seed=0)
+    t0 = time.time()
+    runner = ModelRunner.from_random(cfg, seed=7, args=args)
+    arch = resolve_architecture(cfg["architectures"])
+    config = arch.config_from_dict(cfg, {}, architecture=arch.name)
+    source = RandomSource(expected_tensors(config, arch), 7, torch.float32, "cuda:0")
+    weights = {name: source.get(name) for name in source.entries()}
+    load_s = time.time() - t0
+
+    with torch.device("cuda:0"), torch.no_grad():
+        want = plain_impl.all_logits(cfg, weights, ids).cpu()
+        want_others = {k: plain_impl.all_logits(cfg, weights, v).cpu() for k, v in others.items()}
+    exact = None
+    if a.float64:
+        # the same plain implementation with every ``.float()`` widened to float64: what both float32 results
+        # are rounded versions of (rotation angles stay float32, as the architecture defines them)
+        narrow, norm32 = torch.Tensor.float, plain_impl.rms_norm
+
+        def norm64(x, weight, eps):
+            xf = x.double()
+            return weight.double() * (xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps))
+        try:
+            torch.Tensor.float = lambda self, *args, **kw: self.double()
+            plain_impl.rms_norm = norm64
+            with torch.device("cuda:0"), torch.no_grad():
+                w64 = {k: v.double() for k, v in weights.items()}
+                del weights
+                exact = plain_impl.all_logits(cfg, w64, ids).cpu()
+                del w64
+        finally:
+            torch.Tensor.float, plain_impl.rms_norm = narrow, norm32
+    weights = None
+    torch.cuda.empty_cache()
+
+    def worst(got, ref):
+        return float((got - ref[:got.shape[0]]).abs().max())
+
+    report = {}
+    whole = run_whole(runner, ids)
+    report["whole"] = worst(whole, want)
+    n = len(ids)
+    report["last_32_one_by_one"] = worst(run_portions(runner, ids, [n - 32] + [1] * 32), want)
+    report["portions"] = worst(run_portions(runner, ids, [64, 2, 37, 5, 64, 3]), want)
+    reqs = {"a": ids, **others}
+    plan = [{"a": 100, "b": 30}, {"a": 50, "b": 2, "c": 40}, {"a": 1, "b": 58, "c": 1}] + [{"a": 1, "c": 1, "d": 5}] * 20 + \
+           [{"a": n - 171, "c": 9}]
+    got = run_mixed(runner, reqs, plan, ends={2: ["b"]})
+    report["mixed"] = max([worst(got["a"], want)] + [worst(got[k], want_others[k]) for k in others])
+    out = {"size": a.size, "layers": cfg["num_hidden_layers"], "layers_of_model": full_layers, "tokens": n,
+           "max_abs_logit": round(float(want.abs().max()), 3), "max_abs_diff": {k: float(f"{v:.3e}") for k, v in report.items()},
+           "against_float64": None if exact is None else {"engine": float(f"{float((whole.double() - exact).abs().max()):.3e}"),
+                                                          "plain_float32": float(f"{float((want.double() - exact).abs().max()):.3e}")},
+           "graph_steps": runner.graph_steps, "held_pages_after": runner.cache.held_pages(), "load_s": round(load_s, 1)}
+    print(json.dumps(out))
+    if runner.cache.held_pages() != [0]:
+        return 1
+    if max(report.values()) <= 1e-4:
+        return 0
+    if exact is None:
+        return 1
+    spread = max(report.values()) - min(report.values())          # the cuttings among themselves
+    return 0 if out["against_float64"]["engine"] <= 1e-4 and spread <= 1e-4 else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
