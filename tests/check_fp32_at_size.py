@@ -1,4 +1,5 @@
-"""The float32 path at full model sizes against the plain implementation, in every way of cutting.
+"""The engine at full model sizes against the plain implementation, in every way of cutting (float32,
+and with ``--dtype bfloat16`` the serving kernels).
 
 Not a pytest file (it holds tens of GB on the device for a minute): run it by hand on a B200,
 
@@ -59,6 +60,8 @@ def main() -> int:
     ap.add_argument("size", choices=sorted(SIZES))
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the size has (reported)")
     ap.add_argument("--tokens", type=int, default=200)
+    ap.add_argument("--dtype", default="float32", choices=["float32", "bfloat16"],
+                    help="bfloat16: the serving kernels against the plain implementation over the same bfloat16 weights")
     ap.add_argument("--float64", action="store_true", help="also compare both float32 results with the plain implementation in float64")
     a = ap.parse_args()
 
@@ -84,13 +87,13 @@ def main() -> int:
 
     # pages of 64: the prompt's 4 pages and the other requests' 2 + 2 + 2 fit a pool of 8 only because
     # the last request gets the pages that the first to end gives back
-    args = ServerArgs(dtype="float32", device="cuda:0", context_length=1024, page_size=64, max_total_tokens=8 * 64,
+    args = ServerArgs(dtype=a.dtype, device="cuda:0", context_length=1024, page_size=64, max_total_tokens=(-(-a.tokens // 64) + 4) * 64,
                       max_running_requests=4, random_seed=0)
     t0 = time.time()
     runner = ModelRunner.from_random(cfg, seed=7, args=args)
     arch = resolve_architecture(cfg["architectures"])
     config = arch.config_from_dict(cfg, {}, architecture=arch.name)
-    source = RandomSource(expected_tensors(config, arch), 7, torch.float32, "cuda:0")
+    source = RandomSource(expected_tensors(config, arch), 7, torch.float32 if a.dtype == "float32" else torch.bfloat16, "cuda:0")
     weights = {name: source.get(name) for name in source.entries()}
     load_s = time.time() - t0
 
@@ -125,6 +128,9 @@ def main() -> int:
     report = {}
     whole = run_whole(runner, ids)
     report["whole"] = worst(whole, want)
+    extra = {"mean_abs_diff_whole": float(f"{float((whole - want).abs().mean()):.3e}"),
+             "mean_abs_logit": float(f"{float(want.abs().mean()):.3e}"),
+             "same_argmax_whole": round(float((whole.argmax(-1) == want.argmax(-1)).float().mean()), 4)}
     n = len(ids)
     report["last_32_one_by_one"] = worst(run_portions(runner, ids, [n - 32] + [1] * 32), want)
     report["portions"] = worst(run_portions(runner, ids, [64, 2, 37, 5, 64, 3]), want)
@@ -133,14 +139,19 @@ def main() -> int:
            [{"a": n - 171, "c": 9}]
     got = run_mixed(runner, reqs, plan, ends={2: ["b"]})
     report["mixed"] = max([worst(got["a"], want)] + [worst(got[k], want_others[k]) for k in others])
-    out = {"size": a.size, "layers": cfg["num_hidden_layers"], "layers_of_model": full_layers, "tokens": n,
+    out = {"size": a.size, "dtype": a.dtype, "layers": cfg["num_hidden_layers"], "layers_of_model": full_layers, "tokens": n,
            "max_abs_logit": round(float(want.abs().max()), 3), "max_abs_diff": {k: float(f"{v:.3e}") for k, v in report.items()},
            "against_float64": None if exact is None else {"engine": float(f"{float((whole.double() - exact).abs().max()):.3e}"),
                                                           "plain_float32": float(f"{float((want.double() - exact).abs().max()):.3e}")},
-           "graph_steps": runner.graph_steps, "held_pages_after": runner.cache.held_pages(), "load_s": round(load_s, 1)}
+           **extra, "graph_steps": runner.graph_steps, "held_pages_after": runner.cache.held_pages(), "load_s": round(load_s, 1)}
     print(json.dumps(out))
     if runner.cache.held_pages() != [0]:
         return 1
+    if a.dtype == "bfloat16":
+        # activations carry 8 bits and every layer rounds a few times: the mean difference grows with the square
+        # root of the depth (measured 1.0 % of the mean logit at 2 layers, 1.8 % at 8, 4.4 % at 36); a wrong
+        # kernel shows as tens of per cent
+        return 0 if extra["mean_abs_diff_whole"] < 0.08 * extra["mean_abs_logit"] and max(report.values()) < 1.0 else 1
     if max(report.values()) <= 1e-4:
         return 0
     if exact is None:
