@@ -930,11 +930,12 @@ LILY_API int lily_attention_tc_status() {
 }
 
 // The arguments of lily_attention_prefill_mma with tiles of 128 rows, plus the number of pages of
-// the layer (`kv` is [num_pages, 2, nkv, page_size, d]) and of new tokens (`q` is [tokens, nq, d]).
+// the layer (`kv` is [num_pages, 2, nkv, page_size, d]) and of new tokens (`q` is [tokens, nq, d]);
+// heads_per_block 1 or 2 names the kernel, 0 leaves the choice to the launcher.
 LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out, const int* block_table, int bt_stride,
                                        const int* cu_seqlens, const int* prefix_lens, const int* tile_req,
                                        const int* tile_start, int tiles, int nq, int nkv, int d, int page_size, int window,
-                                       float scale, int tokens, int num_pages, cudaStream_t stream) {
+                                       float scale, int tokens, int num_pages, int heads_per_block, cudaStream_t stream) {
     if (tiles == 0) return 0;
     LILY_REQUIRE(lily_attention_prefill_tc_takes(d, page_size), "attention_prefill_tc: head size %d, page size %d (takes %d and multiples of 64)",
                  d, page_size, fa::D);
@@ -979,16 +980,16 @@ LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out,
     p.block_table = block_table; p.cu_seqlens = cu_seqlens; p.prefix_lens = prefix_lens; p.tile_req = tile_req;
     p.tile_start = tile_start; p.out = (__nv_bfloat16*)out; p.bt_stride = bt_stride; p.tiles = tiles; p.nq = nq; p.nkv = nkv;
     p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
-    static const bool single = [] {
-        const char* v = getenv("LILY_B200_FA_SINGLE");
-        return v && v[0] == '1';
-    }();
-    // two heads of a kv head a block, when that still leaves a block for every SM (short prompts
-    // fill the device better with a head a block)
+    // two heads of a kv head a block when the group size is even and, unless the caller says which, when
+    // that still leaves a block for every SM (short prompts fill the device better with a head a block)
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    if ((nq / nkv) % 2 == 0 && !single && (long)tiles * (nq / 2) >= sms)
+    const bool even = (nq / nkv) % 2 == 0;
+    LILY_REQUIRE(heads_per_block >= 0 && heads_per_block <= 2 && (heads_per_block != 2 || even),
+                 "attention_prefill_tc: %d heads a block with %d query heads per kv head", heads_per_block, nq / nkv);
+    const bool two = heads_per_block == 2 || (heads_per_block == 0 && even && (long)tiles * (nq / 2) >= sms);
+    if (two)
         launch_pdl(fa::attention_prefill_tc2_kernel, dim3(nq / 2, tiles), dim3(fa::THREADS2), (size_t)fa::SMEM2, stream, map_q, map_kv, p);
     else
         launch_pdl(fa::attention_prefill_tc_kernel, dim3(nq, tiles), dim3(fa::THREADS), (size_t)fa::SMEM, stream, map_q, map_kv, p);

@@ -35,7 +35,7 @@ _SIGNATURES = {
     "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
-    "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
     "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
@@ -366,11 +366,12 @@ def attention_tc_status() -> int:
 def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
                       prefix_lens: torch.Tensor, tile_req: torch.Tensor, tile_start: torch.Tensor, out: torch.Tensor,
                       nq: int, nkv: int, d: int, page_size: int, scale: float, window: Optional[int] = None,
-                      tile_rows: Optional[int] = None) -> None:
+                      tile_rows: Optional[int] = None, heads_per_block: int = 0) -> None:
     """Causal attention of each request's new tokens over its cached prefix and themselves.
     ``q`` and ``out`` are [tokens, nq * d] indexed by ``cu_seqlens``; tiles list (request, offset)
     in steps of ``tile_rows`` (default: ``prefill_tile_rows(q.dtype, d)``), which also names the
-    kernel: the tcgen05 kernel takes tiles of its own size, the others theirs."""
+    kernel: the tcgen05 kernel takes tiles of its own size, the others theirs.  ``heads_per_block``
+    (tcgen05 only) 1 or 2 picks between its one-head and its two-head form; 0 lets the launcher choose."""
     _dev(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out)
     if q.dtype != kv_layer.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, cache and out must share a dtype")
@@ -386,7 +387,7 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
                               f"page size {page_size}")
         if not (q.is_contiguous() and out.is_contiguous() and kv_layer.is_contiguous()):
             raise KernelError("attention_prefill: the tcgen05 kernel takes contiguous q, out and cache")
-        _call("lily_attention_prefill_tc", *common, q.shape[0], kv_layer.shape[0], _stream())
+        _call("lily_attention_prefill_tc", *common, q.shape[0], kv_layer.shape[0], int(heads_per_block), _stream())
     elif uses_tensor_cores(q.dtype, d):
         _call("lily_attention_prefill_mma", *common, _stream())
     else:

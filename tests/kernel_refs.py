@@ -129,7 +129,7 @@ def _attend(q, k, v, q_pos, scale, window):
 
 
 def attention_prefill(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out, nq, nkv, d,
-                      page_size, scale, window=None, tile_rows=None):
+                      page_size, scale, window=None, tile_rows=None, heads_per_block=0):
     for r in sorted(set(tile_req.tolist())):
         t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
         prefix = int(prefix_lens[r])

@@ -298,10 +298,22 @@ def test_attention_prefill_tcgen05(nq, nkv, page, window):
     cache, table, q, cu, pre = _attention_case(dtype, nq, nkv, d, page, prefixes, news, window, spike=True)
     treq_t, tstart_t = _tiles_of(news, rows)
     got, want = torch.zeros_like(q), torch.zeros_like(q)
-    o.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, got, nq, nkv, d, page, d ** -0.5, window, tile_rows=rows)
+    o.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, got, nq, nkv, d, page, d ** -0.5, window, tile_rows=rows,
+                        heads_per_block=1)
     assert o.attention_tc_status() == 0
     ref.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, want, nq, nkv, d, page, d ** -0.5, window)
     torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    if (nq // nkv) % 2 == 0:
+        # the form with two heads of a kv head a block
+        both = torch.zeros_like(q)
+        o.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, both, nq, nkv, d, page, d ** -0.5, window, tile_rows=rows,
+                            heads_per_block=2)
+        assert o.attention_tc_status() == 0
+        torch.testing.assert_close(both.float(), want.float(), **tol(dtype))
+    else:
+        with pytest.raises(o.KernelError, match="heads a block"):
+            o.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, torch.zeros_like(q), nq, nkv, d, page, d ** -0.5,
+                                window, tile_rows=rows, heads_per_block=2)
     # the mma.sync kernel on the same case, cut into its own tiles, agrees too
     base = o.prefill_tile_rows(dtype, d)
     breq, bstart = _tiles_of(news, base)
@@ -326,11 +338,14 @@ def test_attention_prefill_tcgen05_rising_scores():
             cache[pg, 1, :, off] = c
     rows = o.prefill_tile_rows(dtype, d, page, 10 ** 6)
     treq_t, tstart_t = _tiles_of(news, rows)
-    got, want = torch.zeros_like(q), torch.zeros_like(q)
-    o.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, got, nq, nkv, d, page, d ** -0.5, None, tile_rows=rows)
-    assert o.attention_tc_status() == 0
+    want = torch.zeros_like(q)
     ref.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, want, nq, nkv, d, page, d ** -0.5, None)
-    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    for heads in (1, 2):
+        got = torch.zeros_like(q)
+        o.attention_prefill(q, cache, table, cu, pre, treq_t, tstart_t, got, nq, nkv, d, page, d ** -0.5, None, tile_rows=rows,
+                            heads_per_block=heads)
+        assert o.attention_tc_status() == 0
+        torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
     assert float(want.float()[-1].view(nq, d)[0].mean()) > 3.5          # the last row sees the strongest key
 
 
