@@ -87,7 +87,7 @@ def main() -> int:
 
     # pages of 64: the prompt's 4 pages and the other requests' 2 + 2 + 2 fit a pool of 8 only because
     # the last request gets the pages that the first to end gives back
-    args = ServerArgs(dtype=a.dtype, device="cuda:0", context_length=1024, page_size=64, max_total_tokens=(-(-a.tokens // 64) + 4) * 64,
+    args = ServerArgs(dtype=a.dtype, device="cuda:0", context_length=max(1024, -(-a.tokens // 64) * 64 + 64), page_size=64, max_total_tokens=(-(-a.tokens // 64) + 4) * 64,
                       max_running_requests=4, random_seed=0)
     t0 = time.time()
     runner = ModelRunner.from_random(cfg, seed=7, args=args)
