@@ -115,7 +115,15 @@ def _i32(t: Optional[torch.Tensor], name: str):
     return _p(t)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    """The current stream's handle.  The step launches a few hundred kernels from Python, so the two
+    C calls are used directly where this torch has them (the public route builds a Stream object a call)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
