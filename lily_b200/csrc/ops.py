@@ -39,6 +39,7 @@ _SIGNATURES = {
     "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
     "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+    "lily_top_logprobs": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_sample": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
 }
 
@@ -70,6 +71,7 @@ def library():
         lib.lily_attention_prefill_tc_takes.restype = _i
         lib.lily_attention_mma_supports.argtypes = [_i]
         lib.lily_attention_mma_supports.restype = _i
+        lib.lily_top_logprobs_cap.restype = _i
         lib.lily_attention_decode_scratch_floats.argtypes = [_i, _i, _i, _i]
         lib.lily_attention_decode_scratch_floats.restype = _sz
         _lib = lib
@@ -474,3 +476,25 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     _call("lily_sample", _p(logits), _p(temperature), _i32(top_k, "top_k"), _p(top_p), _p(min_p), _p(uniform),
           _p(tokens), _p(logprob), rows, vocab, _stream())
     return tokens, logprob
+
+
+def top_logprobs_cap() -> int:
+    """The most entries a row of ``top_logprobs`` can return."""
+    return int(library().lily_top_logprobs_cap())
+
+
+def top_logprobs(logits: torch.Tensor, k: torch.Tensor):
+    """The ``k[r]`` most probable tokens of each row of float32 ``logits`` with their log-probabilities
+    (log-softmax of the logits as given).  Returns (tokens int32 [rows, cap], logprobs float32 [rows, cap],
+    counts int32 [rows]): row r holds ``counts[r] >= k[r]`` entries in no particular order (ties at the
+    k-th value are all kept, up to cap); rows with ``k[r] <= 0`` hold none."""
+    _dev(logits, k)
+    if logits.dtype != torch.float32:
+        raise KernelError("top_logprobs takes float32 logits")
+    rows, vocab = logits.shape
+    cap = top_logprobs_cap()
+    tokens = torch.empty((rows, cap), dtype=torch.int32, device=logits.device)
+    logprobs = torch.empty((rows, cap), dtype=torch.float32, device=logits.device)
+    counts = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _call("lily_top_logprobs", _p(logits), _i32(k, "k"), _p(tokens), _p(logprobs), _p(counts), rows, vocab, _stream())
+    return tokens, logprobs, counts

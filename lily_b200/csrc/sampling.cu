@@ -455,6 +455,49 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     }
 }
 
+// The k most probable tokens of a row and their log-probabilities (log-softmax of the logits as they
+// are, i.e. after penalties and before temperature: lily/layers/sampler.py:118-133).  One block per row:
+// maximum and log-sum-exp, the k-th largest key by radix selection, then every token at or above it is
+// appended to the row's list (ties may make it longer than k, up to `cap`; the host sorts and cuts).
+constexpr int TOP_CAP = 128;
+
+__global__ void __launch_bounds__(STHREADS)
+top_logprobs_kernel(const float* __restrict__ logits, const int* __restrict__ k_per_row, int* __restrict__ out_token,
+                    float* __restrict__ out_logprob, int* __restrict__ out_count, int vocab) {
+    __shared__ RowShared<1> sh;
+    __shared__ int count_s;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * vocab;
+    const int k = min(k_per_row[r], TOP_CAP);
+    if (threadIdx.x == 0) count_s = 0;
+    if (k <= 0) {
+        if (threadIdx.x == 0) out_count[r] = 0;
+        return;
+    }
+    const ArgBest top = block_argmax(row, vocab, 1.f, sh.best);
+    float s = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) s += expf(row[i] - top.v);
+    s = block_sum(s, sh.fsum);
+    const float lse = top.v + logf(s);
+    const RowX xs{row, nullptr, 0, 1.f};
+    int pass = 0;
+    const unsigned kth = k < vocab ? radix_select<1, false>(cluster, sh, xs, 0, vocab, top.v, 0u, (unsigned long long)k, pass) : 0u;
+    __syncthreads();
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float x = row[i];
+        if (ordered_key(x) >= kth) {
+            const int at = atomicAdd(&count_s, 1);
+            if (at < TOP_CAP) {
+                out_token[(size_t)r * TOP_CAP + at] = i;
+                out_logprob[(size_t)r * TOP_CAP + at] = x - lse;
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) out_count[r] = min(count_s, TOP_CAP);
+}
+
 }  // namespace lily
 
 using namespace lily;
@@ -538,5 +581,17 @@ LILY_API int lily_sample(const float* logits, const float* temperature, const in
                                                                                        out_token, out_logprob, vocab, cache_floats);
     }
     LILY_CHECK_LAUNCH("sample");
+    return 0;
+}
+
+LILY_API int lily_top_logprobs_cap() { return TOP_CAP; }
+
+// out_token / out_logprob: [rows, lily_top_logprobs_cap()], out_count [rows]; k_per_row[r] <= 0 leaves row r empty.
+LILY_API int lily_top_logprobs(const float* logits, const int* k_per_row, int* out_token, float* out_logprob, int* out_count,
+                               int rows, int vocab, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    LILY_REQUIRE(vocab > 0, "top_logprobs: vocab=%d", vocab);
+    top_logprobs_kernel<<<rows, STHREADS, 0, stream>>>(logits, k_per_row, out_token, out_logprob, out_count, vocab);
+    LILY_CHECK_LAUNCH("top_logprobs");
     return 0;
 }

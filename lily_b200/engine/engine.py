@@ -85,7 +85,7 @@ class Engine:
     def generate(self, prompts: Sequence[Sequence[int]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[Dict[str, Any]]:
         """Runs the prompts (lists of token ids) to completion with continuous batching and
-        returns, per prompt, ``{"output_ids", "finish_reason", "prompt_tokens", "logprobs"}``."""
+        returns, per prompt, ``{"output_ids", "finish_reason", "prompt_tokens", "logprobs", "top_logprobs"}``."""
         sched = self.new_scheduler()
         if sampling_params is None or isinstance(sampling_params, SamplingParams):
             plist = [sampling_params or SamplingParams()] * len(prompts)
@@ -105,7 +105,7 @@ class Engine:
         for rid in rids:
             r = sched.results[rid]
             out.append({"output_ids": r.output_ids, "finish_reason": r.finish_reason, "prompt_tokens": r.prompt_tokens,
-                        "logprobs": r.logprobs})
+                        "logprobs": r.logprobs, "top_logprobs": r.top_logprobs})
         return out
 
     # ---- text, when a tokenizer is at hand (lily/engine.py:133-142) ---------------------

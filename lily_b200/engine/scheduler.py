@@ -59,6 +59,7 @@ class Req:
     seed: int = 0
     output_ids: List[int] = field(default_factory=list)
     output_logprobs: Optional[List[float]] = None
+    output_top_logprobs: Optional[List[List[tuple]]] = None
     slot: Optional[int] = None
     seq_len: int = 0                    # positions cached
     extend_input_len: int = 0           # tokens this step brings
@@ -113,6 +114,7 @@ class SchedulerOutput:
     finished: bool
     finish_reason: Optional[dict]
     logprobs: Optional[List[float]] = None
+    top_logprobs: Optional[List[List[tuple]]] = None
 
 
 class Scheduler:
@@ -151,6 +153,8 @@ class Scheduler:
                   eos_token_ids=self.eos_token_ids, seed=seed)
         if params.logprobs:
             req.output_logprobs = []
+        if params.top_logprobs:
+            req.output_top_logprobs = []
         cache = self.runner.cache
         n = len(req.origin_input_ids)
         problem = None
@@ -194,7 +198,8 @@ class Scheduler:
         self.results[req.rid] = SchedulerOutput(
             rid=req.rid, output_ids=list(req.output_ids), prompt_tokens=len(req.origin_input_ids),
             completion_tokens=len(req.output_ids), finished=req.finished, finish_reason=req.finished_reason,
-            logprobs=list(req.output_logprobs) if req.output_logprobs is not None else None)
+            logprobs=list(req.output_logprobs) if req.output_logprobs is not None else None,
+            top_logprobs=list(req.output_top_logprobs) if req.output_top_logprobs is not None else None)
 
     def _retract(self, req: Req) -> None:
         self._release(req)
@@ -264,7 +269,7 @@ class Scheduler:
         """With a step in flight: whether the next one has to wait for its tokens (penalties read
         the history; a retraction re-queues prompt + produced tokens)."""
         candidates = self._decode_candidates()
-        if any(not r.sampling_params.plain for r in candidates):
+        if any(not r.sampling_params.plain or r.sampling_params.top_logprobs for r in candidates):
             return True
         return self._decode_pages(candidates) > self.runner.cache.free_pages()
 
@@ -358,6 +363,7 @@ class Scheduler:
     def _collect(self, launched: _Launched) -> None:
         """Reads the tokens of a launched step and lets each request take its own."""
         tokens, logprobs = launched.result.read()
+        tops = launched.result.read_top()
         for i, req in enumerate(launched.sampled):
             req.pending -= 1
             if req.finished:
@@ -365,6 +371,8 @@ class Scheduler:
             req.output_ids.append(int(tokens[i]))
             if req.output_logprobs is not None and logprobs is not None:
                 req.output_logprobs.append(float(logprobs[i]))
+            if req.output_top_logprobs is not None and tops is not None and tops[i] is not None:
+                req.output_top_logprobs.append(tops[i])
             if self.on_token is not None:
                 self.on_token(req, int(tokens[i]))
             if req.check_finished(self.runner.context_len):

@@ -1,8 +1,7 @@
 """Per-request sampling parameters: the fields, defaults and checks of
-lily/sampling/sampling_params.py:9-52.  ``stop`` strings, ``stream``, ``n`` and
-``top_logprobs`` belong to the text front end and the server, which this engine does not have;
-they are accepted and checked so that a caller's parameters carry over, and ``stop`` /
-``top_logprobs`` raise when set because nothing here could honour them."""
+lily/sampling/sampling_params.py:9-52.  ``stop`` strings, ``stream`` and ``n`` belong to the text
+front end and the server, which this engine does not have; they are accepted and checked so that a
+caller's parameters carry over, and ``stop`` raises when set because nothing here could honour it."""
 
 from __future__ import annotations
 
@@ -46,8 +45,8 @@ class SamplingParams:
         if self.stop:
             raise ValueError("stop strings need a detokenizer; this engine is token in, token out "
                              "(use stop_token_ids)")
-        if self.top_logprobs is not None:
-            raise ValueError("top_logprobs is not supported; logprobs=True returns the chosen token's")
+        if self.top_logprobs is not None and not (1 <= self.top_logprobs <= 64):
+            raise ValueError("top_logprobs must be between 1 and 64")
         if self.n != 1:
             raise ValueError("n must be 1; submit the prompt n times with different seeds")
         if self.logit_bias is not None:

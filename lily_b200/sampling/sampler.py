@@ -49,6 +49,7 @@ class Sampled:
     host_tokens: Optional[torch.Tensor] = None     # where an asynchronous copy puts them
     host_logprobs: Optional[torch.Tensor] = None
     copied: Any = None                             # event after the copies
+    top: Any = None                                # (tokens, logprobs, counts, k per row) of ``top_logprobs`` rows
 
     def start_copy(self, pinned_tokens: torch.Tensor, pinned_logprobs: Optional[torch.Tensor] = None) -> None:
         """Starts the copy to pinned host memory behind the sampling kernels and records an event,
@@ -61,6 +62,22 @@ class Sampled:
             self.host_logprobs.copy_(self.logprobs, non_blocking=True)
         self.copied = torch.cuda.Event()
         self.copied.record()
+
+    def read_top(self) -> Optional[List[Optional[List[Tuple[int, float]]]]]:
+        """Per row None, or the ``top_logprobs`` most probable tokens as (token, log-probability), most
+        probable first, ties by the lower token id (lily/layers/sampler.py:124-132)."""
+        if self.top is None:
+            return None
+        tokens, logprobs, counts, ks = self.top
+        tokens, logprobs, counts = tokens.tolist(), logprobs.tolist(), counts.tolist()
+        out: List[Optional[List[Tuple[int, float]]]] = []
+        for r, k in enumerate(ks):
+            if k <= 0:
+                out.append(None)
+                continue
+            pairs = sorted(zip(tokens[r][:counts[r]], logprobs[r][:counts[r]]), key=lambda tv: (-tv[1], tv[0]))
+            out.append([(int(t), float(v)) for t, v in pairs[:k]])
+        return out
 
     def read(self) -> Tuple[List[int], Optional[List[float]]]:
         if self.tokens is None:
@@ -118,8 +135,12 @@ class Sampler:
         if any(not r.params.plain for r in rows):
             self._penalties(logits, rows)
         need_lp = any(r.params.logprobs for r in rows)
+        top = None
+        ks = [int(r.params.top_logprobs or 0) for r in rows]
+        if any(ks):
+            top = (*ops.top_logprobs(logits, torch.tensor(ks, dtype=torch.int32).to(dev)), ks)
         if all(r.params.greedy for r in rows) and not need_lp:
-            return Sampled(ops.argmax(logits))
+            return Sampled(ops.argmax(logits), top=top)
         columns = [torch.tensor([0.0 if r.params.greedy else r.params.temperature for r in rows], dtype=torch.float32),
                    torch.tensor([r.params.top_k for r in rows], dtype=torch.int32),
                    torch.tensor([r.params.top_p for r in rows], dtype=torch.float32),
@@ -130,7 +151,7 @@ class Sampler:
         else:
             temperature, top_k, top_p, min_p, uniform = (c.to(dev) for c in columns)
         tokens, logprobs = ops.sample(logits, temperature, top_k, top_p, min_p, uniform, want_logprob=need_lp)
-        return Sampled(tokens, logprobs)
+        return Sampled(tokens, logprobs, top=top)
 
     def __call__(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> Tuple[List[int], Optional[List[float]]]:
         """``launch`` and read the result at once."""

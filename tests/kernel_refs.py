@@ -182,3 +182,26 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, want_logprob=False
     dev = logits.device
     return (torch.tensor(toks, dtype=torch.int32, device=dev),
             torch.tensor(lps, dtype=torch.float32, device=dev) if want_logprob else None)
+
+
+def top_logprobs_cap():
+    return 128
+
+
+def top_logprobs(logits, k):
+    rows, vocab = logits.shape
+    cap = top_logprobs_cap()
+    tokens = torch.zeros((rows, cap), dtype=torch.int32, device=logits.device)
+    logprobs = torch.zeros((rows, cap), dtype=torch.float32, device=logits.device)
+    counts = torch.zeros((rows,), dtype=torch.int32, device=logits.device)
+    lp = torch.log_softmax(logits.float(), -1)
+    for r in range(rows):
+        kk = min(int(k[r]), cap, vocab)
+        if kk <= 0:
+            continue
+        kth = torch.topk(lp[r], kk).values[-1]
+        idx = torch.nonzero(lp[r] >= kth).flatten()[:cap]
+        counts[r] = idx.numel()
+        tokens[r, :idx.numel()] = idx.to(torch.int32)
+        logprobs[r, :idx.numel()] = lp[r, idx]
+    return tokens, logprobs, counts

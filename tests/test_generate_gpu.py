@@ -123,6 +123,27 @@ def test_overlap_schedule_on_the_gpu_changes_no_token(dtype):
         assert eng.kv_available() == 2048
 
 
+def test_top_logprobs_on_the_gpu():
+    cfg = tiny_models.TINY_LLAMA
+    from lily_b200 import SamplingParams
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 66, tmp)
+        eng = engine(path, "float32", page_size=16)
+        p = tiny_models.random_tokens(40, cfg["vocab_size"], 130)
+        out = eng.generate([p, p], [SamplingParams(max_new_tokens=6, top_logprobs=4, logprobs=True, ignore_eos=True),
+                                    SamplingParams(max_new_tokens=6, temperature=0.8, seed=2, top_logprobs=2, ignore_eos=True)])
+        for o, k in zip(out, (4, 2)):
+            ids = list(p)
+            assert len(o["top_logprobs"]) == 6
+            for tok, top in zip(o["output_ids"], o["top_logprobs"]):
+                want = torch.log_softmax(plain_impl.all_logits(cfg, weights, ids)[-1].double(), -1)
+                best = torch.topk(want, k)
+                assert [t for t, _ in top] == best.indices.tolist()
+                assert all(abs(v - float(w)) < 1e-4 for (_, v), w in zip(top, best.values))
+                ids.append(tok)
+        assert out[0]["top_logprobs"][0][0][0] == out[0]["output_ids"][0] and abs(out[0]["logprobs"][0] - out[0]["top_logprobs"][0][0][1]) < 1e-5
+
+
 def test_small_pool_retracts_on_the_gpu():
     cfg = tiny_models.TINY_QWEN3
     from lily_b200 import SamplingParams

@@ -442,6 +442,29 @@ def test_argmax_and_penalties(vocab):
 
 
 @pytest.mark.parametrize("vocab", [256, 1009, 151936])
+def test_top_logprobs(vocab):
+    g = torch.Generator(device=DEV).manual_seed(23)
+    logits = torch.randn(5, vocab, device=DEV, generator=g) * 3
+    logits[1, 7] = logits[1, 11] = float(logits[1].max()) + 1.0          # a tie at the top
+    ks = [0, 2, 5, 20, 64]
+    tokens, lps, counts = ops().top_logprobs(logits, torch.tensor(ks, device=DEV, dtype=torch.int32))
+    want = torch.log_softmax(logits.double(), -1)
+    for r, k in enumerate(ks):
+        n = int(counts[r])
+        if k == 0:
+            assert n == 0
+            continue
+        assert k <= n <= ops().top_logprobs_cap()
+        got = sorted(zip(tokens[r, :n].tolist(), lps[r, :n].tolist()), key=lambda tv: (-tv[1], tv[0]))[:k]
+        top = torch.topk(want[r], k)
+        assert sorted(t for t, _ in got) == sorted(top.indices.tolist())
+        for t, v in got:
+            assert abs(v - float(want[r, t])) < 1e-4
+    rt, rl, rc = ref.top_logprobs(logits, torch.tensor(ks, device=DEV, dtype=torch.int32))
+    assert rc.tolist() == counts.tolist()
+
+
+@pytest.mark.parametrize("vocab", [256, 1009, 151936])
 def test_sample_matches_filtered_distribution(vocab):
     import plain_impl
 

@@ -221,9 +221,30 @@ def test_overlap_schedule_changes_no_output(setup):
     assert s.runner.cache.held_pages() == [0] and s.runner.cache.slots.available == 8
 
 
+def test_top_logprobs_follow_the_plain_log_softmax(setup):
+    cfg, weights, path = setup
+    p = prompts(cfg, [9], seed=45)[0]
+    s = scheduler(path, overlap=True)
+    s.add_request("a", p, SamplingParams(max_new_tokens=5, top_logprobs=3, logprobs=True, ignore_eos=True))
+    s.add_request("b", p, SamplingParams(max_new_tokens=5, ignore_eos=True))
+    s.run_to_completion()
+    a, b = s.results["a"], s.results["b"]
+    assert a.output_ids == b.output_ids and b.top_logprobs is None and len(a.top_logprobs) == 5
+    ids = list(p)
+    for tok, lp, top in zip(a.output_ids, a.logprobs, a.top_logprobs):
+        want = torch.log_softmax(plain_impl.all_logits(cfg, weights, ids)[-1].double(), -1)
+        best = torch.topk(want, 3)
+        assert [t for t, _ in top] == best.indices.tolist() and top[0][0] == tok       # greedy: the chosen token leads
+        assert all(abs(v - float(w)) < 1e-4 for (_, v), w in zip(top, best.values)) and abs(lp - top[0][1]) < 1e-5
+        ids.append(tok)
+
+
 def test_sampling_params_checks():
+    with pytest.raises(ValueError, match="top_logprobs"):
+        SamplingParams(top_logprobs=0)
+    assert SamplingParams(top_logprobs=5).top_logprobs == 5
     for kw in ({"max_new_tokens": 0}, {"temperature": -1}, {"top_p": 0}, {"top_k": 0}, {"min_p": 1.0},
-               {"repetition_penalty": 0}, {"stop": "x"}, {"top_logprobs": 2}, {"n": 2}):
+               {"repetition_penalty": 0}, {"stop": "x"}, {"top_logprobs": 65}, {"n": 2}):
         with pytest.raises(ValueError):
             SamplingParams(**kw)
     assert SamplingParams().greedy and SamplingParams(temperature=1.0, top_k=1).greedy
