@@ -36,6 +36,11 @@ def main(argv: Optional[List[str]] = None) -> int:
     gen.add_argument("--top-p", type=float, default=1.0)
     gen.add_argument("--min-p", type=float, default=0.0)
     gen.add_argument("--repetition-penalty", type=float, default=1.0)
+    gen.add_argument("--frequency-penalty", type=float, default=0.0)
+    gen.add_argument("--presence-penalty", type=float, default=0.0)
+    gen.add_argument("--stop-token-ids", type=_ids, default=[], help="token ids, comma or space separated")
+    gen.add_argument("--logprobs", action="store_true", help="the chosen tokens' log-probabilities")
+    gen.add_argument("--top-logprobs", type=int, default=None, help="the k most probable tokens at every step")
     gen.add_argument("--seed", type=int, default=None)
     gen.add_argument("--ignore-eos", action="store_true")
 
@@ -75,6 +80,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     engine.server_args = server_args
     params = SamplingParams(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k,
                             top_p=args.top_p, min_p=args.min_p, repetition_penalty=args.repetition_penalty,
+                            frequency_penalty=args.frequency_penalty, presence_penalty=args.presence_penalty,
+                            stop_token_ids=args.stop_token_ids, logprobs=args.logprobs, top_logprobs=args.top_logprobs,
                             seed=args.seed, ignore_eos=args.ignore_eos)
     for out in engine.generate([_ids(p) for p in args.prompt_ids], params):
         print(json.dumps(out))
