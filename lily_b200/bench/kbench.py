@@ -188,7 +188,7 @@ def main() -> int:
             x = torch.randn(a.tokens, a.k, device=dev, generator=g).to(dt)
             w = torch.randn(a.n, a.k, device=dev, generator=g).to(dt)
             if a.kernel == "linear_split":
-                fns.append(lambda x=x, w=w: ops.linear_split(x, w))
+                fns.append(lambda x=x, w=w: ops.linear_split(x, w, splits=a.splits or None))
             elif a.kernel == "gemm_tc":
                 fns.append(lambda x=x, w=w: ops.gemm_tc(x, w))
             elif a.kernel == "gemm_tc_silu":
