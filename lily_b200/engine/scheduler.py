@@ -222,11 +222,20 @@ class Scheduler:
         return [r for r in self.running if not r.ends_with_pending(ctx)]
 
     def _plan_decode(self) -> List[Req]:
-        """Running requests that decode this step, after retracting the youngest while the pool
-        cannot give every one of them its next position.  (Nothing is in flight when it retracts:
+        """Running requests that decode this step, after taking pages back while the pool cannot give
+        every one of them its next position: first from a request still filling its prompt, then by
+        retracting the youngest running one.  (Nothing is in flight when it retracts:
         ``step`` reads the tokens first when the pages are short.)"""
         cache = self.runner.cache
         while self.running and self._decode_pages(self._decode_candidates()) > cache.free_pages():
+            filling = next((r for r in reversed(self.waiting_queue) if r.slot is not None), None)
+            if filling is not None:
+                # a request that waits with part of its prompt cached gives that back first and keeps its place
+                self._release(filling)
+                filling.extend_input_len = 0
+                filling.retractions += 1
+                self.retractions += 1
+                continue
             if len(self.running) == 1:
                 req = self.running.pop()
                 self._release(req)
@@ -242,10 +251,12 @@ class Scheduler:
         # pages the decode tokens take now, and one kept back per running request for its next page
         free_pages = cache.free_pages() - self._decode_pages(decoding) - len(decoding)
         budget = min(self.max_prefill_tokens, self.chunked_prefill_size)
-        slots = self.max_running_requests - len(decoding)
+        # every request with a slot counts, also one whose last token is still in flight and one that waits
+        # with part of its prompt cached
+        slots = self.max_running_requests - len(self.running) - sum(r.slot is not None for r in self.waiting_queue)
         selected: List[Req] = []
         for req in list(self.waiting_queue):
-            if slots <= 0 or budget <= 0 or free_pages <= 0:
+            if budget <= 0 or free_pages <= 0 or (req.slot is None and slots <= 0):
                 break
             needed = len(req.fill_ids) - req.seq_len
             held = pages_for(req.seq_len, page)
@@ -257,7 +268,7 @@ class Scheduler:
             req.is_chunked = take < needed
             selected.append(req)
             budget -= take
-            slots -= 1
+            slots -= req.slot is None
             free_pages -= pages_for(req.seq_len + take, page) - held
             if req.is_chunked:
                 break                      # the rest of this prompt comes before any later request

@@ -221,6 +221,88 @@ def test_overlap_schedule_changes_no_output(setup):
     assert s.runner.cache.held_pages() == [0] and s.runner.cache.slots.available == 8
 
 
+def test_slots_count_requests_whose_last_token_is_in_flight(setup):
+    """With every slot taken and requests ending by their length limit while others wait, a new
+    request is admitted only when a slot has really come back (the ending request keeps its slot
+    until its last token is read)."""
+    cfg, weights, path = setup
+    ps = prompts(cfg, [5, 9, 3, 12, 7, 4, 8, 6, 10, 2], seed=70)
+    outs = {}
+    for overlap in (False, True):
+        s = scheduler(path, max_requests=2, overlap=overlap)
+        for i, p in enumerate(ps):
+            s.add_request(f"r{i}", p, SamplingParams(max_new_tokens=1 + i % 3, ignore_eos=True))
+        s.run_to_completion()
+        assert s.runner.cache.slots.available == 2 and s.runner.cache.held_pages() == [0]
+        outs[overlap] = {k: (v.output_ids, v.finish_reason) for k, v in s.results.items()}
+        assert all(len(outs[overlap][f"r{i}"][0]) == 1 + i % 3 for i in range(len(ps)))
+    assert outs[False] == outs[True]
+
+
+def test_a_prompt_still_filling_gives_its_pages_back_before_a_running_request_ends(setup):
+    """One request decodes, another waits with part of its prompt cached and holds the rest of the
+    pool: the decoding one is not cut short ("KV cache exhausted" is for a request that is alone);
+    the filling one starts again later and both end as asked."""
+    cfg, weights, path = setup
+    a, b = prompts(cfg, [14, 120], seed=71)
+    s = scheduler(path, max_tokens=160, page_size=16, chunked_prefill_size=32)
+    s.add_request("a", a, SamplingParams(max_new_tokens=60, ignore_eos=True))
+    s.step()
+    s.add_request("b", b, SamplingParams(max_new_tokens=4, ignore_eos=True))
+    s.run_to_completion()
+    assert s.retractions >= 1
+    for rid, p, n in (("a", a, 60), ("b", b, 4)):
+        r = s.results[rid]
+        assert r.finish_reason == {"type": "length"} and r.output_ids == plain_impl.greedy_generate(cfg, weights, p, n), rid
+    assert s.runner.cache.held_pages() == [0]
+
+
+@pytest.mark.parametrize("seed", [2, 4, 14])
+def test_random_arrivals_overlap_equals_reading_first(setup, seed):
+    """Random workloads (staggered arrivals, every kind of sampling parameters, small pools, few
+    slots, prompt portions of several sizes): launching ahead changes no token and no finish
+    reason, nothing is left held, and no request is refused a slot."""
+    import random
+    cfg, weights, path = setup
+
+    def one(overlap):
+        rnd = random.Random(seed)
+        s = scheduler(path, max_tokens=rnd.choice([160, 320, 1024]), max_requests=rnd.choice([4, 8, 16]),
+                      overlap=overlap, chunked_prefill_size=rnd.choice([32, 64, 128, 8192]))
+        reqs = []
+        for i in range(rnd.randint(20, 50)):
+            p = tiny_models.random_tokens(rnd.choice([1, 2, 3, 5, 17, 40, 100, 150]), cfg["vocab_size"], seed * 1000 + i)
+            kind = rnd.random()
+            kw = dict(max_new_tokens=rnd.choice([1, 2, 5, 17, 40]), seed=i)
+            if 0.3 <= kind < 0.6:
+                kw.update(temperature=rnd.choice([0.5, 1.0, 1.5]), top_p=rnd.choice([1.0, 0.9]), top_k=rnd.choice([-1, 20]))
+            elif 0.6 <= kind < 0.7:
+                kw.update(repetition_penalty=1.2)
+            elif 0.7 <= kind < 0.8:
+                kw.update(temperature=1.0, logprobs=True)
+            elif 0.8 <= kind < 0.9:
+                kw.update(top_logprobs=3)
+            elif kind >= 0.9:
+                kw.update(temperature=1.0, stop_token_ids=[rnd.randrange(cfg["vocab_size"]) for _ in range(40)])
+            if rnd.random() < 0.8:
+                kw["ignore_eos"] = kind < 0.9
+            reqs.append((f"r{i}", p, SamplingParams(**kw)))
+        waiting = list(reqs)
+        for _ in range(20000):
+            for _ in range(rnd.randint(0, 3)):
+                if waiting:
+                    s.add_request(*waiting.pop(0))
+            if not s.step() and not waiting:
+                break
+        assert not s.has_work() and not waiting and s.runner.cache.held_pages() == [0]
+        assert s.runner.cache.slots.available == s.runner.max_requests
+        return {rid: (s.results[rid].output_ids, s.results[rid].finish_reason) for rid, _, _ in reqs}, s
+
+    (a, sa), (b, sb) = one(False), one(True)
+    assert a == b
+    assert sb.overlapped_steps > 20 and sa.overlapped_steps == 0
+
+
 def test_top_logprobs_follow_the_plain_log_softmax(setup):
     cfg, weights, path = setup
     p = prompts(cfg, [9], seed=45)[0]
