@@ -69,6 +69,37 @@ def test_head_size_128_paths_inside_the_engine(dtype):
             assert ops.attention_tc_status() == 0 and ops.gemm_tc_status() == 0          # no bounded wait gave up
 
 
+@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_configurations_in_every_cutting(seed, dtype):
+    """Configurations drawn at random (head counts and groups, head sizes in steps of 16, widths and vocabularies
+    that are no power of two, page sizes 16 to 64): whole, last 32 one by one, random portions down to two tokens,
+    and mixed over a pool so small that pages are used again."""
+    import random
+    cfg = tiny_models.random_config(seed)
+    r = random.Random(seed + 999)
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, seed, tmp)
+        v = cfg["vocab_size"]
+        n, page = r.choice([70, 150, 260]), r.choice([16, 32, 64])
+        ids = tiny_models.random_tokens(n, v, seed)
+        others = {k: tiny_models.random_tokens(m, v, seed * 7 + i) for i, (k, m) in enumerate((("b", 60), ("c", 45), ("d", 70)))}
+        w = rounded(weights, dtype)
+        want = plain_impl.all_logits(cfg, w, ids)
+        pool = (-(-n // page) - (-60 // page) - (-45 // page) + 1) * page     # "d" fits only in what "b" gives back
+        runner = make_runner(path, dtype=dtype, device="cuda", page_size=page, max_tokens=pool, max_requests=4, context_length=1024)
+        close(run_whole(runner, ids), want, dtype, "whole")
+        close(run_portions(runner, ids, [n - 32] + [1] * 32), want, dtype, "last 32 one by one")
+        close(run_portions(runner, ids, [r.choice([2, 3, 5, 16, 17, 31, 64]) for _ in range(40)]), want, dtype, "portions")
+        plan = [{"a": n // 2, "b": 20}, {"a": n // 4, "b": 2, "c": 30}, {"a": 1, "b": 38, "c": 1}] + [{"a": 1, "c": 1, "d": 4}] * 14 + \
+               [{"a": n, "c": 9, "d": 14}]
+        got = run_mixed(runner, {"a": ids, **others}, plan, ends={2: ["b"]})
+        close(got["a"], want, dtype, "a")
+        for k, toks in others.items():
+            close(got[k], plain_impl.all_logits(cfg, w, toks)[:got[k].shape[0]], dtype, k)
+        assert runner.cache.held_pages() == [0]
+
+
 def test_pages_whose_offset_passes_two_to_the_31_elements():
     """A pool of 8.9 GB in which the request's pages lie past element 2^31 of a layer's cache (16 requests that only
     hold pages fill the front of the pool): the same logits, bit for bit, as in a small pool, through the

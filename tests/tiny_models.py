@@ -113,6 +113,31 @@ MID_QWEN3 = {
     "torch_dtype": "float32",
 }
 
+def random_config(seed: int) -> dict:
+    """A configuration drawn from everything the architecture's config.json can say: 1 to 4 kv heads with 1 to 8
+    query heads each, head sizes from 16 to 256 in steps of 16, widths and intermediate sizes in steps of 8,
+    any vocabulary, 1 to 3 layers, either family, with or without llama3 rope scaling, bias and a tied head."""
+    import random
+    r = random.Random(seed)
+    qwen = r.random() < 0.5
+    nkv = r.choice([1, 2, 3, 4])
+    cfg = {
+        "architectures": ["Qwen3ForCausalLM" if qwen else "LlamaForCausalLM"], "model_type": "qwen3" if qwen else "llama",
+        "num_hidden_layers": r.randint(1, 3), "hidden_size": 8 * r.randint(8, 80),
+        "num_attention_heads": nkv * r.choice([1, 2, 3, 4, 5, 8]), "num_key_value_heads": nkv,
+        "head_dim": r.choice([16, 32, 48, 64, 80, 96, 112, 128, 160, 192, 256]),
+        "intermediate_size": 8 * r.randint(8, 200), "vocab_size": r.randint(100, 3000),
+        "rope_theta": r.choice([1e4, 3e4, 5e5, 1e6]), "rms_norm_eps": r.choice([1e-6, 3e-6, 1e-5]),
+        "tie_word_embeddings": r.random() < 0.5, "max_position_embeddings": 1024, "torch_dtype": "float32",
+    }
+    if r.random() < 0.4:
+        cfg["rope_scaling"] = {"rope_type": "llama3", "factor": r.choice([2.0, 4.0, 8.0]), "low_freq_factor": 1.0,
+                               "high_freq_factor": r.choice([2.0, 4.0]), "original_max_position_embeddings": r.choice([32, 64, 128])}
+    if r.random() < 0.3:
+        cfg["attention_bias"] = True
+    return cfg
+
+
 CONFIGS = {"tiny_qwen3": TINY_QWEN3, "tiny_llama": TINY_LLAMA, "odd_qwen3": ODD_QWEN3, "odd_llama": ODD_LLAMA}
 
 
