@@ -136,7 +136,7 @@ def test_skinny_gemm_partial_sums(m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 6144, 4096), (300, 1000, 136), (65, 331, 200), (1, 24, 8),
-                                   (777, 512, 4096), (129, 257, 72)])
+                                   (777, 512, 4096), (129, 257, 72), (1100, 5000, 520), (2048, 4096, 12288), (4100, 2500, 72)])
 def test_gemm_tcgen05(m, n, k):
     o = ops()
     g = torch.Generator(device=DEV).manual_seed(13)
@@ -151,6 +151,7 @@ def test_gemm_tcgen05(m, n, k):
     assert float((got.float() - want).abs().max()) <= float(want.abs().max()) * 2 ** -7
     torch.testing.assert_close(o.gemm_tc(x, w, b).float(), want + b.float(), atol=2e-2 * (k ** 0.5) + 0.1, rtol=1e-2)
     assert o.gemm_tc_status() == 0
+    assert torch.equal(o.gemm_tc(x, w), got) and o.gemm_tc_status() == 0          # again: the same bits
 
 
 @pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (2048, 12288, 4096), (300, 384, 136), (70, 256, 4096)])
