@@ -982,9 +982,7 @@ LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out,
     p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
     // two heads of a kv head a block when the group size is even and, unless the caller says which, when
     // that still leaves a block for every SM (short prompts fill the device better with a head a block)
-    int sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const int sms = sm_count();
     const bool even = (nq / nkv) % 2 == 0;
     LILY_REQUIRE(heads_per_block >= 0 && heads_per_block <= 2 && (heads_per_block != 2 || even),
                  "attention_prefill_tc: %d heads a block with %d query heads per kv head", heads_per_block, nq / nkv);

@@ -578,7 +578,7 @@ LILY_API int lily_silu_mul(const void* gate_up, void* out, int tokens, int inter
     if (check_summed("silu_mul", act_dtype, in_dtype, splits)) return 1;
     const bool vec = block % 4 == 0 && stride % 4 == 0 && aligned16(gate_up) && aligned16(out);
     const size_t work = vec ? total / 4 : total;
-    const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
+    const int blocks = (int)((work + 255) / 256 < sm_count() * 16 ? (work + 255) / 256 : sm_count() * 16);
 #define GO(T, IN, V) launch_pdl(silu_mul_kernel<T, IN, V>, dim3(blocks), dim3(256), 0, stream, Summed<IN>{(const IN*)gate_up, splits, stride}, (T*)out, inter, block, total)
     if (act_dtype == kBF16 && in_dtype == kBF16) { if (vec) GO(__nv_bfloat16, __nv_bfloat16, 4); else GO(__nv_bfloat16, __nv_bfloat16, 1); }
     else if (act_dtype == kBF16) { if (vec) GO(__nv_bfloat16, float, 4); else GO(__nv_bfloat16, float, 1); }
@@ -644,7 +644,7 @@ LILY_API int lily_qk_norm_rope_write(const void* qkv, const void* q_gain, const 
 
 LILY_API int lily_cast(const void* in, int in_dtype, void* out, int out_dtype, size_t n, cudaStream_t stream) {
     if (n == 0) return 0;
-    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    const int blocks = (int)((n + 255) / 256 < sm_count() * 16 ? (n + 255) / 256 : sm_count() * 16);
     if (in_dtype == kBF16 && out_dtype == kF32)
         cast_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, n);
     else if (in_dtype == kF32 && out_dtype == kBF16)

@@ -40,7 +40,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 // NT: 8-token tiles (M <= 8 * NT).  MT: 16-row tiles of w per warp.  WARPS per block.  KT: k per
-// tile (64 or 256: 128 or 512 contiguous bytes of each row per copy round).
+// tile (64: 128 contiguous bytes of each row per copy round).
 template <int NT, int MT, int WARPS, int STAGES, int KT>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
@@ -149,16 +149,12 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 struct Shape {
     int nt, mt, warps, stages, kt;
 };
-// Tiles of 256 k (512 contiguous bytes of a row per copy round) measured no faster than tiles of
-// 64 k with these ring sizes and cost shared memory that x's slice needs; they stay switched off.
-static Shape shape_for(int M, int K, int N = 0) {
-    // a wide product whose 256-row blocks fit the SMs in one wave runs one big block per SM, whole k
-    // (measured on 8 x 24576 x 4096: 41.9 us against the library's 35.6 us, so it stays switched off)
-    if (false && M <= 8 && N > 148 * 128 && N <= 148 * 256 && (size_t)8 * 5 * 32 * KB * 2 + (size_t)8 * K * 2 <= 224 * 1024)
-        return Shape{1, 2, 8, 5, 64};
-    const bool wide = false && K % 256 == 0;
-    if (M <= 8) return wide ? Shape{1, 1, 4, 3, 256} : Shape{1, 1, 8, 5, 64};
-    if (M <= 16) return wide ? Shape{2, 1, 4, 3, 256} : Shape{2, 1, 8, 5, 64};
+// Measured and not kept: tiles of 256 k (512 contiguous bytes of a row per copy round) were no faster than
+// tiles of 64 k and cost shared memory that x's slice needs; one 256-row block per SM over the whole k for a
+// wide product (8 x 24576 x 4096) took 41.9 us against the library's 35.6 us.
+static Shape shape_for(int M) {
+    if (M <= 8) return {1, 1, 8, 5, 64};
+    if (M <= 16) return {2, 1, 8, 5, 64};
     if (M <= 32) return {4, 2, 4, 5, 64};
     return {8, 2, 4, 5, 64};
 }
@@ -201,12 +197,11 @@ LILY_API int lily_skinny_gemm_max_rows() { return 64; }
 // products, which the library streams well without cutting k, and more than 16 tokens to it.
 LILY_API int lily_skinny_gemm_splits(int M, int N, int K) {
     if (K % skinny::KB != 0 || M < 1 || M > 16 || K < skinny::KB) return 0;
-    const skinny::Shape sh = skinny::shape_for(M, K, N);
+    const skinny::Shape sh = skinny::shape_for(M);
     const int rows_per_block = sh.warps * 16 * sh.mt;
     const int row_blocks = (N + rows_per_block - 1) / rows_per_block;
     const int tiles = K / sh.kt;
-    const int held = 148 * 2;
-    if (sh.mt == 2 && M <= 8) return 1;                  // the one-block-per-SM shape: no split
+    const int held = sm_count() * 2;
     if (row_blocks > held / 2) return 0;
     int s = held / row_blocks;
     const int longest = tiles * sh.kt / 512 > 0 ? tiles * sh.kt / 512 : 1;      // slices of at least 512 k
@@ -220,17 +215,14 @@ LILY_API int lily_skinny_gemm(const void* x, const void* w, float* parts, int M,
     if (M == 0 || N == 0) return 0;
     LILY_REQUIRE(M >= 1 && M <= 64, "skinny_gemm: %d tokens (takes 1..64)", M);
     LILY_REQUIRE(K > 0 && K % skinny::KB == 0, "skinny_gemm: K=%d is not a multiple of %d", K, skinny::KB);
-    const skinny::Shape sh = skinny::shape_for(M, K, N);
+    const skinny::Shape sh = skinny::shape_for(M);
     LILY_REQUIRE(ksplit >= 1 && ksplit <= K / sh.kt, "skinny_gemm: %d slices of K=%d", ksplit, K);
     LILY_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "skinny_gemm: operands must be 16-byte aligned");
     const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
     int rc;
-    if (M <= 8 && sh.mt == 2) rc = skinny::launch<1, 2, 8, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
-    else if (M <= 8) rc = sh.kt == 256 ? skinny::launch<1, 1, 4, 3, 256>(xp, wp, parts, M, N, K, ksplit, stream)
-                                  : skinny::launch<1, 1, 8, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
-    else if (M <= 16) rc = sh.kt == 256 ? skinny::launch<2, 1, 4, 3, 256>(xp, wp, parts, M, N, K, ksplit, stream)
-                                        : skinny::launch<2, 1, 8, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
+    if (M <= 8) rc = skinny::launch<1, 1, 8, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
+    else if (M <= 16) rc = skinny::launch<2, 1, 8, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
     else if (M <= 32) rc = skinny::launch<4, 2, 4, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
     else rc = skinny::launch<8, 2, 4, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
     if (rc) return rc;

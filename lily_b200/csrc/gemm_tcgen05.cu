@@ -480,16 +480,6 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld,
     return 0;
 }
 
-static int sm_count() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    return sms;
-}
-
 // LILY_B200_GEMM_PAIR=0 keeps every product on the one-block kernel.
 static bool pair_enabled() {
     static const bool on = [] {

@@ -506,7 +506,7 @@ using namespace lily;
 // rows * chunks floats and as many ints when it is more than 1.
 LILY_API int lily_argmax_chunks(int rows, int vocab) {
     if (vocab < 16384) return 1;
-    int chunks = (148 * 4 + rows - 1) / (rows > 0 ? rows : 1);
+    int chunks = (sm_count() * 4 + rows - 1) / (rows > 0 ? rows : 1);
     const int most = vocab / 2048;
     chunks = chunks > most ? most : chunks;
     return chunks < 1 ? 1 : (chunks > 256 ? 256 : chunks);

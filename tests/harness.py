@@ -3,7 +3,6 @@
 from __future__ import annotations
 
 import os
-import tempfile
 from typing import Dict, List, Sequence
 
 import torch

@@ -8,7 +8,6 @@ compute in float32 and round once to the output dtype.  Nothing in ``lily_b200``
 
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 

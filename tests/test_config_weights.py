@@ -9,11 +9,10 @@ import torch
 from safetensors.torch import load_file, save_file
 
 import tiny_models
-from lily_b200.config import (ConfigError, DenseDecoderConfig, ServerArgs, register_architecture,
-                              resolve_architecture, supported_architectures)
+from lily_b200.config import ConfigError, DenseDecoderConfig, ServerArgs, resolve_architecture, supported_architectures
 from lily_b200.models.assembled import AssembledModel
 from lily_b200.parts.base import BuildContext, TensorSpec
-from lily_b200.weights.loader import CheckpointSource, WeightsError, check, kept_dtype, load_model_weights
+from lily_b200.weights.loader import CheckpointSource, WeightsError, kept_dtype, load_model_weights
 from lily_b200.weights.random_init import RandomSource, expected_tensors, write_random_model
 from lily_b200.weights.safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
 

@@ -7,7 +7,6 @@ import tempfile
 import pytest
 import torch
 
-import kernel_refs
 import plain_impl
 import tiny_models
 from harness import make_runner, model_dir

@@ -7,7 +7,6 @@ Each toy is checked against a plain whole-sequence statement written beside it. 
 use the kernels' PyTorch statements as ops; the ``gpu`` variants use the CUDA kernels.
 """
 
-import tempfile
 from dataclasses import dataclass
 
 import pytest

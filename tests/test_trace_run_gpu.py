@@ -4,7 +4,6 @@ logits read back from the files it writes."""
 import json
 import os
 import subprocess
-import sys
 import tempfile
 
 import numpy as np
