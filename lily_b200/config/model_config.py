@@ -121,6 +121,13 @@ class DenseDecoderConfig:
             theta = rope_params.get("rope_theta", theta)
             if rope_params.get("rope_type", "default") != "default":
                 rope_scaling = dict(rope_params)
+        # options of other decoders that this architecture's code does not have (lily/models/llama.py:36-38 has no
+        # MLP bias; its attention sees every earlier key): a file that turns one on would get other results
+        if text.get("mlp_bias"):
+            raise ConfigError("mlp_bias is set: this architecture's feed-forward has no bias")
+        if text.get("use_sliding_window") and text.get("sliding_window"):
+            raise ConfigError(f"use_sliding_window is set (window {text.get('sliding_window')}): this architecture "
+                              "attends to every earlier key")
         eos = (generation or {}).get("eos_token_id", text.get("eos_token_id"))
         eos_ids = [] if eos is None else [int(eos)] if isinstance(eos, int) else [int(e) for e in eos]
         out = cls(

@@ -55,6 +55,38 @@ def test_registry():
         resolve_architecture(["GPT2LMHeadModel"])
 
 
+def test_files_of_real_checkpoints_parse_and_foreign_options_are_refused():
+    """The keys a published Qwen3 / Llama-3.1 config.json carries beside the sizes (dropout, window switches that are off,
+    library version, a null rope_scaling, a list of end tokens) are read or passed over; an option this architecture's
+    code does not have is refused when it is switched on."""
+    qwen = {"architectures": ["Qwen3ForCausalLM"], "attention_bias": False, "attention_dropout": 0.0, "bos_token_id": 151643,
+            "eos_token_id": 151645, "head_dim": 128, "hidden_act": "silu", "hidden_size": 4096, "initializer_range": 0.02,
+            "intermediate_size": 12288, "max_position_embeddings": 40960, "max_window_layers": 36, "model_type": "qwen3",
+            "num_attention_heads": 32, "num_hidden_layers": 36, "num_key_value_heads": 8, "rms_norm_eps": 1e-06,
+            "rope_scaling": None, "rope_theta": 1000000, "sliding_window": None, "tie_word_embeddings": False,
+            "torch_dtype": "bfloat16", "transformers_version": "4.51.0", "use_cache": True, "use_sliding_window": False,
+            "vocab_size": 151936}
+    llama = {"architectures": ["LlamaForCausalLM"], "attention_bias": False, "attention_dropout": 0.0, "bos_token_id": 128000,
+             "eos_token_id": [128001, 128008, 128009], "hidden_act": "silu", "hidden_size": 4096, "initializer_range": 0.02,
+             "intermediate_size": 14336, "max_position_embeddings": 131072, "mlp_bias": False, "model_type": "llama",
+             "num_attention_heads": 32, "num_hidden_layers": 32, "num_key_value_heads": 8, "pretraining_tp": 1,
+             "rms_norm_eps": 1e-05, "rope_scaling": {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                                     "original_max_position_embeddings": 8192, "rope_type": "llama3"},
+             "rope_theta": 500000.0, "tie_word_embeddings": False, "torch_dtype": "bfloat16", "use_cache": True, "vocab_size": 128256}
+    q = DenseDecoderConfig.from_dict(qwen)
+    assert (q.qk_norm, q.head_dim, q.rope_theta, q.rope_scaling.rope_type, q.eos_token_ids) == (True, 128, 1e6, "default", [151645])
+    l = DenseDecoderConfig.from_dict(llama)
+    assert (l.qk_norm, l.head_dim, l.rope_scaling.rope_type, l.rope_scaling.factor, l.eos_token_ids) == \
+        (False, 128, "llama3", 8.0, [128001, 128008, 128009])
+    newer = {k: v for k, v in qwen.items() if k not in ("torch_dtype", "rope_theta", "rope_scaling")}
+    newer.update(dtype="bfloat16", rope_parameters={"rope_theta": 1000000, "rope_type": "default"}, layer_types=["full_attention"] * 36)
+    assert DenseDecoderConfig.from_dict(newer) == q
+    for bad, word in (({**llama, "mlp_bias": True}, "mlp_bias"), ({**qwen, "use_sliding_window": True, "sliding_window": 4096}, "sliding"),
+                      ({**qwen, "hidden_act": "gelu"}, "activation"), ({**llama, "rope_scaling": {"rope_type": "yarn", "factor": 4.0}}, "yarn")):
+        with pytest.raises(ConfigError, match=word):
+            DenseDecoderConfig.from_dict(bad)
+
+
 def test_server_args_flags_and_checks():
     a = ServerArgs.parse(["--model-path", "x", "--dtype", "float32", "--chunked-prefill-size", "64",
                           "--max-total-tokens", "4096", "--disable-cuda-graph", "--cuda-graph-bs", "1", "8"])
