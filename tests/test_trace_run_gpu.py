@@ -73,3 +73,19 @@ def test_replay_mixed_trace(name, dtype):
                 for w in e["want"]:
                     close(rows[i][at:at + 1], plain[k][start + w:start + w + 1], dtype, f"step {i} request {k} place {w}")
                     at += 1
+
+
+def test_replay_past_the_files_max_position():
+    """A request of 300 tokens through a model whose config.json says max_position_embeddings 256: the pool
+    (--max-tokens) bounds a request, not that number."""
+    cfg = tiny_models.CONFIGS["tiny_qwen3"]
+    v = cfg["vocab_size"]
+    assert cfg["max_position_embeddings"] == 256
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 72, tmp)
+        ids = tiny_models.random_tokens(300, v, 9)
+        steps = [{"step": 0, "entries": [{"id": "a", "tokens": ids[:268], "want": [267]}], "end": []}] + \
+                [{"step": i, "entries": [{"id": "a", "tokens": ids[267 + i:268 + i], "want": [0]}], "end": []} for i in range(1, 33)]
+        rows = replay(path, "float32", steps, 320, tmp, v)
+        got = torch.cat([rows[i] for i in range(33)])
+        close(got, plain_impl.all_logits(cfg, weights, ids)[267:], "float32", "positions 267 to 299")
