@@ -17,12 +17,15 @@
 #include "attention_args.cuh"
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 namespace lily {
-
-
 namespace mma {
 
+namespace cg = cooperative_groups;
+
 constexpr int BN = 64;        // keys per tile
+constexpr int MAX_CLUSTER = 16;      // blocks of a cluster that merges the splits of a decode row
 constexpr int THREADS = 128;
 #ifndef LILY_DECODE_STAGES
 #define LILY_DECODE_STAGES 2
@@ -62,7 +65,18 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * (D * 2) + ((((chunk ^ row) & 7) | (chunk & ~7)) << 4));
 }
 
-template <int D, bool DECODE, int STAGES>
+// Shared memory of one block: the key/value stages (reused for the merge of the four warps), then, when a
+// cluster merges the splits (CLUSTER), what the other blocks of the cluster send: per split this block's share
+// of the output sums, and per split and row (max, sum).
+template <int D, int STAGES>
+__host__ __device__ constexpr size_t stage_bytes(bool decode) {
+    const size_t stages = 2 * (size_t)STAGES * BN * D * 2, merge = (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
+    return decode && merge > stages ? merge : stages;
+}
+// Output sums a block of a cluster of `splits` blocks merges: its share of rows x D.
+__host__ __device__ inline int cluster_share(int rows, int d, int splits) { return (rows * d + splits - 1) / splits; }
+
+template <int D, bool DECODE, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS, D <= 128 ? 3 : 1)
 attention_mma_kernel(const AttnArgs a, const int page_shift) {
     constexpr int CH = D / 8;                  // 16-byte pieces per row
@@ -334,6 +348,14 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
     }
     __syncthreads();
     const float ln2 = 0.6931471805599453f;
+    // CLUSTER: the blocks of the cluster hold the splits of one (request, kv head); each sends every other its
+    // share of the merged sums through distributed shared memory, and after one cluster barrier each block
+    // finishes its share of the output, so that neither scratch in global memory nor a combine kernel is needed
+    cg::cluster_group cluster = cg::this_cluster();
+    const int splits = a.splits, me = blockIdx.z;
+    const int share = cluster_share(min(16, group), D, splits);
+    float* recv_o = reinterpret_cast<float*>(smem_raw + stage_bytes<D, STAGES>(true));     // [splits][share]
+    float* recv_ml = recv_o + (size_t)splits * share;                                        // [splits][16][2]
     for (int i = tid; i < nrows * D; i += THREADS) {
         const int r = i / D, col = i % D;
         float mx = -INFINITY;
@@ -350,7 +372,15 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
             }
         }
         const int head = head0 + r;
-        if (a.splits > 1) {
+        if (CLUSTER) {
+            const int owner = i / share;
+            cluster.map_shared_rank(recv_o, owner)[me * share + (i - owner * share)] = acc;
+            if (col < splits) {                            // column p of the row tells block p the row's (max, sum)
+                float* ml = cluster.map_shared_rank(recv_ml, col) + (me * 16 + r) * 2;
+                ml[0] = mx;
+                ml[1] = den;
+            }
+        } else if (a.splits > 1) {
             const size_t base = ((size_t)tok0 * a.nq + head) * a.splits + blockIdx.z;
             a.part_o[base * D + col] = acc;
             if (col == 0) {
@@ -362,16 +392,118 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
                 __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
         }
     }
+    if (CLUSTER) {
+        cluster.sync();                                     // every block's sums have arrived; nobody is written to after this
+        for (int slot = tid; slot < share; slot += THREADS) {
+            const int i = me * share + slot;
+            if (i >= nrows * D) break;
+            const int r = i / D, col = i % D;
+            float mx = -INFINITY;
+            for (int sp = 0; sp < splits; ++sp) mx = fmaxf(mx, recv_ml[(sp * 16 + r) * 2]);
+            float acc = 0.f, den = 0.f;
+            for (int sp = 0; sp < splits; ++sp) {           // in the order of the splits, whichever block merges
+                const float ms = recv_ml[(sp * 16 + r) * 2];
+                if (ms > -INFINITY) {
+                    const float f = exp2f(ms - mx);
+                    acc += recv_o[sp * share + slot] * f;
+                    den += recv_ml[(sp * 16 + r) * 2 + 1] * f;
+                }
+            }
+            ((__nv_bfloat16*)a.out)[((size_t)tok0 * a.nq + head0 + r) * D + col] =
+                __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+        }
+    }
 }
 
-template <int D, bool DECODE, int STAGES>
-static int launch(const AttnArgs& a, dim3 grid, int page_shift, cudaStream_t stream) {
-    size_t smem = 2 * (size_t)STAGES * BN * D * 2;
-    if (DECODE) {
-        const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
-        if (merge > smem) smem = merge;
+// Raises the kernel's dynamic shared memory limit to `bytes` if it is lower (never lowers it).
+template <int D, int STAGES>
+static bool cluster_smem(size_t bytes) {
+    static size_t granted = 0;
+    if (bytes > granted) {
+        if (cudaFuncSetAttribute(attention_mma_kernel<D, true, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)bytes) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        granted = bytes;
     }
-    auto kern = attention_mma_kernel<D, DECODE, STAGES>;
+    return true;
+}
+
+// How many clusters of `splits` blocks of the decode kernel the device holds at once (asked once per head
+// size and cluster size; 0: such a cluster cannot be placed).
+template <int D, int STAGES>
+static int cluster_capacity(int splits, size_t smem) {
+    static int known[MAX_CLUSTER + 1] = {};                     // 0 not asked, -1 none, else the count
+    if (known[splits] == 0) {
+        int clusters = 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, splits);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = splits;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        // more than 8 blocks a cluster is a size the device has to allow explicitly
+        const bool ok = cluster_smem<D, STAGES>(smem) &&
+                        (splits <= 8 || cudaFuncSetAttribute(attention_mma_kernel<D, true, STAGES, true>,
+                                                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) &&
+                        cudaOccupancyMaxActiveClusters(&clusters, attention_mma_kernel<D, true, STAGES, true>, &cfg) == cudaSuccess &&
+                        clusters > 0;
+        if (!ok) cudaGetLastError();
+        known[splits] = ok ? clusters : -1;
+    }
+    return known[splits] > 0 ? known[splits] : 0;
+}
+
+// LILY_B200_DECODE_CLUSTER=0 keeps the splits on scratch and the combine kernel.
+static bool cluster_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("LILY_B200_DECODE_CLUSTER");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
+// Returns 0 on success, and in `merged` whether the kernel itself merged the splits into `out`.
+template <int D, bool DECODE, int STAGES>
+static int launch(const AttnArgs& a, dim3 grid, int page_shift, cudaStream_t stream, bool* merged) {
+    size_t smem = stage_bytes<D, STAGES>(DECODE);
+    // clusters pay when all of them are resident at once; over several rounds of blocks their placement costs
+    // more than the combine kernel (measured: 32 requests x 8 kv heads x 7 splits 116 against 103 us)
+    if (DECODE && a.splits >= 2 && a.splits <= MAX_CLUSTER && cluster_enabled()) {
+        const int rows = a.nq / a.nkv < 16 ? a.nq / a.nkv : 16;
+        const size_t with_recv = smem + ((size_t)a.splits * cluster_share(rows, D, a.splits) + (size_t)a.splits * 16 * 2) * sizeof(float);
+        if ((long)grid.x * grid.y <= cluster_capacity<D, DECODE ? STAGES : 2>(a.splits, with_recv)) {
+            auto kern = attention_mma_kernel<D, true, DECODE ? STAGES : 2, true>;
+            if (!cluster_smem<D, DECODE ? STAGES : 2>(with_recv)) {
+                set_error("attention_mma: cannot get %zu bytes of shared memory", with_recv);
+                return 2;
+            }
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = grid;
+            cfg.blockDim = dim3(THREADS);
+            cfg.dynamicSmemBytes = with_recv;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[2];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = a.splits;
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = pdl_enabled() ? 2 : 1;
+            cudaLaunchKernelEx(&cfg, kern, a, page_shift);
+            *merged = true;
+            return 0;
+        }
+    }
+    auto kern = attention_mma_kernel<D, DECODE, STAGES, false>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -382,11 +514,12 @@ static int launch(const AttnArgs& a, dim3 grid, int page_shift, cudaStream_t str
         configured = true;
     }
     launch_pdl(kern, grid, dim3(THREADS), smem, stream, a, page_shift);
+    *merged = false;
     return 0;
 }
 
 template <bool DECODE>
-static int dispatch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
+static int dispatch(const AttnArgs& a, dim3 grid, cudaStream_t stream, bool* merged) {
     int page_shift = 0;
     while ((1 << page_shift) < a.page_size) ++page_shift;
     if ((1 << page_shift) != a.page_size) {
@@ -395,10 +528,10 @@ static int dispatch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
     }
     constexpr int ST = DECODE ? LILY_DECODE_STAGES : 2;
     switch (a.d) {
-        case 64: return launch<64, DECODE, ST>(a, grid, page_shift, stream);
-        case 128: return launch<128, DECODE, ST>(a, grid, page_shift, stream);
-        case 192: return launch<192, DECODE, DECODE ? 2 : 2>(a, grid, page_shift, stream);
-        case 256: return launch<256, DECODE, 2>(a, grid, page_shift, stream);
+        case 64: return launch<64, DECODE, ST>(a, grid, page_shift, stream, merged);
+        case 128: return launch<128, DECODE, ST>(a, grid, page_shift, stream, merged);
+        case 192: return launch<192, DECODE, 2>(a, grid, page_shift, stream, merged);
+        case 256: return launch<256, DECODE, 2>(a, grid, page_shift, stream, merged);
     }
     set_error("attention_mma: head_dim %d is not one of 64, 128, 192, 256", a.d);
     return 1;
@@ -425,15 +558,35 @@ LILY_API int lily_attention_prefill_mma(const void* q, const void* kv, void* out
     a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride;
     a.cu_seqlens = cu_seqlens; a.prefix_lens = prefix_lens; a.tile_req = tile_req; a.tile_start = tile_start;
     a.splits = 1; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
-    int rc = mma::dispatch<false>(a, dim3(tiles, nq), stream);
+    bool merged = false;
+    int rc = mma::dispatch<false>(a, dim3(tiles, nq), stream, &merged);
     if (rc) return rc;
     LILY_CHECK_LAUNCH("attention_prefill_mma");
     return 0;
 }
 
-// The partial results of splits > 1 go to `scratch` in the layout of attention_simt.cu
-// ([requests, nq, splits, d] outputs, then [requests, nq, splits, 2] (max, sum)); the caller runs
-// lily_attention_combine afterwards.
+extern "C" int lily_attention_combine(const float*, void*, int, int, int, int, int, cudaStream_t);
+
+// Clusters of `splits` blocks of the decode kernel that the device holds at once for this head size and
+// group size (0: none, or more splits than a cluster takes): with at most that many (request, kv head) pairs
+// the kernel merges the splits inside clusters.
+LILY_API int lily_attention_decode_mma_clusters(int d, int splits, int group) {
+    if (splits < 2 || splits > mma::MAX_CLUSTER || !mma::cluster_enabled()) return 0;
+    const int rows = group < 16 ? group : 16;
+    const size_t recv = ((size_t)splits * mma::cluster_share(rows, d, splits) + (size_t)splits * 16 * 2) * sizeof(float);
+    switch (d) {
+        case 64: return mma::cluster_capacity<64, LILY_DECODE_STAGES>(splits, mma::stage_bytes<64, LILY_DECODE_STAGES>(true) + recv);
+        case 128: return mma::cluster_capacity<128, LILY_DECODE_STAGES>(splits, mma::stage_bytes<128, LILY_DECODE_STAGES>(true) + recv);
+        case 192: return mma::cluster_capacity<192, 2>(splits, mma::stage_bytes<192, 2>(true) + recv);
+        case 256: return mma::cluster_capacity<256, 2>(splits, mma::stage_bytes<256, 2>(true) + recv);
+    }
+    return 0;
+}
+
+// One query token per request over its cached keys, the keys cut into `splits` ranges.  With 2 to 16 splits (and all blocks resident at once) the
+// blocks of a (request, kv head) form a cluster and merge their results through distributed shared memory; with
+// more, the partial results go to `scratch` in the layout of attention_simt.cu ([requests, nq, splits, d]
+// outputs, then [requests, nq, splits, 2] (max, sum)) and the combine kernel is launched behind.
 LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out, const int* block_table,
                                        int bt_stride, const int* seq_lens, float* scratch, int requests, int splits,
                                        int nq, int nkv, int d, int page_size, int window, float scale,
@@ -449,8 +602,10 @@ LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out,
     a.splits = splits; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
     a.part_o = scratch;
     a.part_ml = scratch ? scratch + (size_t)requests * nq * splits * d : nullptr;
-    int rc = mma::dispatch<true>(a, dim3(requests, nkv * chunks, splits), stream);
+    bool merged = false;
+    int rc = mma::dispatch<true>(a, dim3(requests, nkv * chunks, splits), stream, &merged);
     if (rc) return rc;
     LILY_CHECK_LAUNCH("attention_decode_mma");
+    if (splits > 1 && !merged) return lily_attention_combine(scratch, out, requests, nq, d, splits, kBF16, stream);
     return 0;
 }

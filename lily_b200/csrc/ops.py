@@ -404,6 +404,12 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
         _call("lily_attention_prefill_simt", *common, _dt(q), _stream())
 
 
+def decode_clusters(d: int, splits: int, group: int) -> int:
+    """How many (request, kv head) pairs the tensor-core decode attention can merge inside clusters of
+    ``splits`` blocks at once (0: it would use scratch and the combine kernel)."""
+    return int(library().lily_attention_decode_mma_clusters(int(d), int(splits), int(group)))
+
+
 def decode_scratch_floats(requests: int, nq: int, d: int, splits: int) -> int:
     return int(library().lily_attention_decode_scratch_floats(requests, nq, d, splits))
 
@@ -424,9 +430,9 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
               _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0),
               float(scale))
     if uses_tensor_cores(q.dtype, d):
-        _call("lily_attention_decode_mma", *common, _stream())
-        if splits > 1:
-            _call("lily_attention_combine", _p(scratch), _p(out), requests, nq, d, splits, _dt(q), _stream())
+        _call("lily_attention_decode_mma", *common, _stream())       # merges the splits itself (cluster, or combine behind)
+        if splits > 1 and requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv):
+            launches["count"] += 1                                   # the combine kernel, launched inside
     else:
         _call("lily_attention_decode_simt", *common, _dt(q), _stream())
         if splits > 1:

@@ -16,7 +16,7 @@ tokens in the flat token array); block tables replace ``req_to_token`` rows.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -125,17 +125,30 @@ def order_entries(entries: Sequence[StepEntry]) -> List[int]:
 
 
 def choose_decode_splits(num_decode: int, kv_heads: int, max_seq_len: int, sm_count: int = 148,
-                         blocks_per_sm: int = 3, min_keys: int = 256, max_splits: int = 32) -> int:
+                         blocks_per_sm: int = 3, min_keys: int = 256, max_splits: int = 32,
+                         clusters: Optional[Callable[[int], int]] = None) -> int:
     """How many ranges the keys of a decode row are cut into.  One block works on one (request, kv
-    head, range); the device holds ``sm_count * blocks_per_sm`` blocks at a time.  Measured on a
-    B200 (head size 128, 4096 keys): the fastest grid is the single wave that comes closest to
-    filling the device (batch 8: 6 to 7 ranges; batch 16: 3); when the rows alone overfill it, about
-    four waves (batch 64: 4 ranges).  The reference fixes 32 splits with a floor of 64 keys
+    head, range); the device holds ``sm_count * blocks_per_sm`` blocks at a time.
+
+    ``clusters(s)`` says how many clusters of ``s`` blocks the attention kernel can have resident at
+    once (``ops.decode_clusters``): while every (request, kv head) pair gets one, the blocks of a
+    pair merge their ranges through distributed shared memory and no combine kernel follows, and the
+    most ranges that allow this are the fastest (measured on a B200, head size 128, 8 kv heads:
+    batch 1 and 2: 16 ranges; 4: 10; 8: 6; 16: 3; 24: 2; sizes past 8 want a tenth of room to spare:
+    24 pairs in clusters of 15, of which exactly 24 fit, took 21 us against 16 us in clusters of 13).
+    Without that (float32, other head sizes, more pairs than clusters of two): the single wave that
+    comes closest to filling the device, and when the rows alone overfill it, about four waves
+    (batch 64: 4 ranges).  The reference fixes 32 splits with a floor of 64 keys
     (lily/layers/attention/triton_backend.py:21, decode_attention.py:68,172)."""
     if num_decode == 0:
         return 1
     limit = max(1, min(max_splits, max_seq_len // min_keys))
     pairs, held = num_decode * kv_heads, sm_count * blocks_per_sm
+    if clusters is not None:
+        for s in range(min(limit, 16), 1, -1):
+            room = clusters(s)
+            if pairs <= (room if s <= 8 else 0.9 * room):
+                return s
     one_wave = min(limit, held // pairs)
     if one_wave >= 1 and (pairs * one_wave >= 0.7 * held or one_wave == limit):
         return one_wave
@@ -146,7 +159,8 @@ def build_step_batch(entries: Sequence[StepEntry], prefix_lens: Sequence[int],
                      tables: Sequence[Sequence[Sequence[int]]], device, *, kv_heads_for_splits: int = 1,
                      workspace: Optional[Workspace] = None, pinned: Optional[torch.Tensor] = None,
                      table_widths: Optional[Sequence[int]] = None, decode_splits: Optional[int] = None,
-                     logit_rows: Optional[Sequence[int]] = None) -> StepBatch:
+                     logit_rows: Optional[Sequence[int]] = None,
+                     split_clusters: Optional[Callable[[int], int]] = None) -> StepBatch:
     """Packs a step.  ``entries`` are already ordered (one-token requests first);
     ``prefix_lens[i]`` positions of entry i are cached; ``tables[g][i]`` is the block table of
     entry i in cache group g (covering prefix + new tokens).  ``logit_rows`` (flat token indices)
@@ -204,7 +218,7 @@ def build_step_batch(entries: Sequence[StepEntry], prefix_lens: Sequence[int],
     parts = torch.split(dev, sizes) if total else [dev] * len(sizes)
     max_seq = max(seq_lens, default=0)
     splits = decode_splits if decode_splits is not None else choose_decode_splits(
-        num_decode, kv_heads_for_splits, max((seq_lens[i] for i in range(num_decode)), default=0))
+        num_decode, kv_heads_for_splits, max((seq_lens[i] for i in range(num_decode)), default=0), clusters=split_clusters)
     return StepBatch(
         num_tokens=n, num_requests=b, num_decode=num_decode,
         token_ids=parts[0], positions=parts[1], token_req=parts[2], cu_seqlens=parts[3], prefix_lens=parts[4],

@@ -76,7 +76,7 @@ class _DecodeGraph:
         self.static = torch.zeros(total, dtype=torch.int32, device=runner.device)
         self.copied: Optional[torch.cuda.Event] = None
         parts = torch.split(self.static, self.sizes)
-        splits = choose_decode_splits(b, runner._kv_heads, runner.context_len)
+        splits = choose_decode_splits(b, runner._kv_heads, runner.context_len, clusters=runner._split_clusters)
         self.batch = StepBatch(
             num_tokens=b, num_requests=b, num_decode=b, token_ids=parts[0], positions=parts[1], token_req=parts[2],
             cu_seqlens=parts[3], prefix_lens=parts[4], seq_lens=parts[5], slots=parts[6], logit_rows=parts[7],
@@ -184,6 +184,12 @@ class ModelRunner:
         self.seq_lens: Dict[int, int] = {}
         self._ring = _PinnedRing() if self.device.type == "cuda" else None
         self._kv_heads = max((need.kv_heads for need, _ in groups), default=1)
+        # how many clusters of s blocks the decode attention can keep resident (it then merges its key ranges inside
+        # them): asked of the kernels for the head size of the cache group with the most kv heads
+        self._split_clusters = None
+        if hasattr(ops, "decode_clusters") and self.dtype == torch.bfloat16 and groups:
+            head_dim = max(groups, key=lambda g: g[0].kv_heads)[0].head_dim
+            self._split_clusters = lambda s, d=head_dim: ops.decode_clusters(d, s, 1)
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
@@ -276,7 +282,8 @@ class ModelRunner:
             len(entries) * max((len(t) for t in g), default=1) for g in tables) + 8
         pinned, ring_index = self._ring.take(need) if self._ring is not None else (None, -1)
         batch = build_step_batch(ordered, prefix, tables, self.device, kv_heads_for_splits=self._kv_heads,
-                                 workspace=self.workspace, pinned=pinned, logit_rows=rows)
+                                 workspace=self.workspace, pinned=pinned, logit_rows=rows,
+                                 split_clusters=self._split_clusters)
         if self._ring is not None:
             self._ring.mark(ring_index)
         batch.future_tokens = self.future_tokens

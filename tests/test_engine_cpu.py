@@ -66,3 +66,15 @@ def test_wanted_rows_come_in_the_given_order(setup):
     la, lb = plain_impl.all_logits(cfg, weights, a), plain_impl.all_logits(cfg, weights, b)
     want = torch.stack([lb[4], lb[0], la[8]])
     assert float((out - want).abs().max()) < TOL
+
+
+def test_decode_splits_follow_the_clusters_that_fit():
+    """With the kernel's answer on how many clusters of s blocks fit (a B200's, head size 128), the most ranges
+    whose clusters are all resident; without it, or with more rows than clusters of two, the wave rule."""
+    from lily_b200.engine.batch import choose_decode_splits
+    room = {2: 222, 3: 142, 4: 104, 5: 82, 6: 71, 7: 56, 8: 48, 9: 45, 10: 41, 11: 31, 12: 31, 13: 28, 14: 24, 15: 24, 16: 21}
+    pick = lambda b, ctx=4096: choose_decode_splits(b, 8, ctx, clusters=lambda s: room.get(s, 0))
+    assert [pick(b) for b in (1, 2, 3, 4, 6, 8, 12, 16, 24)] == [16, 16, 13, 10, 8, 6, 4, 3, 2]
+    assert pick(1, 1024) == 4 and pick(8, 1024) == 4 and pick(8, 300) == 1            # at least 256 keys a range
+    assert pick(32) == choose_decode_splits(32, 8, 4096) == 7 and pick(64) == 4       # no cluster fits: the wave rule
+    assert choose_decode_splits(8, 8, 4096) == 6 and choose_decode_splits(0, 8, 4096) == 1

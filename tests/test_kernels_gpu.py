@@ -351,7 +351,7 @@ def test_attention_prefill_tcgen05_rising_scores():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("splits", [1, 3, 6, 7, 8, 12])
 @pytest.mark.parametrize("nq,nkv,d,page,window", [
     (4, 2, 16, 16, None), (8, 2, 32, 16, None), (6, 2, 48, 8, 40), (5, 1, 80, 32, None), (32, 8, 128, 64, None),
     (2, 2, 256, 16, 100), (40, 1, 32, 16, None), (16, 16, 64, 16, 7), (40, 2, 64, 16, None), (6, 2, 192, 32, 500),
