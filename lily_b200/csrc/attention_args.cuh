@@ -19,6 +19,20 @@ struct AttnArgs {
     int splits;
     int nq, nkv, d, page_size, window;
     float scale;
+    // decode, tensor-core kernel only: the qkv product as it leaves the projection (this kernel then norms and
+    // rotates its own query heads, and the block whose key range holds the new position does the same for the
+    // key, and writes key and value to the cache, before it reads them).  Null: `q` holds finished queries.
+    const void* qkv;          // [planes][requests, (nq + 2 nkv) d]: float32 partial sums, or bfloat16 with one plane
+    int qkv_planes, qkv_f32;
+    size_t qkv_stride;        // elements between planes
+    const void* q_gain;       // [d] per-head RMSNorm gains (both or none), float32 or bfloat16
+    const void* k_gain;
+    int gain_f32;
+    float eps;
+    const float* cos_t;       // [positions, rd / 2] (both or none)
+    const float* sin_t;
+    int rd;                   // rotary width
+    int write_kv;             // 0: the cache already holds this position (a layer that reads another layer's cache)
 };
 
 }  // namespace lily

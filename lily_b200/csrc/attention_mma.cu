@@ -174,6 +174,149 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
     }
 
     // ---- queries to shared memory (zero rows beyond nrows), then to A fragments -------------
+    if (DECODE && a.qkv != nullptr) {
+        // straight from the projection: a warp per head sums the planes, norms (lily/models/qwen3.py:27-29), rotates
+        // (lily/layers/rotary.py:18-20, 70-87) and rounds to bfloat16 as the separate kernel does; the block whose
+        // range holds this step's position also finishes the key and the value and writes them to their page
+        for (int i = tid; i < (BM - nrows) * CH; i += THREADS)
+            *reinterpret_cast<uint4*>(q_s + swz<D>(nrows + i / CH, i % CH)) = make_uint4(0, 0, 0, 0);
+        const size_t width = (size_t)(a.nq + 2 * a.nkv) * D;
+        auto in = [&](size_t idx) -> float {
+            if (!a.qkv_f32) return __bfloat162float(((const __nv_bfloat16*)a.qkv)[idx]);
+            const float* p = (const float*)a.qkv + idx;
+            float sum = 0.f;
+            for (int pl = 0; pl < a.qkv_planes; ++pl) sum += p[(size_t)pl * a.qkv_stride];
+            return sum;
+        };
+        const int half = a.rd >> 1;
+        const float* cs = a.cos_t ? a.cos_t + (size_t)pos0 * half : nullptr;
+        const float* sn = a.sin_t ? a.sin_t + (size_t)pos0 * half : nullptr;
+        const bool owner = a.write_kv && kbeg <= pos0 && pos0 < kend;
+        const int jobs = nrows + (owner ? 2 : 0);                      // the query heads, then the key, then the value
+        const bool whole = cs == nullptr || a.rd == D;                 // no rotation, or over the whole head
+        for (int job = warp; job < jobs; job += THREADS / 32) {
+            const bool is_q = job < nrows, is_v = job == nrows + 1;
+            const int head = is_q ? head0 + job : a.nq + (is_v ? a.nkv : 0) + kvh;
+            const size_t src = (size_t)tok0 * width + (size_t)head * D;
+            const void* gain = is_q ? a.q_gain : (is_v ? nullptr : a.k_gain);
+            __nv_bfloat16* cached = nullptr;
+            if (!is_q) {
+                const int page = table[pos0 >> page_shift];
+                cached = const_cast<__nv_bfloat16*>(kv_head) + (size_t)page * page_stride + (is_v ? (size_t)a.nkv * head_stride : 0) +
+                         (size_t)(pos0 & page_mask) * D;
+            }
+            auto gain_at = [&](int i) -> float {
+                return a.gain_f32 ? ((const float*)gain)[i] : __bfloat162float(((const __nv_bfloat16*)gain)[i]);
+            };
+            if (whole) {
+                // a lane holds E neighbouring features; the feature half a head further is in lane ^ 16, same place
+                constexpr int E = D / 32;
+                const int e0 = lane * E;
+                float x[E];
+                if (a.qkv_f32) {
+                    const float2* p = reinterpret_cast<const float2*>((const float*)a.qkv + src + e0);
+                    const size_t step = a.qkv_stride / 2;
+#pragma unroll
+                    for (int j = 0; j < E; ++j) x[j] = 0.f;
+                    int pl = 0;
+                    for (; pl + 4 <= a.qkv_planes; pl += 4) {          // four planes' loads in flight before the first sum
+                        float2 v[4][E / 2];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int j = 0; j < E / 2; ++j) v[u][j] = p[(size_t)(pl + u) * step + j];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int j = 0; j < E / 2; ++j) {
+                                x[2 * j] += v[u][j].x;
+                                x[2 * j + 1] += v[u][j].y;
+                            }
+                    }
+                    for (; pl < a.qkv_planes; ++pl)
+#pragma unroll
+                        for (int j = 0; j < E / 2; ++j) {
+                            const float2 v = p[(size_t)pl * step + j];
+                            x[2 * j] += v.x;
+                            x[2 * j + 1] += v.y;
+                        }
+                } else {
+                    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>((const __nv_bfloat16*)a.qkv + src + e0);
+#pragma unroll
+                    for (int j = 0; j < E / 2; ++j) {
+                        const float2 v = __bfloat1622float2(p[j]);
+                        x[2 * j] = v.x;
+                        x[2 * j + 1] = v.y;
+                    }
+                }
+                if (gain) {
+                    float ssq = 0.f;
+#pragma unroll
+                    for (int j = 0; j < E; ++j) ssq += x[j] * x[j];
+                    const float inv = rsqrtf(warp_sum(ssq) / (float)D + a.eps);
+#pragma unroll
+                    for (int j = 0; j < E; ++j) x[j] = (x[j] * inv) * gain_at(e0 + j);
+                }
+                if (cs && !is_v) {
+                    const int t0 = e0 - (lane >= 16 ? D / 2 : 0);      // this lane's place in the tables
+#pragma unroll
+                    for (int j = 0; j < E; ++j) {
+                        const float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
+                        const float cc = cs[t0 + j], ss = sn[t0 + j];
+                        const float x1 = lane < 16 ? x[j] : other, x2 = lane < 16 ? other : x[j];
+                        x[j] = lane < 16 ? x1 * cc - x2 * ss : x2 * cc + x1 * ss;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < E / 2; ++j) {
+                    const uint32_t two = pack_bf16(x[2 * j], x[2 * j + 1]);
+                    const int i = e0 + 2 * j;
+                    if (is_q) *reinterpret_cast<uint32_t*>(q_s + swz<D>(job, i >> 3) + (i & 7) * 2) = two;
+                    else *reinterpret_cast<uint32_t*>(cached + i) = two;
+                }
+                continue;
+            }
+            auto put = [&](int i, float v) {
+                const __nv_bfloat16 b = __float2bfloat16_rn(v);
+                if (is_q) *reinterpret_cast<__nv_bfloat16*>(q_s + swz<D>(job, i >> 3) + (i & 7) * 2) = b;
+                else cached[i] = b;
+            };
+            if (is_v) {
+                for (int i = lane; i < D; i += 32) put(i, in(src + i));
+                continue;
+            }
+            float inv = 1.f;
+            if (gain) {
+                float ssq = 0.f;
+                for (int i = lane; i < D; i += 32) {
+                    const float x = in(src + i);
+                    ssq += x * x;
+                }
+                inv = rsqrtf(warp_sum(ssq) / (float)D + a.eps);
+            }
+            for (int i = lane; i < half; i += 32) {
+                float x1 = in(src + i), x2 = in(src + i + half);
+                if (gain) {
+                    x1 = (x1 * inv) * gain_at(i);
+                    x2 = (x2 * inv) * gain_at(i + half);
+                }
+                float o1 = x1, o2 = x2;
+                if (cs) {
+                    const float cc = cs[i], ss = sn[i];
+                    o1 = x1 * cc - x2 * ss;
+                    o2 = x2 * cc + x1 * ss;
+                }
+                put(i, o1);
+                put(i + half, o2);
+            }
+            for (int i = a.rd + lane; i < D; i += 32) {
+                float x = in(src + i);
+                if (gain) x = (x * inv) * gain_at(i);
+                put(i, x);
+            }
+        }
+        if (owner) __threadfence();                // the key and the value are in place before this block's copies read them
+    } else
     for (int i = tid; i < BM * CH; i += THREADS) {
         const int r = i / CH, ch = i % CH;
         uint4 val = make_uint4(0, 0, 0, 0);
@@ -583,21 +726,15 @@ LILY_API int lily_attention_decode_mma_clusters(int d, int splits, int group) {
     return 0;
 }
 
-// One query token per request over its cached keys, the keys cut into `splits` ranges.  With 2 to 16 splits (and all blocks resident at once) the
-// blocks of a (request, kv head) form a cluster and merge their results through distributed shared memory; with
-// more, the partial results go to `scratch` in the layout of attention_simt.cu ([requests, nq, splits, d]
-// outputs, then [requests, nq, splits, 2] (max, sum)) and the combine kernel is launched behind.
-LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out, const int* block_table,
-                                       int bt_stride, const int* seq_lens, float* scratch, int requests, int splits,
-                                       int nq, int nkv, int d, int page_size, int window, float scale,
-                                       cudaStream_t stream) {
+static int decode_mma(AttnArgs& a, const void* q, const void* kv, void* out, const int* block_table, int bt_stride,
+                      const int* seq_lens, float* scratch, int requests, int splits, int nq, int nkv, int d, int page_size,
+                      int window, float scale, cudaStream_t stream) {
     if (requests == 0) return 0;
     LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_decode: %d query heads over %d kv heads", nq, nkv);
     LILY_REQUIRE(splits >= 1 && splits <= 65535 && page_size > 0, "attention_decode: splits=%d page_size=%d", splits, page_size);
     LILY_REQUIRE(splits == 1 || scratch != nullptr, "attention_decode: splits need scratch");
     const int group = nq / nkv, chunks = (group + 15) / 16;
     LILY_REQUIRE(nkv * chunks <= 65535, "attention_decode: %d kv heads", nkv);
-    AttnArgs a{};
     a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride; a.seq_lens = seq_lens;
     a.splits = splits; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
     a.part_o = scratch;
@@ -608,4 +745,40 @@ LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out,
     LILY_CHECK_LAUNCH("attention_decode_mma");
     if (splits > 1 && !merged) return lily_attention_combine(scratch, out, requests, nq, d, splits, kBF16, stream);
     return 0;
+}
+
+// One query token per request over its cached keys, the keys cut into `splits` ranges.  With 2 to 16 splits (and all
+// clusters resident at once) the blocks of a (request, kv head) form a cluster and merge their results through
+// distributed shared memory; else the partial results go to `scratch` in the layout of attention_simt.cu
+// ([requests, nq, splits, d] outputs, then [requests, nq, splits, 2] (max, sum)) and the combine kernel is launched behind.
+LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out, const int* block_table,
+                                       int bt_stride, const int* seq_lens, float* scratch, int requests, int splits,
+                                       int nq, int nkv, int d, int page_size, int window, float scale,
+                                       cudaStream_t stream) {
+    AttnArgs a{};
+    return decode_mma(a, q, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv, d, page_size,
+                      window, scale, stream);
+}
+
+// The same from the qkv product itself ([planes][requests, (nq + 2 nkv) d], float32 partial sums or bfloat16 with
+// one plane): the kernel norms and rotates its query heads (gains and tables optional, as in
+// lily_qk_norm_rope_write) and, unless write_kv is 0, writes this step's key and value to the cache before it
+// reads them, so that no kernel runs between the projection and the attention.
+LILY_API int lily_attention_decode_mma_fused(const void* qkv, int qkv_planes, size_t qkv_stride, int qkv_dtype,
+                                             const void* q_gain, const void* k_gain, int gain_dtype, float eps,
+                                             const float* cos_t, const float* sin_t, int rd, int write_kv,
+                                             void* kv, void* out, const int* block_table, int bt_stride,
+                                             const int* seq_lens, float* scratch, int requests, int splits, int nq,
+                                             int nkv, int d, int page_size, int window, float scale, cudaStream_t stream) {
+    LILY_REQUIRE(qkv != nullptr && qkv_planes >= 1 && (qkv_dtype == kF32 || qkv_planes == 1),
+                 "attention_decode_fused: %d planes of dtype %d", qkv_planes, qkv_dtype);
+    LILY_REQUIRE(rd >= 0 && rd <= d && rd % 2 == 0, "attention_decode_fused: rotary_dim %d does not fit head_dim %d", rd, d);
+    LILY_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "attention_decode_fused: q and k gains come together");
+    LILY_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "attention_decode_fused: cos and sin tables come together");
+    AttnArgs a{};
+    a.qkv = qkv; a.qkv_planes = qkv_planes; a.qkv_stride = qkv_stride; a.qkv_f32 = qkv_dtype == kF32;
+    a.q_gain = q_gain; a.k_gain = k_gain; a.gain_f32 = gain_dtype == kF32; a.eps = eps;
+    a.cos_t = cos_t; a.sin_t = sin_t; a.rd = cos_t ? rd : 0; a.write_kv = write_kv;
+    return decode_mma(a, nullptr, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv, d,
+                      page_size, window, scale, stream);
 }

@@ -37,6 +37,8 @@ _SIGNATURES = {
     "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "lily_attention_decode_mma_fused": [_vp, _i, _sz, _i, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp,
+                                        _i, _i, _i, _i, _i, _i, _i, _f, _vp],
     "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_top_logprobs": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
@@ -437,6 +439,45 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
         _call("lily_attention_decode_simt", *common, _dt(q), _stream())
         if splits > 1:
             launches["count"] += 1          # the combine kernel, launched inside
+
+
+def decode_fused_takes(dtype: torch.dtype, d: int, blocks: int = 0) -> bool:
+    """Whether ``attention_decode_fused`` runs for this cache dtype and head size (the tensor-core decode kernel's),
+    and, given the number of blocks of the step's attention (requests x kv heads x key ranges), whether it pays:
+    every block finishes its own queries, which costs less than a kernel of its own while all blocks are resident
+    at once (three a SM) and more when they run in several rounds (measured at batch 64: 2 % of the step)."""
+    return uses_tensor_cores(dtype, d) and blocks <= 3 * 148
+
+
+def attention_decode_fused(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                           cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], kv_layer: torch.Tensor,
+                           block_table: torch.Tensor, seq_lens: torch.Tensor, out: torch.Tensor,
+                           scratch: Optional[torch.Tensor], splits: int, nq: int, nkv: int, d: int, rotary_dim: int,
+                           page_size: int, scale: float, window: Optional[int] = None, write_kv: bool = True) -> None:
+    """``qk_norm_rope_write`` and ``attention_decode`` of a step in which every request brings one token, as one
+    kernel: ``qkv`` is the projection's result ([requests, (nq + 2 nkv) d] in the cache's dtype, or float32 partial
+    sums [splits, requests, ...]); the attention blocks finish their own query heads, and the block whose key range
+    holds the new position finishes the key and the value and writes them to the cache before it reads them."""
+    _dev(qkv, q_gain, k_gain, cos, sin, kv_layer, block_table, seq_lens, out, scratch)
+    requests = qkv.shape[-2]
+    planes, stride = _summed(qkv, requests, (nq + 2 * nkv) * d, "attention_decode_fused qkv")
+    if not uses_tensor_cores(kv_layer.dtype, d) or out.dtype != kv_layer.dtype or qkv.dtype not in (kv_layer.dtype, torch.float32):
+        raise KernelError(f"attention_decode_fused: cache {kv_layer.dtype}, qkv {qkv.dtype}, out {out.dtype}, head size {d}")
+    if tuple(kv_layer.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError(f"cache layer shape {tuple(kv_layer.shape)} does not fit kv_heads={nkv} page={page_size} d={d}")
+    if cos is not None and (cos.dtype != torch.float32 or cos.shape[-1] != rotary_dim // 2):
+        raise KernelError("rotation tables must be float32 [positions, rotary_dim / 2]")
+    if q_gain is not None and q_gain.dtype != k_gain.dtype:
+        raise KernelError("q and k gains must share a dtype")
+    need = decode_scratch_floats(requests, nq, d, splits)
+    if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
+        raise KernelError(f"attention_decode: scratch of {need} float32 needed")
+    _call("lily_attention_decode_mma_fused", _p(qkv), planes, stride, _dt(qkv), _p(q_gain), _p(k_gain),
+          _dt(q_gain) if q_gain is not None else _F32, float(eps), _p(cos), _p(sin), int(rotary_dim), int(write_kv),
+          _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1], _i32(seq_lens, "seq_lens"),
+          _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0), float(scale), _stream())
+    if splits > 1 and requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv):
+        launches["count"] += 1                                       # the combine kernel, launched inside
 
 
 # ------------------------------------------------------------------------------ sampling

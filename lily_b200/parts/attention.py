@@ -107,11 +107,22 @@ class Attention(Mixer):
         qkv = getattr(ops, "linear_auto", ops.linear)(x, self.w_qkv, self.b_qkv)
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
+        nd = batch.num_decode
+        if nd == batch.num_tokens and hasattr(ops, "attention_decode_fused") and ops.decode_fused_takes(
+                cache.data.dtype, s.head_dim, nd * s.num_kv_heads * -(-(s.num_heads // s.num_kv_heads) // 16) * batch.decode_splits):
+            # every request brings one token: the decode attention kernel finishes q, k and v itself
+            out = torch.empty((nd, s.num_heads * s.head_dim), dtype=cache.data.dtype, device=cache.data.device)
+            splits = batch.decode_splits
+            need = ops.decode_scratch_floats(nd, s.num_heads, s.head_dim, splits)
+            scratch = batch.workspace.floats("attention_decode", need) if need else None
+            ops.attention_decode_fused(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, cache.data, table, batch.seq_lens,
+                                       out, scratch, splits, s.num_heads, s.num_kv_heads, s.head_dim, rotary_dim, page,
+                                       self.scale, s.window, write_kv=write_cache)
+            return getattr(ops, "linear_auto", ops.linear)(out, self.w_o, self.b_o)
         q = ops.qk_norm_rope_write(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, batch.positions,
                                    batch.token_req, table, cache.data, s.num_heads, s.num_kv_heads, s.head_dim,
                                    rotary_dim, page, write_kv=write_cache)
         out = torch.empty_like(q)       # [tokens, heads * head_dim]
-        nd = batch.num_decode
         if nd:
             splits = batch.decode_splits
             need = ops.decode_scratch_floats(nd, s.num_heads, s.head_dim, splits)

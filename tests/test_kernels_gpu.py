@@ -369,6 +369,52 @@ def test_attention_decode(dtype, splits, nq, nkv, d, page, window):
     torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("planes", [1, 3])
+@pytest.mark.parametrize("splits", [1, 4, 6, 12])
+@pytest.mark.parametrize("nq,nkv,d,page,window,rd,gains", [
+    (32, 8, 128, 64, None, 128, True), (8, 2, 64, 16, None, 64, False), (40, 2, 64, 16, 70, 32, True),
+    (6, 2, 192, 32, None, 0, True), (2, 2, 256, 16, 100, 256, False), (5, 1, 128, 8, None, 128, True)])
+def test_attention_decode_from_the_projection(planes, splits, nq, nkv, d, page, window, rd, gains):
+    """One kernel from the qkv product to the attention output (bfloat16, tensor-core head sizes) against the two
+    kernels it replaces: the same output and the same cache afterwards, with per-head gains or without, full,
+    partial or no rotation, a window, the product as bfloat16 or as float32 partial sums, and sequence lengths whose
+    new position opens a page, ends one, or is the only one.  (Up to a last bit of bfloat16: the two sum a head's
+    squares in different orders.)"""
+    o = ops()
+    dtype = torch.bfloat16
+    seqs = [1, 8, 65, 500, 1000, 3, 257, 64, 129]
+    prefixes, news = [n - 1 for n in seqs], [1] * len(seqs)
+    cache, table, _, cu, pre = _attention_case(dtype, nq, nkv, d, page, prefixes, news, window, seed=8)
+    g = torch.Generator(device=DEV).manual_seed(81)
+    n, width = len(seqs), (nq + 2 * nkv) * d
+    qkv = torch.randn(planes, n, width, device=DEV, generator=g) * 0.7 if planes > 1 else \
+        torch.randn(n, width, device=DEV, generator=g).to(dtype)
+    qg = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)).to(dtype) if gains else None
+    kg = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)).to(dtype) if gains else None
+    cos = torch.rand(1100, rd // 2, device=DEV, generator=g) if rd else None
+    sin = torch.rand(1100, rd // 2, device=DEV, generator=g) if rd else None
+    seq_t = torch.tensor(seqs, device=DEV, dtype=torch.int32)
+    pos = seq_t - 1
+    req = torch.arange(n, device=DEV, dtype=torch.int32)
+    scratch = torch.full((max(o.decode_scratch_floats(n, nq, d, splits), 1),), float("nan"), device=DEV)
+    two, one = cache.clone(), cache.clone()
+    q = o.qk_norm_rope_write(qkv, qg, kg, 1e-6, cos, sin, pos, req, table, two, nq, nkv, d, rd, page)
+    want = torch.zeros(n, nq * d, device=DEV, dtype=dtype)
+    o.attention_decode(q, two, table, seq_t, want, scratch, splits, nq, nkv, d, page, d ** -0.5, window)
+    got = torch.zeros_like(want)
+    o.attention_decode_fused(qkv, qg, kg, 1e-6, cos, sin, one, table, seq_t, got, scratch, splits, nq, nkv, d, rd, page,
+                             d ** -0.5, window)
+    last_bit = dict(atol=2 ** -7, rtol=2 ** -7)
+    torch.testing.assert_close(one.float(), two.float(), **last_bit, msg="the cache after the step")
+    assert float((one.float() - two.float()).abs().gt(0).float().mean()) < 1e-3        # and nearly everywhere the same bits
+    torch.testing.assert_close(got.float(), want.float(), **last_bit)
+    # a layer that reads another layer's cache: nothing is written
+    kept = two.clone()
+    o.attention_decode_fused(qkv * 0.5 if planes > 1 else qkv, qg, kg, 1e-6, cos, sin, kept, table, seq_t, got, scratch, splits,
+                             nq, nkv, d, rd, page, d ** -0.5, window, write_kv=False)
+    assert torch.equal(kept, two)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,page", [(4, 2, 16, 16), (8, 2, 128, 64), (6, 2, 48, 8)])
 def test_attention_window_edge_and_page_edge(dtype, nq, nkv, d, page):
