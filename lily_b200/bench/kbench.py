@@ -3,6 +3,7 @@ CUDA-event timing after warm-up, inputs rotated through several copies so that n
 from L2, results as achieved GB/s or TFLOP/s and as a fraction of the measured peaks.
 
     python -m lily_b200.bench.kbench attention_decode --batch 8 --ctx 4096
+    python -m lily_b200.bench.kbench attention_decode_fused --batch 8 --ctx 4096   (from the qkv product's partial sums)
     python -m lily_b200.bench.kbench attention_prefill --tokens 2048
     python -m lily_b200.bench.kbench add_rmsnorm --tokens 8
     python -m lily_b200.bench.kbench silu_mul --tokens 2048
@@ -82,7 +83,7 @@ def time_ms(fns, reps, warmup=3, graph=False):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attention_decode", "attention_prefill", "add_rmsnorm", "silu_mul", "rope", "linear", "linear_split", "gemm_tc", "gemm_tc_silu"])
+    ap.add_argument("kernel", choices=["attention_decode", "attention_decode_fused", "attention_prefill", "add_rmsnorm", "silu_mul", "rope", "linear", "linear_split", "gemm_tc", "gemm_tc_silu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
@@ -113,8 +114,8 @@ def main() -> int:
     g = torch.Generator(device=dev).manual_seed(0)
     fns, bytes_moved, flops = [], 0.0, 0.0
 
-    if a.kernel in ("attention_decode", "attention_prefill"):
-        decode = a.kernel == "attention_decode"
+    if a.kernel in ("attention_decode", "attention_decode_fused", "attention_prefill"):
+        decode = a.kernel != "attention_prefill"
         reqs = a.batch if decode else 1
         total_len = a.ctx if decode else a.prefix + a.tokens
         width = -(-total_len // a.page)
@@ -125,8 +126,18 @@ def main() -> int:
                 q = torch.randn(reqs, a.nq * a.d, device=dev, generator=g).to(dt)
                 out = torch.empty_like(q)
                 seq = torch.full((reqs,), a.ctx, device=dev, dtype=torch.int32)
-                splits = a.splits or choose_decode_splits(reqs, a.nkv, a.ctx)
+                splits = a.splits or choose_decode_splits(reqs, a.nkv, a.ctx, clusters=lambda n: ops.decode_clusters(a.d, n, a.nq // a.nkv))
                 scratch = torch.empty(max(1, ops.decode_scratch_floats(reqs, a.nq, a.d, splits)), device=dev)
+                if a.kernel == "attention_decode_fused":
+                    # the projection's result as the skinny product leaves it: float32 partial sums over 6 slices of k
+                    qkv = torch.randn(6, reqs, (a.nq + 2 * a.nkv) * a.d, device=dev, generator=g)
+                    gain = torch.ones(a.d, device=dev, dtype=dt)
+                    cos = torch.rand(a.ctx, a.d // 2, device=dev, generator=g)
+                    sin = torch.rand(a.ctx, a.d // 2, device=dev, generator=g)
+                    fns.append(lambda qkv=qkv, gain=gain, cos=cos, sin=sin, cache=cache, table=table, seq=seq, out=out,
+                               scratch=scratch: ops.attention_decode_fused(qkv, gain, gain, 1e-6, cos, sin, cache, table, seq, out,
+                                                                           scratch, splits, a.nq, a.nkv, a.d, a.d, a.page, a.d ** -0.5))
+                    continue
                 fns.append(lambda q=q, cache=cache, table=table, seq=seq, out=out, scratch=scratch: ops.attention_decode(
                     q, cache, table, seq, out, scratch, splits, a.nq, a.nkv, a.d, a.page, a.d ** -0.5))
             else:
