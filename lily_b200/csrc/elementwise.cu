@@ -477,6 +477,9 @@ static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 LILY_API const char* lily_last_error() { return g_error; }
 
+// Streaming multiprocessors of the current device.
+LILY_API int lily_sm_count() { return sm_count(); }
+
 LILY_API int lily_embed(const void* table, int table_dtype, const int* ids, const int* future, float* out, int tokens,
                         int hidden, int vocab, cudaStream_t stream) {
     if (tokens == 0) return 0;

@@ -441,12 +441,17 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
             launches["count"] += 1          # the combine kernel, launched inside
 
 
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (148 on a B200)."""
+    return int(library().lily_sm_count())
+
+
 def decode_fused_takes(dtype: torch.dtype, d: int, blocks: int = 0) -> bool:
     """Whether ``attention_decode_fused`` runs for this cache dtype and head size (the tensor-core decode kernel's),
     and, given the number of blocks of the step's attention (requests x kv heads x key ranges), whether it pays:
     every block finishes its own queries, which costs less than a kernel of its own while all blocks are resident
     at once (three a SM) and more when they run in several rounds (measured at batch 64: 2 % of the step)."""
-    return uses_tensor_cores(dtype, d) and blocks <= 3 * 148
+    return uses_tensor_cores(dtype, d) and blocks <= 3 * sm_count()
 
 
 def attention_decode_fused(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,

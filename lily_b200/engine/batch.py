@@ -160,7 +160,7 @@ def build_step_batch(entries: Sequence[StepEntry], prefix_lens: Sequence[int],
                      workspace: Optional[Workspace] = None, pinned: Optional[torch.Tensor] = None,
                      table_widths: Optional[Sequence[int]] = None, decode_splits: Optional[int] = None,
                      logit_rows: Optional[Sequence[int]] = None,
-                     split_clusters: Optional[Callable[[int], int]] = None) -> StepBatch:
+                     split_clusters: Optional[Callable[[int], int]] = None, sm_count: int = 148) -> StepBatch:
     """Packs a step.  ``entries`` are already ordered (one-token requests first);
     ``prefix_lens[i]`` positions of entry i are cached; ``tables[g][i]`` is the block table of
     entry i in cache group g (covering prefix + new tokens).  ``logit_rows`` (flat token indices)
@@ -218,7 +218,8 @@ def build_step_batch(entries: Sequence[StepEntry], prefix_lens: Sequence[int],
     parts = torch.split(dev, sizes) if total else [dev] * len(sizes)
     max_seq = max(seq_lens, default=0)
     splits = decode_splits if decode_splits is not None else choose_decode_splits(
-        num_decode, kv_heads_for_splits, max((seq_lens[i] for i in range(num_decode)), default=0), clusters=split_clusters)
+        num_decode, kv_heads_for_splits, max((seq_lens[i] for i in range(num_decode)), default=0), sm_count=sm_count,
+        clusters=split_clusters)
     return StepBatch(
         num_tokens=n, num_requests=b, num_decode=num_decode,
         token_ids=parts[0], positions=parts[1], token_req=parts[2], cu_seqlens=parts[3], prefix_lens=parts[4],

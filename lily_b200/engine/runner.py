@@ -76,7 +76,8 @@ class _DecodeGraph:
         self.static = torch.zeros(total, dtype=torch.int32, device=runner.device)
         self.copied: Optional[torch.cuda.Event] = None
         parts = torch.split(self.static, self.sizes)
-        splits = choose_decode_splits(b, runner._kv_heads, runner.context_len, clusters=runner._split_clusters)
+        splits = choose_decode_splits(b, runner._kv_heads, runner.context_len, sm_count=runner._sm_count,
+                                      clusters=runner._split_clusters)
         self.batch = StepBatch(
             num_tokens=b, num_requests=b, num_decode=b, token_ids=parts[0], positions=parts[1], token_req=parts[2],
             cu_seqlens=parts[3], prefix_lens=parts[4], seq_lens=parts[5], slots=parts[6], logit_rows=parts[7],
@@ -187,6 +188,7 @@ class ModelRunner:
         # how many clusters of s blocks the decode attention can keep resident (it then merges its key ranges inside
         # them): asked of the kernels for the head size of the cache group with the most kv heads
         self._split_clusters = None
+        self._sm_count = ops.sm_count() if hasattr(ops, "sm_count") else 148
         if hasattr(ops, "decode_clusters") and self.dtype == torch.bfloat16 and groups:
             head_dim = max(groups, key=lambda g: g[0].kv_heads)[0].head_dim
             self._split_clusters = lambda s, d=head_dim: ops.decode_clusters(d, s, 1)
@@ -283,7 +285,7 @@ class ModelRunner:
         pinned, ring_index = self._ring.take(need) if self._ring is not None else (None, -1)
         batch = build_step_batch(ordered, prefix, tables, self.device, kv_heads_for_splits=self._kv_heads,
                                  workspace=self.workspace, pinned=pinned, logit_rows=rows,
-                                 split_clusters=self._split_clusters)
+                                 split_clusters=self._split_clusters, sm_count=self._sm_count)
         if self._ring is not None:
             self._ring.mark(ring_index)
         batch.future_tokens = self.future_tokens
