@@ -204,7 +204,7 @@ __global__ void add_rmsnorm_cluster_kernel(float* __restrict__ resid, const Summ
                                            const W* __restrict__ weight, T* __restrict__ out,
                                            const int* __restrict__ rows, int hidden, float eps, int write_residual) {
     __shared__ float red[40];
-    __shared__ float share[1];
+    __shared__ float share[CL];                                      // every block's sum of squares, sent by its owner
     cg::cluster_group cluster = cg::this_cluster();
     pdl_enter_small();
     const int m = blockIdx.y;
@@ -216,15 +216,16 @@ __global__ void add_rmsnorm_cluster_kernel(float* __restrict__ resid, const Summ
         v.x += dl.x; v.y += dl.y; v.z += dl.z; v.w += dl.w;
         if (write_residual) store4(resid, src + i, v);
     }
+    const float4 g = load4(weight, i);
     const float mine = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
-    if (threadIdx.x == 0) share[0] = mine;
+    // each block tells every block of the cluster its sum; after the one barrier nobody touches another block's
+    // shared memory again, so a block may leave as soon as it is done
+    if (threadIdx.x < CL) cluster.map_shared_rank(&share[0], threadIdx.x)[blockIdx.x] = mine;
     cluster.sync();
     float total = 0.f;
 #pragma unroll
-    for (int r = 0; r < CL; ++r) total += *cluster.map_shared_rank(&share[0], r);    // same order in every block
-    cluster.sync();                                                  // nobody leaves while its sum may still be read
+    for (int r = 0; r < CL; ++r) total += share[r];                  // same order in every block
     const float inv = rsqrtf(total / (float)hidden + eps);
-    const float4 g = load4(weight, i);
     store4(out + (size_t)m * hidden, i, make_float4((v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w));
 }
 
