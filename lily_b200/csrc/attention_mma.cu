@@ -6,8 +6,15 @@
 //  * prefill: grid (query tiles of 64 new tokens, query heads), 4 warps of 16 query rows each.
 //  * decode:  grid (requests, kv heads x row chunks, splits).  The query heads that share a kv head
 //    are the (up to 16) rows; the 4 warps take 16 keys each of every 64-key tile and keep their own
-//    running (max, sum, output), merged through shared memory at the end; splits > 1 leave partial
-//    results in scratch for the combine kernel of attention_simt.cu.
+//    running (max, sum, output), merged through shared memory at the end.  The splits of one
+//    (request, kv head) are merged either inside a thread-block cluster (1 x 1 x splits, up to 16
+//    blocks: each block sends every other its share of the sums through distributed shared memory,
+//    one cluster barrier, each finishes its share of the output; used while all clusters are resident
+//    at once) or through scratch and the combine kernel of attention_simt.cu.
+//    The queries come finished from `q`, or, in a step where every request brings one token, from
+//    the qkv product itself: a warp per head sums the product's partial planes, applies the per-head
+//    RMSNorm and the rotation, and the block whose key range holds the new position does the same
+//    for the key, copies the value, and writes both to their page before it reads them.
 //
 // Key and value tiles of 64 positions are brought in with cp.async (16-byte pieces, any page
 // size: each row's page is looked up in the block table), double buffered, into shared memory
