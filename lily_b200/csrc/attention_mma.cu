@@ -126,7 +126,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         tok0 = req;
         pos0 = seq - 1;
     } else {
-        const int tile = blockIdx.x;
+        const int tile = gridDim.x - 1 - blockIdx.x;       // the tiles come ordered by the keys they see: longest first
         req = a.tile_req[tile];
         const int start = a.tile_start[tile];
         const int t0 = a.cu_seqlens[req], len = a.cu_seqlens[req + 1] - t0;

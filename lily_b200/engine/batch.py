@@ -102,14 +102,13 @@ class StepBatch:
 
     def tiles(self, rows: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """(request, offset) of each tile of ``rows`` new tokens over the requests that bring a
-        portion (those after the first ``num_decode``)."""
+        portion (those after the first ``num_decode``), in the order of the keys they attend to."""
         if rows not in self._tiles:
-            req: List[int] = []
-            start: List[int] = []
-            for r in range(self.num_decode, self.num_requests):
-                for s in range(0, self.h_new_lens[r], rows):
-                    req.append(r)
-                    start.append(s)
+            pairs = [(self.h_prefix_lens[r] + s, r, s) for r in range(self.num_decode, self.num_requests)
+                     for s in range(0, self.h_new_lens[r], rows)]
+            pairs.sort()                   # by the keys a tile sees: the kernels start with the last, longest ones
+            req = [r for _, r, _ in pairs]
+            start = [s for _, _, s in pairs]
             dev = self.token_ids.device
             both = torch.tensor([req, start], dtype=torch.int32).reshape(2, -1)
             both = both.to(dev) if dev.type != "cpu" else both
