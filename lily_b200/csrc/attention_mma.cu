@@ -124,7 +124,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         nrows = min(16, group - r0);
         head0 = kvh * group + r0;
         tok0 = req;
-        pos0 = seq - 1;
+        pos0 = seq > 0 ? seq - 1 : 0;                        // an empty row (no position yet) reads table entry 0 at most
     } else {
         const int tile = gridDim.x - 1 - blockIdx.x;       // the tiles come ordered by the keys they see: longest first
         req = a.tile_req[tile];
