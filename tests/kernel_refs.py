@@ -147,6 +147,23 @@ def attention_decode(q, kv_layer, block_table, seq_lens, out, scratch, splits, n
         out[r] = o.reshape(nq * d).to(out.dtype)
 
 
+def decode_fused_takes(dtype, d, blocks=0):
+    return True
+
+
+def attention_decode_fused(qkv, q_gain, k_gain, eps, cos, sin, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv,
+                           d, rotary_dim, page_size, scale, window=None, write_kv=True):
+    """What the one kernel does, as the two statements it replaces: every request brings one token, at position
+    seq_len - 1."""
+    if qkv.dim() == 3:
+        qkv = qkv.sum(0)
+    n = qkv.shape[0]
+    q = qk_norm_rope_write(qkv, q_gain, k_gain, eps, cos, sin, (seq_lens - 1).to(torch.int32),
+                           torch.arange(n, dtype=torch.int32, device=qkv.device), block_table, kv_layer, nq, nkv, d, rotary_dim,
+                           page_size, write_kv=write_kv)
+    attention_decode(q.to(out.dtype), kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv, d, page_size, scale, window)
+
+
 def argmax(logits, out=None):
     return torch.argmax(logits, dim=-1).to(torch.int32)
 
