@@ -256,11 +256,12 @@ class Scheduler:
         slots = self.max_running_requests - len(self.running) - sum(r.slot is not None for r in self.waiting_queue)
         selected: List[Req] = []
         for req in list(self.waiting_queue):
-            if budget <= 0 or free_pages <= 0 or (req.slot is None and slots <= 0):
+            if budget <= 0 or (req.slot is None and slots <= 0):
                 break
             needed = len(req.fill_ids) - req.seq_len
             held = pages_for(req.seq_len, page)
-            room = (held + free_pages) * page - req.seq_len        # tokens the request could still cache
+            # tokens the request could still cache: what is left of the last page it holds, and the free pages
+            room = (held + max(free_pages, 0)) * page - req.seq_len
             take = min(needed, budget, room)
             if take <= 0:
                 break

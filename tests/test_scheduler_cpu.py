@@ -65,6 +65,27 @@ def test_chunked_prefill_equals_unchunked(setup):
     assert seen[:3] == [[64], [64], [22]]
 
 
+def test_last_portion_fits_the_page_already_held(setup):
+    """All pages are held after two portions; the rest of the prompt still fits the last of them
+    and must be taken, not refused."""
+    cfg, weights, path = setup
+    p = prompts(cfg, [94], seed=9)
+    whole = scheduler(path, max_tokens=96)
+    want = run(whole, p, 2)
+    assert whole.results["r0"].finish_reason == {"type": "length"} and len(want[0]) == 2
+    chunked = scheduler(path, max_tokens=96, chunked_prefill_size=45)
+    taken = []
+    chunked.add_request("r0", p[0], SamplingParams(max_new_tokens=2, ignore_eos=True))
+    while chunked.has_work():
+        assert chunked.step()
+        if chunked.last_batch.get("prefill_tokens"):
+            taken.append(chunked.last_batch["prefill_tokens"])
+            chunked.last_batch = {}
+    assert taken == [45, 45, 4]
+    assert chunked.results["r0"].output_ids == want[0] == plain_impl.greedy_generate(cfg, weights, p[0], 2)
+    assert chunked.runner.cache.held_pages() == [0]
+
+
 def test_budget_portions_and_mixed_batches(setup):
     cfg, weights, path = setup
     s = scheduler(path, chunked_prefill_size=40, max_running_requests=3)
