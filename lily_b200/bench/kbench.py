@@ -105,7 +105,7 @@ def main() -> int:
     a = ap.parse_args()
 
     from lily_b200.csrc import ops
-    from lily_b200.engine.batch import choose_decode_splits
+    from lily_b200.csrc.ops import choose_decode_splits
 
     dev = "cuda"
     dt = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32

@@ -581,11 +581,14 @@ static bool cluster_smem(size_t bytes) {
 }
 
 // How many clusters of `splits` blocks of the decode kernel the device holds at once (asked once per head
-// size and cluster size; 0: such a cluster cannot be placed).
+// size, cluster size and shared-memory size, which grows with the query heads of a kv head; 0: such a cluster
+// cannot be placed).
 template <int D, int STAGES>
 static int cluster_capacity(int splits, size_t smem) {
     static int known[MAX_CLUSTER + 1] = {};                     // 0 not asked, -1 none, else the count
-    if (known[splits] == 0) {
+    static size_t known_smem[MAX_CLUSTER + 1] = {};             // the shared memory the answer was given for
+    if (known[splits] == 0 || known_smem[splits] != smem) {
+        known_smem[splits] = smem;
         int clusters = 0;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1, 1, splits);

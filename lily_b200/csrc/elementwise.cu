@@ -100,7 +100,7 @@ struct Summed {
 // after the step before (`future`), so that a step can be launched before the host has seen it.
 template <typename T, int VEC>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ future,
-                             float* __restrict__ out, int hidden, int vocab) {
+                             float* __restrict__ out, int hidden, int vocab, float scale) {
     pdl_enter_small();
     const int n = blockIdx.x;
     int id = ids[n];
@@ -109,9 +109,21 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     const T* src = table + (size_t)id * hidden;
     float* dst = out + (size_t)n * hidden;
     if (VEC == 4) {
-        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) store4(dst, i, load4(src, i));
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float4 v = load4(src, i);
+            v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+            store4(dst, i, v);
+        }
     } else {
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]) * scale;
+    }
+}
+
+// logits[i] = cap * tanh(scale * logits[i] / cap) (cap > 0), else scale * logits[i]; in place, float32.
+__global__ void logit_transform_kernel(float* __restrict__ logits, size_t n, float scale, float cap) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = logits[i] * scale;
+        logits[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
     }
 }
 
@@ -481,17 +493,25 @@ LILY_API const char* lily_last_error() { return g_error; }
 // Streaming multiprocessors of the current device.
 LILY_API int lily_sm_count() { return sm_count(); }
 
+LILY_API int lily_logit_transform(float* logits, size_t n, float scale, float cap, cudaStream_t stream) {
+    if (n == 0) return 0;
+    const size_t blocks = (n + 255) / 256;
+    logit_transform_kernel<<<(unsigned)(blocks < 4096 ? blocks : 4096), 256, 0, stream>>>(logits, n, scale, cap);
+    LILY_CHECK_LAUNCH("logit_transform");
+    return 0;
+}
+
 LILY_API int lily_embed(const void* table, int table_dtype, const int* ids, const int* future, float* out, int tokens,
-                        int hidden, int vocab, cudaStream_t stream) {
+                        int hidden, int vocab, float scale, cudaStream_t stream) {
     if (tokens == 0) return 0;
     LILY_REQUIRE(hidden > 0 && vocab > 0, "embed: bad sizes hidden=%d vocab=%d", hidden, vocab);
     const bool vec = hidden % 4 == 0 && aligned16(table) && aligned16(out);
     if (table_dtype == kBF16) {
-        if (vec) launch_pdl(embed_kernel<__nv_bfloat16, 4>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, future, out, hidden, vocab);
-        else launch_pdl(embed_kernel<__nv_bfloat16, 1>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, future, out, hidden, vocab);
+        if (vec) launch_pdl(embed_kernel<__nv_bfloat16, 4>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, future, out, hidden, vocab, scale);
+        else launch_pdl(embed_kernel<__nv_bfloat16, 1>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, future, out, hidden, vocab, scale);
     } else {
-        if (vec) launch_pdl(embed_kernel<float, 4>, dim3(tokens), dim3(256), 0, stream, (const float*)table, ids, future, out, hidden, vocab);
-        else launch_pdl(embed_kernel<float, 1>, dim3(tokens), dim3(256), 0, stream, (const float*)table, ids, future, out, hidden, vocab);
+        if (vec) launch_pdl(embed_kernel<float, 4>, dim3(tokens), dim3(256), 0, stream, (const float*)table, ids, future, out, hidden, vocab, scale);
+        else launch_pdl(embed_kernel<float, 1>, dim3(tokens), dim3(256), 0, stream, (const float*)table, ids, future, out, hidden, vocab, scale);
     }
     LILY_CHECK_LAUNCH("embed");
     return 0;

@@ -12,7 +12,8 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Optional
+from dataclasses import dataclass
+from typing import Callable, Optional, Sequence, Tuple
 
 import torch
 
@@ -22,7 +23,8 @@ _F32, _BF16 = 0, 1
 _vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
 
 _SIGNATURES = {
-    "lily_embed": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "lily_embed": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+    "lily_logit_transform": [_vp, _sz, _f, _f, _vp],
     "lily_scatter_tokens": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _sz, _vp],
     "lily_silu_mul": [_vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _vp],
@@ -135,17 +137,26 @@ def _stream():
 # ------------------------------------------------------------------------------ elementwise
 
 def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None,
-          future: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Rows of ``table`` [vocab, hidden] at ``ids`` [tokens] as float32 (the residual stream).  With
-    ``future`` (int32, one entry per request slot) an id ``-(slot + 1)`` stands for the token that
-    ``scatter_tokens`` stored for that slot."""
+          future: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """Rows of ``table`` [vocab, hidden] at ``ids`` [tokens], times ``scale``, as float32 (the residual
+    stream).  With ``future`` (int32, one entry per request slot) an id ``-(slot + 1)`` stands for the
+    token that ``scatter_tokens`` stored for that slot."""
     _dev(table, ids, out, future)
     n, (vocab, hidden) = ids.numel(), table.shape
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
     _call("lily_embed", _p(table), _dt(table), _i32(ids, "ids"), _i32(future, "future") if future is not None else None,
-          _p(out), n, hidden, vocab, _stream())
+          _p(out), n, hidden, vocab, float(scale), _stream())
     return out
+
+
+def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: Optional[float] = None) -> torch.Tensor:
+    """In place on float32 ``logits``: times ``scale``, then ``softcap * tanh(. / softcap)`` when a cap is given."""
+    _dev(logits)
+    if logits.dtype != torch.float32:
+        raise KernelError("logit_transform takes float32 logits")
+    _call("lily_logit_transform", _p(logits), logits.numel(), float(scale), float(softcap or 0.0), _stream())
+    return logits
 
 
 def scatter_tokens(tokens: torch.Tensor, logit_rows: torch.Tensor, token_req: torch.Tensor, slots: torch.Tensor,
@@ -347,6 +358,23 @@ def linear_auto(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     return linear(x, weight, bias)
 
 
+def logits(x: torch.Tensor, head: torch.Tensor) -> torch.Tensor:
+    """``x [rows, hidden] . head [vocab, hidden]^T`` as float32 [rows, vocab]: for a few rows the head is
+    streamed once by this package's kernel when one slice of K serves, else a product that keeps the
+    accumulator's precision (lily/layers/vocab_embedding.py:89-96 casts a model-dtype product)."""
+    parts = linear_split(x, head)
+    if parts is not None and parts.shape[0] == 1:
+        return parts[0]
+    return linear(x, head, out_dtype=torch.float32)
+
+
+def gate_up_interleave(dtype: torch.dtype, intermediate: int) -> Optional[int]:
+    """How a fused gate/up matrix should be laid out for these kernels: None for all gate rows, then all up
+    rows; a number for alternating runs of that many gate rows and the up rows of the same outputs (what the
+    tcgen05 product's SiLU*mul epilogue wants: both halves of 128 outputs inside one 256-row tile)."""
+    return 128 if dtype == torch.bfloat16 and intermediate % 128 == 0 else None
+
+
 # ------------------------------------------------------------------------------ attention
 
 def uses_tensor_cores(dtype: torch.dtype, d: int) -> bool:
@@ -452,12 +480,77 @@ def sm_count() -> int:
     return int(library().lily_sm_count())
 
 
-def decode_fused_takes(dtype: torch.dtype, d: int, blocks: int = 0) -> bool:
-    """Whether ``attention_decode_fused`` runs for this cache dtype and head size (the tensor-core decode kernel's),
-    and, given the number of blocks of the step's attention (requests x kv heads x key ranges), whether it pays:
-    every block finishes its own queries, which costs less than a kernel of its own while all blocks are resident
-    at once (three a SM) and more when they run in several rounds (measured at batch 64: 2 % of the step)."""
-    return uses_tensor_cores(dtype, d) and blocks <= 3 * sm_count()
+def choose_decode_splits(num_decode: int, kv_heads: int, max_seq_len: int, sm_count: int = 148,
+                         blocks_per_sm: int = 3, min_keys: int = 256, max_splits: int = 32,
+                         clusters: Optional[Callable[[int], int]] = None) -> int:
+    """How many ranges the keys of a decode row are cut into.  One block works on one (request, kv
+    head, range); the device holds ``sm_count * blocks_per_sm`` blocks at a time.
+
+    ``clusters(s)`` says how many clusters of ``s`` blocks the attention kernel can have resident at
+    once (``decode_clusters``): while every (request, kv head) pair gets one, the blocks of a pair
+    merge their ranges through distributed shared memory and no combine kernel follows, and the
+    most ranges that allow this are the fastest (measured on a B200, head size 128, 8 kv heads:
+    batch 1 and 2: 16 ranges; 4: 10; 8: 6; 16: 3; 24: 2; sizes past 8 want a tenth of room to spare:
+    24 pairs in clusters of 15, of which exactly 24 fit, took 21 us against 16 us in clusters of 13).
+    Without that (float32, other head sizes, more pairs than clusters of two): the single wave that
+    comes closest to filling the device, and when the rows alone overfill it, about four waves
+    (batch 64: 4 ranges).  The reference fixes 32 splits with a floor of 64 keys
+    (lily/layers/attention/triton_backend.py:21, decode_attention.py:68,172)."""
+    if num_decode == 0:
+        return 1
+    limit = max(1, min(max_splits, max_seq_len // min_keys))
+    pairs, held = num_decode * kv_heads, sm_count * blocks_per_sm
+    if clusters is not None:
+        for s in range(min(limit, 16), 1, -1):
+            room = clusters(s)
+            if pairs <= (room if s <= 8 else 0.9 * room):
+                return s
+    one_wave = min(limit, held // pairs)
+    if one_wave >= 1 and (pairs * one_wave >= 0.7 * held or one_wave == limit):
+        return one_wave
+    return max(1, min(limit, -(-4 * held // pairs)))
+
+
+@dataclass(frozen=True)
+class DecodePlan:
+    """How the decode attention of a step runs (the same for every layer of a cache group)."""
+
+    splits: int                 # key ranges per (request, kv head)
+    fused: bool                 # the attention kernel starts from the qkv product (norm, rotation, cache write inside)
+    scratch_floats: int         # float32 scratch the split ranges are merged through (0: merged inside clusters)
+    arm: str                    # which rule chose the splits: "cluster", "wave" or "single"
+
+
+def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, d: int, max_seq_len: int) -> DecodePlan:
+    """The plan for ``requests`` rows that bring one token each, none longer than ``max_seq_len`` positions.
+    A step in which every request brings one token may hand the qkv product straight to the attention kernel
+    (``fused``): every block then finishes its own queries, which costs less than a kernel of its own while all
+    blocks are resident at once (three a SM) and more when they run in several rounds (measured at batch 64:
+    2 % of the step)."""
+    if requests == 0:
+        return DecodePlan(1, False, 0, "single")
+    group = nq // nkv
+    tensor_cores = uses_tensor_cores(dtype, d)
+    room = (lambda s: decode_clusters(d, s, group)) if tensor_cores else None
+    splits = choose_decode_splits(requests, nkv, max_seq_len, sm_count=sm_count(), clusters=room)
+    row_blocks = -(-group // 16)                 # the tensor-core kernel takes 16 query heads of a kv head a block
+    pairs = requests * nkv * row_blocks
+    in_clusters = tensor_cores and splits > 1 and pairs <= decode_clusters(d, splits, group)
+    fused = tensor_cores and pairs * splits <= 3 * sm_count()
+    arm = "single" if splits == 1 else ("cluster" if in_clusters else "wave")
+    return DecodePlan(splits, fused, decode_scratch_floats(requests, nq, d, splits), arm)
+
+
+def prefill_tiles(prefix_lens: Sequence[int], new_lens: Sequence[int], first: int, rows: int,
+                  device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(request, offset) of each tile of ``rows`` new tokens over the requests from ``first`` on, as two int32
+    device tensors, in the order of the keys a tile attends to (the prefill kernels start with the last,
+    longest ones)."""
+    pairs = [(prefix_lens[r] + s, r, s) for r in range(first, len(new_lens)) for s in range(0, new_lens[r], rows)]
+    pairs.sort()
+    both = torch.tensor([[r for _, r, _ in pairs], [s for _, _, s in pairs]], dtype=torch.int32).reshape(2, -1)
+    both = both.to(device, non_blocking=True)
+    return both[0].contiguous(), both[1].contiguous()
 
 
 def attention_decode_fused(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,

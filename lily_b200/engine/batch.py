@@ -16,7 +16,7 @@ tokens in the flat token array); block tables replace ``req_to_token`` rows.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Callable, Dict, List, Optional, Sequence
 
 import torch
 
@@ -55,7 +55,7 @@ class Workspace:
     def floats(self, name: str, count: int) -> torch.Tensor:
         buf = self._buffers.get(name)
         if buf is None or buf.numel() < count:
-            if torch.cuda.is_current_stream_capturing():
+            if torch.device(self.device).type == "cuda" and torch.cuda.is_current_stream_capturing():
                 raise RuntimeError(f"workspace {name!r} must be sized before a graph is captured")
             buf = torch.empty((max(count, 1),), dtype=torch.float32, device=self.device)
             self._buffers[name] = buf
@@ -81,11 +81,11 @@ class StepBatch:
     h_new_lens: List[int]
     h_prefix_lens: List[int]
     h_slots: List[int]
-    max_seq_len: int
-    decode_splits: int
+    max_seq_len: int                                 # the longest sequence after the step (a bound, in a captured batch)
+    max_decode_len: int = 0                          # the same over the requests that bring one token
     workspace: Optional[Workspace] = None
     future_tokens: Optional[torch.Tensor] = None     # int32 [request slots]: what negative token ids stand for
-    _tiles: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
+    plans: Dict[Any, Any] = field(default_factory=dict)
 
     @property
     def num_prefill_requests(self) -> int:
@@ -100,20 +100,13 @@ class StepBatch:
         """Requests whose first token comes in this step."""
         return [p == 0 for p in self.h_prefix_lens]
 
-    def tiles(self, rows: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        """(request, offset) of each tile of ``rows`` new tokens over the requests that bring a
-        portion (those after the first ``num_decode``), in the order of the keys they attend to."""
-        if rows not in self._tiles:
-            pairs = [(self.h_prefix_lens[r] + s, r, s) for r in range(self.num_decode, self.num_requests)
-                     for s in range(0, self.h_new_lens[r], rows)]
-            pairs.sort()                   # by the keys a tile sees: the kernels start with the last, longest ones
-            req = [r for _, r, _ in pairs]
-            start = [s for _, _, s in pairs]
-            dev = self.token_ids.device
-            both = torch.tensor([req, start], dtype=torch.int32).reshape(2, -1)
-            both = both.to(dev) if dev.type != "cpu" else both
-            self._tiles[rows] = (both[0].contiguous(), both[1].contiguous())
-        return self._tiles[rows]
+    def plan(self, key: Any, make: Callable[["StepBatch"], Any]) -> Any:
+        """What a part worked out for this step, made once and shared by every layer that asks with the same
+        ``key``: a mixer plans its step here (how to cut its work, which kernel form to take, lists it needs on
+        the device) from the batch's host fields, so that the step function knows nothing of any mixer."""
+        if key not in self.plans:
+            self.plans[key] = make(self)
+        return self.plans[key]
 
 
 def order_entries(entries: Sequence[StepEntry]) -> List[int]:
@@ -123,43 +116,11 @@ def order_entries(entries: Sequence[StepEntry]) -> List[int]:
     return ones + rest
 
 
-def choose_decode_splits(num_decode: int, kv_heads: int, max_seq_len: int, sm_count: int = 148,
-                         blocks_per_sm: int = 3, min_keys: int = 256, max_splits: int = 32,
-                         clusters: Optional[Callable[[int], int]] = None) -> int:
-    """How many ranges the keys of a decode row are cut into.  One block works on one (request, kv
-    head, range); the device holds ``sm_count * blocks_per_sm`` blocks at a time.
-
-    ``clusters(s)`` says how many clusters of ``s`` blocks the attention kernel can have resident at
-    once (``ops.decode_clusters``): while every (request, kv head) pair gets one, the blocks of a
-    pair merge their ranges through distributed shared memory and no combine kernel follows, and the
-    most ranges that allow this are the fastest (measured on a B200, head size 128, 8 kv heads:
-    batch 1 and 2: 16 ranges; 4: 10; 8: 6; 16: 3; 24: 2; sizes past 8 want a tenth of room to spare:
-    24 pairs in clusters of 15, of which exactly 24 fit, took 21 us against 16 us in clusters of 13).
-    Without that (float32, other head sizes, more pairs than clusters of two): the single wave that
-    comes closest to filling the device, and when the rows alone overfill it, about four waves
-    (batch 64: 4 ranges).  The reference fixes 32 splits with a floor of 64 keys
-    (lily/layers/attention/triton_backend.py:21, decode_attention.py:68,172)."""
-    if num_decode == 0:
-        return 1
-    limit = max(1, min(max_splits, max_seq_len // min_keys))
-    pairs, held = num_decode * kv_heads, sm_count * blocks_per_sm
-    if clusters is not None:
-        for s in range(min(limit, 16), 1, -1):
-            room = clusters(s)
-            if pairs <= (room if s <= 8 else 0.9 * room):
-                return s
-    one_wave = min(limit, held // pairs)
-    if one_wave >= 1 and (pairs * one_wave >= 0.7 * held or one_wave == limit):
-        return one_wave
-    return max(1, min(limit, -(-4 * held // pairs)))
-
-
 def build_step_batch(entries: Sequence[StepEntry], prefix_lens: Sequence[int],
-                     tables: Sequence[Sequence[Sequence[int]]], device, *, kv_heads_for_splits: int = 1,
+                     tables: Sequence[Sequence[Sequence[int]]], device, *,
                      workspace: Optional[Workspace] = None, pinned: Optional[torch.Tensor] = None,
-                     table_widths: Optional[Sequence[int]] = None, decode_splits: Optional[int] = None,
-                     logit_rows: Optional[Sequence[int]] = None,
-                     split_clusters: Optional[Callable[[int], int]] = None, sm_count: int = 148) -> StepBatch:
+                     table_widths: Optional[Sequence[int]] = None,
+                     logit_rows: Optional[Sequence[int]] = None) -> StepBatch:
     """Packs a step.  ``entries`` are already ordered (one-token requests first);
     ``prefix_lens[i]`` positions of entry i are cached; ``tables[g][i]`` is the block table of
     entry i in cache group g (covering prefix + new tokens).  ``logit_rows`` (flat token indices)
@@ -216,13 +177,11 @@ def build_step_batch(entries: Sequence[StepEntry], prefix_lens: Sequence[int],
     dev = host.to(device, non_blocking=True) if torch.device(device).type != "cpu" else host.clone()
     parts = torch.split(dev, sizes) if total else [dev] * len(sizes)
     max_seq = max(seq_lens, default=0)
-    splits = decode_splits if decode_splits is not None else choose_decode_splits(
-        num_decode, kv_heads_for_splits, max((seq_lens[i] for i in range(num_decode)), default=0), sm_count=sm_count,
-        clusters=split_clusters)
     return StepBatch(
         num_tokens=n, num_requests=b, num_decode=num_decode,
         token_ids=parts[0], positions=parts[1], token_req=parts[2], cu_seqlens=parts[3], prefix_lens=parts[4],
         seq_lens=parts[5], slots=parts[6], logit_rows=parts[7],
         block_tables=[parts[8 + i].view(b, w) for i, w in enumerate(widths)],
         h_new_lens=new_lens, h_prefix_lens=list(prefix_lens), h_slots=[e.slot for e in entries],
-        max_seq_len=max_seq, decode_splits=splits, workspace=workspace)
+        max_seq_len=max_seq, max_decode_len=max((seq_lens[i] for i in range(num_decode)), default=0),
+        workspace=workspace)

@@ -24,8 +24,7 @@ from lily_b200.cache.kv_cache import KVCacheManager, OutOfPages, bytes_per_token
 from lily_b200.config.model_config import read_model_dir
 from lily_b200.config.registry import resolve_architecture
 from lily_b200.config.server_args import ServerArgs
-from lily_b200.engine.batch import (FUTURE, StepBatch, StepEntry, Workspace, build_step_batch, choose_decode_splits,
-                                    order_entries)
+from lily_b200.engine.batch import FUTURE, StepBatch, StepEntry, Workspace, build_step_batch, order_entries
 from lily_b200.models.assembled import AssembledModel
 from lily_b200.parts.base import BuildContext, ModelSpec
 from lily_b200.weights.loader import CheckpointSource, load_model_weights
@@ -76,14 +75,13 @@ class _DecodeGraph:
         self.static = torch.zeros(total, dtype=torch.int32, device=runner.device)
         self.copied: Optional[torch.cuda.Event] = None
         parts = torch.split(self.static, self.sizes)
-        splits = choose_decode_splits(b, runner._kv_heads, runner.context_len, sm_count=runner._sm_count,
-                                      clusters=runner._split_clusters)
         self.batch = StepBatch(
             num_tokens=b, num_requests=b, num_decode=b, token_ids=parts[0], positions=parts[1], token_req=parts[2],
             cu_seqlens=parts[3], prefix_lens=parts[4], seq_lens=parts[5], slots=parts[6], logit_rows=parts[7],
             block_tables=[parts[8 + i].view(b, w) for i, w in enumerate(self.widths)],
             h_new_lens=[1] * b, h_prefix_lens=[0] * b, h_slots=[0] * b, max_seq_len=runner.context_len,
-            decode_splits=splits, workspace=Workspace(runner.device),   # scratch of its own: the graph holds its address
+            max_decode_len=runner.context_len,          # the mixers plan for the longest sequence a replay may bring
+            workspace=Workspace(runner.device),         # scratch of its own: the graph holds its address
             future_tokens=runner.future_tokens)
         self.fill([], [], [[] for _ in self.widths], [])
         self.static.copy_(self.host)
@@ -95,11 +93,11 @@ class _DecodeGraph:
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
-        counter = getattr(runner.model.ctx.ops, "launches", None)
-        before = counter["count"] if counter else 0
+        counter = runner.model.ctx.ops.launches
+        before = counter["count"]
         with torch.cuda.graph(self.graph), torch.no_grad():
             self.logits = runner.model.forward(self.batch, runner.cache)
-        self.kernels = (counter["count"] - before) if counter else 0     # this package's kernels in one replay
+        self.kernels = counter["count"] - before        # this package's kernels in one replay
         self._counter = counter
 
     def fill(self, tokens: Sequence[int], prefix: Sequence[int], tables, slots: Sequence[int]) -> None:
@@ -128,8 +126,7 @@ class _DecodeGraph:
         self.copied = torch.cuda.Event()
         self.copied.record()
         self.graph.replay()
-        if self._counter:
-            self._counter["count"] += self.kernels
+        self._counter["count"] += self.kernels
         return self.logits[:len(tokens)]
 
 
@@ -184,20 +181,11 @@ class ModelRunner:
         self._last_rows: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None
         self.seq_lens: Dict[int, int] = {}
         self._ring = _PinnedRing() if self.device.type == "cuda" else None
-        self._kv_heads = max((need.kv_heads for need, _ in groups), default=1)
-        # how many clusters of s blocks the decode attention can keep resident (it then merges its key ranges inside
-        # them): asked of the kernels for the head size of the cache group with the most kv heads
-        self._split_clusters = None
-        self._sm_count = ops.sm_count() if hasattr(ops, "sm_count") else 148
-        if hasattr(ops, "decode_clusters") and self.dtype == torch.bfloat16 and groups:
-            head_dim = max(groups, key=lambda g: g[0].kv_heads)[0].head_dim
-            self._split_clusters = lambda s, d=head_dim: ops.decode_clusters(d, s, 1)
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
         self._graphs: Dict[int, _DecodeGraph] = {}
-        self.use_graphs = (self.device.type == "cuda" and not args.disable_cuda_graph and self.model.graph_safe
-                           and ops.__name__.endswith("csrc.ops"))
+        self.use_graphs = self.device.type == "cuda" and not args.disable_cuda_graph and self.model.graph_safe
         max_bs = args.cuda_graph_max_bs or min(self.max_requests, 256)
         self.graph_buckets = sorted(set(args.cuda_graph_bs or
                                         [b for b in (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256) if b <= max_bs]
@@ -283,9 +271,8 @@ class ModelRunner:
         need = 3 * run + 4 * len(entries) + 1 + len(rows) + sum(
             len(entries) * max((len(t) for t in g), default=1) for g in tables) + 8
         pinned, ring_index = self._ring.take(need) if self._ring is not None else (None, -1)
-        batch = build_step_batch(ordered, prefix, tables, self.device, kv_heads_for_splits=self._kv_heads,
-                                 workspace=self.workspace, pinned=pinned, logit_rows=rows,
-                                 split_clusters=self._split_clusters, sm_count=self._sm_count)
+        batch = build_step_batch(ordered, prefix, tables, self.device, workspace=self.workspace, pinned=pinned,
+                                 logit_rows=rows)
         if self._ring is not None:
             self._ring.mark(ring_index)
         batch.future_tokens = self.future_tokens

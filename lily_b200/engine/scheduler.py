@@ -137,7 +137,7 @@ class Scheduler:
         self.decode_steps = 0
         self.retractions = 0
         self.last_batch: Dict[str, int] = {}
-        self.overlap = bool(overlap) and hasattr(runner, "store_future")
+        self.overlap = bool(overlap)
         self.overlapped_steps = 0
         self._inflight: Optional[_Launched] = None
         self._pinned: List[Any] = []

@@ -4,7 +4,10 @@ q, k and v come from one product with the stacked matrix ``[q rows | k rows | v 
 kernel then normalises each q and k head (when ``qk_norm``), rotates them by the position tables,
 leaves q in a buffer and writes k and v into the token's page; attention runs over the cache
 (split-key decode kernel for requests that bring one token, prefill kernel for portions); the
-output projection closes the part.  Sizes, eps, scale, window and the position encoding are
+output projection closes the part.  How a step's attention is cut (key ranges, kernel forms, tile
+lists) is this part's own plan, made once a step from the batch's host fields by asking the kernels
+(``ops.plan_decode_attention``, ``ops.prefill_tile_rows``, ``ops.prefill_tiles``); the step function
+knows nothing of it.  Sizes, eps, scale, window and the position encoding are
 parameters of the spec; nothing here knows which model it serves.
 
 Formulas: lily/models/llama.py:50-90 (projections, scale = head_dim^-0.5 unless the spec gives
@@ -35,6 +38,16 @@ class AttentionSpec:
     scale: Optional[float] = None         # None: head_dim ** -0.5
     position: Any = None                  # a position spec (e.g. RopeSpec) or None
     kind: str = "attention"
+
+
+@dataclass
+class AttentionPlan:
+    """One step's attention for one set of sizes: the decode rows' plan (``ops.plan_decode_attention``) and,
+    when requests bring portions, the prefill kernel's tile height and its (request, offset) lists."""
+
+    decode: Any
+    tile_rows: Optional[int]
+    tiles: Any
 
 
 @dataclass
@@ -100,38 +113,49 @@ class Attention(Mixer):
 
     # ---- one step ----------------------------------------------------------------
 
+    def _plan(self, batch, group: int, dtype, page: int):
+        """How this step's attention runs for this mixer's sizes in cache group ``group``; made once a step and
+        shared by every layer with the same sizes (``batch.plan``)."""
+        s, ops = self.spec, self.ctx.ops
+        key = ("attention", group, s.num_heads, s.num_kv_heads, s.head_dim, dtype, page)
+
+        def make(b):
+            nd = b.num_decode
+            decode = ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len)
+            rows = tiles = None
+            if b.num_requests > nd:
+                rows = ops.prefill_tile_rows(dtype, s.head_dim, page, b.num_tokens - nd)
+                tiles = ops.prefill_tiles(b.h_prefix_lens, b.h_new_lens, nd, rows, b.token_ids.device)
+            return AttentionPlan(decode, rows, tiles)
+        return batch.plan(key, make)
+
     def forward(self, x, batch, cache: LayerCache, state=None, write_cache: bool = True):
         s, ops = self.spec, self.ctx.ops
         page = cache.data.shape[3]
         table = batch.block_tables[cache.group]
-        qkv = getattr(ops, "linear_auto", ops.linear)(x, self.w_qkv, self.b_qkv)
+        plan = self._plan(batch, cache.group, cache.data.dtype, page)
+        qkv = ops.linear_auto(x, self.w_qkv, self.b_qkv)
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
-        nd = batch.num_decode
-        if nd == batch.num_tokens and hasattr(ops, "attention_decode_fused") and ops.decode_fused_takes(
-                cache.data.dtype, s.head_dim, nd * s.num_kv_heads * -(-(s.num_heads // s.num_kv_heads) // 16) * batch.decode_splits):
+        nd, dec = batch.num_decode, plan.decode
+        scratch = batch.workspace.floats("attention_decode", dec.scratch_floats) if nd and dec.scratch_floats else None
+        if nd == batch.num_tokens and dec.fused:
             # every request brings one token: the decode attention kernel finishes q, k and v itself
             out = torch.empty((nd, s.num_heads * s.head_dim), dtype=cache.data.dtype, device=cache.data.device)
-            splits = batch.decode_splits
-            need = ops.decode_scratch_floats(nd, s.num_heads, s.head_dim, splits)
-            scratch = batch.workspace.floats("attention_decode", need) if need else None
             ops.attention_decode_fused(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, cache.data, table, batch.seq_lens,
-                                       out, scratch, splits, s.num_heads, s.num_kv_heads, s.head_dim, rotary_dim, page,
+                                       out, scratch, dec.splits, s.num_heads, s.num_kv_heads, s.head_dim, rotary_dim, page,
                                        self.scale, s.window, write_kv=write_cache)
-            return getattr(ops, "linear_auto", ops.linear)(out, self.w_o, self.b_o)
+            return ops.linear_auto(out, self.w_o, self.b_o)
         q = ops.qk_norm_rope_write(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, batch.positions,
                                    batch.token_req, table, cache.data, s.num_heads, s.num_kv_heads, s.head_dim,
                                    rotary_dim, page, write_kv=write_cache)
         out = torch.empty_like(q)       # [tokens, heads * head_dim]
         if nd:
-            splits = batch.decode_splits
-            need = ops.decode_scratch_floats(nd, s.num_heads, s.head_dim, splits)
-            scratch = batch.workspace.floats("attention_decode", need) if need else None
-            ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out[:nd], scratch, splits,
+            ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out[:nd], scratch, dec.splits,
                                  s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window)
         if batch.num_requests > nd:
-            rows = ops.prefill_tile_rows(q.dtype, s.head_dim, page, batch.num_tokens - nd)
-            tile_req, tile_start = batch.tiles(rows)
+            tile_req, tile_start = plan.tiles
             ops.attention_prefill(q, cache.data, table, batch.cu_seqlens, batch.prefix_lens, tile_req, tile_start,
-                                  out, s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window, tile_rows=rows)
-        return getattr(ops, "linear_auto", ops.linear)(out, self.w_o, self.b_o)
+                                  out, s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window,
+                                  tile_rows=plan.tile_rows)
+        return ops.linear_auto(out, self.w_o, self.b_o)

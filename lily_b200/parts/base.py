@@ -23,8 +23,13 @@ Interfaces
 ``Mixer.state_need()`` -> ``StateNeed`` (fixed-size per-request state) or None.
 ``Mixer.forward(x, batch, cache, state, write_cache)`` -> [tokens, hidden] delta.
 ``FeedForward.forward(x, batch)`` -> [tokens, hidden] delta.
+``Mixer.forward`` reads the step from ``batch`` (device tensors; host lists when it is not
+                        ``graph_safe``) and may keep a plan of its own there (``batch.plan``).
+``FeedForward.forward(x, batch)`` -> [tokens, hidden] delta.
 ``Norm.forward(residual, delta, delta_bias, rows, write_residual)`` -> normed activations.
-``Block.forward(residual, delta, batch, cache, state, write_cache)`` -> next pending delta.
+``Block.mixers``     -> the mixers of the block, in a fixed order; each run of the block gets a
+                        cache layer and a state tensor for each of them (``RunSlots``).
+``Block.forward(residual, delta, batch, run)`` -> next pending delta.
 """
 
 from __future__ import annotations
@@ -124,10 +129,26 @@ class Norm(Part):
         raise NotImplementedError
 
 
-class Block(Part):
-    mixer: Mixer
+@dataclass
+class RunSlots:
+    """What one run of a block (one position of the schedule) owns: for each mixer of the block, in the
+    order of ``Block.mixers``, its layer of the paged cache (or None) and its per-request state tensor
+    ``[slots + 1, *shape]`` (or None); ``write_cache`` False when the run reads another run's cache."""
 
-    def forward(self, residual, delta, batch, cache, state, write_cache: bool = True):
+    caches: List[Any]
+    states: List[Any]
+    write_cache: bool = True
+
+
+class Block(Part):
+    """An arrangement of mixers, feed-forwards and norms around the residual stream.  A block kind is built
+    from a spec of its own (any dataclass with ``kind`` and ``prefix``); the model asks it only for
+    ``mixers``, ``parts``, ``tensors``, ``load`` and ``forward``."""
+
+    mixers: Tuple[Mixer, ...] = ()
+    parts: Tuple[Part, ...] = ()
+
+    def forward(self, residual, delta, batch, run: RunSlots):
         raise NotImplementedError
 
 
@@ -179,7 +200,8 @@ def _load_builtin_parts() -> None:
 
 @dataclass
 class BlockSpec:
-    """One block: its checkpoint prefix and the specs of its parts."""
+    """The pre-norm block (kind "prenorm"): its checkpoint prefix and the specs of its parts.  Another block
+    kind brings a spec class of its own; ``ModelSpec.blocks`` takes any mix of them."""
 
     prefix: str
     mixer: Any
@@ -210,7 +232,7 @@ class ModelSpec:
     architecture: str
     vocab_size: int
     hidden_size: int
-    blocks: List[BlockSpec]
+    blocks: List[Any]                                 # BlockSpec, or the spec of any registered block kind
     schedule: List[ScheduleEntry]
     final_norm: Any
     embed_name: str = "model.embed_tokens.weight"
@@ -219,3 +241,6 @@ class ModelSpec:
     max_position: int = 4096
     eos_token_ids: List[int] = field(default_factory=list)
     ignored_tensors: Tuple[str, ...] = ("rotary_emb.inv_freq",)   # lily/models/llama.py:217-218
+    embed_scale: float = 1.0                          # the embedding rows are multiplied by this
+    logit_scale: float = 1.0                          # logits = logit_scale * (x . head^T) ...
+    logit_softcap: Optional[float] = None             # ... then cap * tanh(. / cap) when given

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from typing import Dict
 
-from lily_b200.parts.base import Block, BlockSpec, BuildContext, TensorSpec, build_part, register_part
+from lily_b200.parts.base import Block, BlockSpec, BuildContext, RunSlots, TensorSpec, build_part, register_part
 
 
 @register_part("block", "prenorm")
@@ -21,6 +21,7 @@ class PreNormBlock(Block):
         self.mixer = build_part("mixer", spec.mixer, f"{p}.{spec.mixer_name}", ctx)
         self.norm_post = build_part("norm", spec.norm_post, f"{p}.{spec.norm_post_name}", ctx)
         self.feed_forward = build_part("feed_forward", spec.feed_forward, f"{p}.{spec.feed_forward_name}", ctx)
+        self.mixers = (self.mixer,)
         self.parts = (self.norm_in, self.mixer, self.norm_post, self.feed_forward)
 
     def tensors(self) -> Dict[str, TensorSpec]:
@@ -33,8 +34,8 @@ class PreNormBlock(Block):
         for part in self.parts:
             part.load(get)
 
-    def forward(self, residual, delta, batch, cache, state, write_cache: bool = True):
+    def forward(self, residual, delta, batch, run: RunSlots):
         x = self.norm_in.forward(residual, delta)
-        a = self.mixer.forward(x, batch, cache, state, write_cache)
+        a = self.mixer.forward(x, batch, run.caches[0], run.states[0], run.write_cache)
         y = self.norm_post.forward(residual, a)
         return self.feed_forward.forward(y, batch)

@@ -43,13 +43,12 @@ class SwiGLU(FeedForward):
         gate = get(f"{p}.gate_proj.weight")
         h = self.spec.hidden_size
         self.w_gate_up = torch.empty((2 * i, h), dtype=gate.dtype, device=gate.device)
-        fused = gate.dtype == torch.bfloat16 and i % 128 == 0 and hasattr(self.ctx.ops, "gemm_tc")
-        if fused:
-            self.block = 128
-            runs = self.w_gate_up.view(i // 128, 2, 128, h)
-            runs[:, 0].copy_(gate.view(i // 128, 128, h))
+        self.block = b = self.ctx.ops.gate_up_interleave(gate.dtype, i)
+        if b:
+            runs = self.w_gate_up.view(i // b, 2, b, h)
+            runs[:, 0].copy_(gate.view(i // b, b, h))
             del gate
-            runs[:, 1].copy_(get(f"{p}.up_proj.weight").view(i // 128, 128, h))
+            runs[:, 1].copy_(get(f"{p}.up_proj.weight").view(i // b, b, h))
         else:
             self.w_gate_up[:i].copy_(gate)
             del gate
@@ -58,7 +57,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, batch):
         ops = self.ctx.ops
-        product = getattr(ops, "linear_auto", ops.linear)        # partial sums for a few tokens, else [M, N]
+        product = ops.linear_auto                                # partial sums for a few tokens, else [M, N]
         if self.block and x.shape[0] >= ops.TC_MIN_ROWS and ops.gemm_tc_takes(x, self.w_gate_up):
             act = ops.gemm_tc(x, self.w_gate_up, silu_mul_block=True)
         elif self.block:

@@ -8,19 +8,40 @@ compute in float32 and round once to the output dtype.  Nothing in ``lily_b200``
 
 from __future__ import annotations
 
+from dataclasses import dataclass
 
 import torch
+
+launches = {"count": 0}        # the kernels' Python faces count their launches here; these statements launch nothing
+TC_MIN_ROWS = 65               # as the kernels: products of this many rows and more take the fused gate/up epilogue
+FUSE_DECODE = True             # tests flip this to send all-decode steps through either form of the attention
 
 
 def library():
     return None
 
 
-def embed(table, ids, out=None, future=None):
+def sm_count():
+    return 148
+
+
+def _sum(t):
+    """Kernels that take a product take it whole or as float32 partial sums [splits, rows, cols]."""
+    return t.sum(0) if t.dim() == 3 else t
+
+
+def embed(table, ids, out=None, future=None, scale=1.0):
     ids = ids.long()
     if future is not None:
         ids = torch.where(ids < 0, future.long()[(-ids - 1).clamp(min=0)], ids)
-    return table[ids].float()
+    return table[ids].float() * scale
+
+
+def logit_transform(logits, scale=1.0, softcap=None):
+    logits.mul_(scale)
+    if softcap:
+        logits.copy_(softcap * torch.tanh(logits / softcap))
+    return logits
 
 
 def scatter_tokens(tokens, logit_rows, token_req, slots, future):
@@ -29,6 +50,8 @@ def scatter_tokens(tokens, logit_rows, token_req, slots, future):
 
 
 def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_residual=True, out=None):
+    if delta is not None:
+        delta = _sum(delta)
     if rows is not None:
         v = resid[rows.long()]
         if delta is not None:
@@ -47,17 +70,20 @@ def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_residual=
 
 
 def silu_mul(gate_up, out_dtype=None, out=None, block=None):
+    out_dtype = out_dtype or gate_up.dtype
+    gate_up = _sum(gate_up)
     i = gate_up.shape[1] // 2
     if block:
         runs = gate_up.view(gate_up.shape[0], i // block, 2, block)
         g, u = runs[:, :, 0].reshape(-1, i).float(), runs[:, :, 1].reshape(-1, i).float()
     else:
         g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
-    return ((g / (1 + torch.exp(-g))) * u).to(gate_up.dtype)
+    return ((g / (1 + torch.exp(-g))) * u).to(out_dtype)
 
 
 def qk_norm_rope_write(qkv, q_gain, k_gain, eps, cos, sin, positions, token_req, block_table, kv_layer, nq, nkv, d,
                        rotary_dim, page_size, write_kv=True, q_out=None):
+    qkv = _sum(qkv)
     n = qkv.shape[0]
     x = qkv.float().view(n, nq + 2 * nkv, d)
     q, k, v = x[:, :nq], x[:, nq:nq + nkv], x[:, nq + nkv:]
@@ -84,7 +110,7 @@ def qk_norm_rope_write(qkv, q_gain, k_gain, eps, cos, sin, positions, token_req,
         within = pos % page_size
         kv_layer[page, 0, :, within] = k.to(kv_layer.dtype)
         kv_layer[page, 1, :, within] = v.to(kv_layer.dtype)
-    return q.reshape(n, nq * d).to(qkv.dtype)
+    return q.reshape(n, nq * d).to(kv_layer.dtype)
 
 
 def cast(x, dtype):
@@ -98,8 +124,74 @@ def linear(x, weight, bias=None, out_dtype=None):
     return out.to(out_dtype or x.dtype)
 
 
+def linear_split(x, weight, splits=None):
+    """For a few tokens the product comes as float32 partial sums over slices of K (here: two halves)."""
+    m, k = x.shape
+    if m > 16 or k % 2 or (splits is not None and splits < 1):
+        return None
+    n = splits or 2
+    if k % n:
+        return None
+    xs, ws = x.float().view(m, n, k // n), weight.float().view(-1, n, k // n)
+    return torch.einsum("msk,nsk->smn", xs, ws).contiguous()
+
+
+def linear_auto(x, weight, bias=None):
+    if bias is None:
+        parts = linear_split(x, weight)
+        if parts is not None:
+            return parts
+    return linear(x, weight, bias)
+
+
+def logits(x, head):
+    return linear(x, head, out_dtype=torch.float32)
+
+
+def gate_up_interleave(dtype, intermediate):
+    return 128 if dtype == torch.bfloat16 and intermediate % 128 == 0 else None
+
+
+def gemm_tc_takes(x, weight):
+    return x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+
+
+def gemm_tc(x, weight, bias=None, silu_mul_block=False):
+    out = linear(x, weight, bias, out_dtype=torch.float32)
+    return silu_mul(out, x.dtype, block=128) if silu_mul_block else out.to(x.dtype)
+
+
+def uses_tensor_cores(dtype, d):
+    return dtype == torch.bfloat16 and d in (64, 128, 192, 256)
+
+
 def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0):
     return 32
+
+
+def prefill_tiles(prefix_lens, new_lens, first, rows, device):
+    pairs = [(r, s) for r in range(first, len(new_lens)) for s in range(0, new_lens[r], rows)]
+    both = torch.tensor([[r for r, _ in pairs], [s for _, s in pairs]], dtype=torch.int32).reshape(2, -1).to(device)
+    return both[0].contiguous(), both[1].contiguous()
+
+
+def decode_clusters(d, splits, group):
+    return 0
+
+
+@dataclass(frozen=True)
+class DecodePlan:
+    splits: int
+    fused: bool
+    scratch_floats: int
+    arm: str
+
+
+def plan_decode_attention(dtype, requests, nq, nkv, d, max_seq_len):
+    if requests == 0:
+        return DecodePlan(1, False, 0, "single")
+    splits = 2 if max_seq_len >= 32 else 1
+    return DecodePlan(splits, FUSE_DECODE, decode_scratch_floats(requests, nq, d, splits), "wave" if splits > 1 else "single")
 
 
 def decode_scratch_floats(requests, nq, d, splits):
@@ -147,16 +239,11 @@ def attention_decode(q, kv_layer, block_table, seq_lens, out, scratch, splits, n
         out[r] = o.reshape(nq * d).to(out.dtype)
 
 
-def decode_fused_takes(dtype, d, blocks=0):
-    return True
-
-
 def attention_decode_fused(qkv, q_gain, k_gain, eps, cos, sin, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv,
                            d, rotary_dim, page_size, scale, window=None, write_kv=True):
     """What the one kernel does, as the two statements it replaces: every request brings one token, at position
     seq_len - 1."""
-    if qkv.dim() == 3:
-        qkv = qkv.sum(0)
+    qkv = _sum(qkv)
     n = qkv.shape[0]
     q = qk_norm_rope_write(qkv, q_gain, k_gain, eps, cos, sin, (seq_lens - 1).to(torch.int32),
                            torch.arange(n, dtype=torch.int32, device=qkv.device), block_table, kv_layer, nq, nkv, d, rotary_dim,

@@ -71,10 +71,36 @@ def test_wanted_rows_come_in_the_given_order(setup):
 def test_decode_splits_follow_the_clusters_that_fit():
     """With the kernel's answer on how many clusters of s blocks fit (a B200's, head size 128), the most ranges
     whose clusters are all resident; without it, or with more rows than clusters of two, the wave rule."""
-    from lily_b200.engine.batch import choose_decode_splits
+    from lily_b200.csrc.ops import choose_decode_splits
     room = {2: 222, 3: 142, 4: 104, 5: 82, 6: 71, 7: 56, 8: 48, 9: 45, 10: 41, 11: 31, 12: 31, 13: 28, 14: 24, 15: 24, 16: 21}
     pick = lambda b, ctx=4096: choose_decode_splits(b, 8, ctx, clusters=lambda s: room.get(s, 0))
     assert [pick(b) for b in (1, 2, 3, 4, 6, 8, 12, 16, 24)] == [16, 16, 13, 10, 8, 6, 4, 3, 2]
     assert pick(1, 1024) == 4 and pick(8, 1024) == 4 and pick(8, 300) == 1            # at least 256 keys a range
     assert pick(32) == choose_decode_splits(32, 8, 4096) == 7 and pick(64) == 4       # no cluster fits: the wave rule
     assert choose_decode_splits(8, 8, 4096) == 6 and choose_decode_splits(0, 8, 4096) == 1
+
+
+def test_both_forms_of_the_decode_step_agree(setup, monkeypatch):
+    """A step in which every request brings one token may start its attention from the qkv product or run the
+    norm / rotation / cache-write kernel first: same logits, same cache."""
+    import kernel_refs
+    cfg, weights, path = setup
+    ids = tiny_models.random_tokens(60, cfg["vocab_size"], 4)
+    want = plain_impl.all_logits(cfg, weights, ids)
+    for fused in (True, False):
+        monkeypatch.setattr(kernel_refs, "FUSE_DECODE", fused)
+        runner = make_runner(path, page_size=16, max_tokens=160)
+        assert float((run_portions(runner, ids, [30] + [1] * 30) - want).abs().max()) < TOL, fused
+
+
+def test_bfloat16_layouts_on_the_host(setup):
+    """In bfloat16 the fused gate/up matrix alternates runs of gate and up rows when the kernels ask for it, and
+    a few tokens' products come as partial sums: the plain statements follow, so the packing is checked here."""
+    cfg, weights, path = setup
+    ids = tiny_models.random_tokens(90, cfg["vocab_size"], 6)
+    want = plain_impl.all_logits(cfg, weights, ids)
+    runner = make_runner(path, dtype="bfloat16", page_size=16, max_tokens=160)
+    scale = float(want.abs().max())
+    for got in (run_whole(runner, ids), run_portions(runner, ids, [70, 3] + [1] * 17)):
+        err = (got - want).abs()
+        assert float(err.max()) < 2e-2 * scale and float(err.mean()) < 3e-3 * scale

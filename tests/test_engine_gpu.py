@@ -13,10 +13,11 @@ from harness import make_runner, model_dir, run_mixed, run_portions, run_whole
 
 pytestmark = pytest.mark.gpu
 
-# float32: rounding only.  bfloat16: activations carry 8 bits; with logits of order one the
-# expected error is a few 1e-3 and the bound below is ten times that.
-TOL = {"float32": 1e-4, "bfloat16": 4e-2}
-MEAN_TOL = {"float32": 1e-5, "bfloat16": 6e-3}
+# float32: rounding only, absolute (logits are of order one).  bfloat16: activations carry 8 bits; the bounds are
+# relative to the largest logit of the sequence, about three times what correct kernels give (largest error
+# 0.2 to 0.6 % of it, mean 0.03 to 0.13 %), so a defect worth a hundredth of a logit fails.
+TOL = {"float32": 1e-4, "bfloat16": 2e-2}
+MEAN_TOL = {"float32": 1e-5, "bfloat16": 3e-3}
 
 
 def rounded(weights, dtype):
@@ -28,8 +29,10 @@ def rounded(weights, dtype):
 
 def close(got, want, dtype, what=""):
     err = (got - want).abs()
-    assert float(err.max()) < TOL[dtype], f"{what}: max error {float(err.max()):.3e} at {int(err.argmax()) // want.shape[1]}"
-    assert float(err.mean()) < MEAN_TOL[dtype], f"{what}: mean error {float(err.mean()):.3e}"
+    scale = float(want.abs().max()) if dtype == "bfloat16" else 1.0
+    assert float(err.max()) < TOL[dtype] * scale, \
+        f"{what}: max error {float(err.max()):.3e} at {int(err.argmax()) // want.shape[1]} (logits up to {scale:.2f})"
+    assert float(err.mean()) < MEAN_TOL[dtype] * scale, f"{what}: mean error {float(err.mean()):.3e} (logits up to {scale:.2f})"
 
 
 @pytest.fixture(scope="module", params=["tiny_qwen3", "tiny_llama", "odd_qwen3", "odd_llama"])

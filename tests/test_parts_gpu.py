@@ -11,7 +11,7 @@ from lily_b200.cache.kv_cache import KVCacheManager
 from lily_b200.config.model_config import RopeScaling
 from lily_b200.engine.batch import StepEntry, Workspace, build_step_batch
 from lily_b200.parts.attention import AttentionSpec, LayerCache
-from lily_b200.parts.base import BlockSpec, BuildContext, build_part
+from lily_b200.parts.base import BlockSpec, BuildContext, RunSlots, build_part
 from lily_b200.parts.mlp import SwiGLUSpec
 from lily_b200.parts.norm import RMSNormSpec
 from lily_b200.parts.rope import RopeSpec
@@ -166,7 +166,7 @@ def test_prenorm_block(dtype):
     slot = cache.open_request()
     batch = one_request_batch(cache, t, 0, slot)
     r = r0.to(DEV)
-    delta = block.forward(r, d0.to(DEV), batch, LayerCache(0, cache.groups[0].data[0]), None)
+    delta = block.forward(r, d0.to(DEV), batch, RunSlots([LayerCache(0, cache.groups[0].data[0])], [None]))
     if delta.dim() == 3:
         delta = delta.sum(0)
     torch.testing.assert_close((r + delta.float()).cpu(), want_r, **tol(dtype))

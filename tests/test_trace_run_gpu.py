@@ -40,39 +40,63 @@ def replay(path, dtype, steps, max_tokens, tmp, vocab):
     return rows
 
 
+class Trace:
+    """Builds the steps of a replay and remembers which logits each step's file should hold."""
+
+    def __init__(self, requests):
+        self.requests, self.done = requests, {k: 0 for k in requests}
+        self.steps, self.expect = [], []         # expect[i]: (request, position) of each wanted row of step i
+
+    def step(self, portions, end=(), want=None):
+        """``portions``: request -> how many of its next tokens; every place is wanted unless ``want`` gives, per
+        request, the places among the portion's tokens."""
+        entries, rows = [], []
+        for k, n in portions.items():
+            toks = self.requests[k][self.done[k]:self.done[k] + n]
+            places = list(range(len(toks))) if want is None or k not in want else list(want[k])
+            entries.append({"id": k, "tokens": toks, "want": places})
+            rows += [(k, self.done[k] + w) for w in places]
+            self.done[k] += len(toks)
+        self.steps.append({"step": len(self.steps), "entries": entries, "end": list(end)})
+        self.expect.append(rows)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_qwen3", "tiny_llama"])
-def test_replay_mixed_trace(name, dtype):
+@pytest.mark.parametrize("name", ["tiny_qwen3", "tiny_llama", "odd_qwen3", "odd_llama"])
+def test_replay_in_every_cutting(name, dtype):
+    """One trace through the tool: a request whole; one with its last 32 tokens one by one; one in portions of
+    changing size down to two tokens; then up to four live requests, portions of some beside decoded tokens of
+    others, ends that free pages which later requests take.  The pool holds 320 tokens, so pages are used again
+    from the second request on."""
     cfg = tiny_models.CONFIGS[name]
     v = cfg["vocab_size"]
     with tempfile.TemporaryDirectory() as tmp:
         path, weights = model_dir(cfg, 71, tmp)
         reqs = {k: tiny_models.random_tokens(n, v, 120 + i) for i, (k, n) in enumerate(
-            {"a": 100, "b": 70, "c": 64, "d": 90, "e": 40}.items())}
-        # up to four live; portions beside decoded tokens; ends free pages that later requests reuse
-        plan = [({"a": 60}, []), ({"a": 1, "b": 33}, []), ({"a": 1, "b": 2, "c": 64}, []), ({"b": 35, "a": 1, "d": 5}, ["c"]),
-                ({"a": 37, "d": 2}, ["b"]), ({"d": 83, "e": 3}, ["a"]), ({"e": 1}, ["d"]), ({"e": 36}, ["e"])]
-        steps, done, where = [], {k: 0 for k in reqs}, {k: [] for k in reqs}
-        for i, (step, end) in enumerate(plan):
-            entries = []
-            for k, n in step.items():
-                toks = reqs[k][done[k]:done[k] + n]
-                want = list(range(len(toks))) if k != "c" else [len(toks) - 1, 0]
-                entries.append({"id": k, "tokens": toks, "want": want})
-                where[k].append((i, done[k], want))
-                done[k] += len(toks)
-            steps.append({"step": i, "entries": entries, "end": end})
-        # live tokens, each request rounded up to 64, peak at steps 3 to 5: 128 + 64 + 64 + 64 = 320, five pages of 64
-        rows = replay(path, dtype, steps, 320, tmp, v)
+            {"w": 150, "t": 140, "p": 131, "a": 100, "b": 70, "c": 64, "d": 90, "e": 40}.items())}
+        t = Trace(reqs)
+        t.step({"w": 150}, end=["w"])
+        t.step({"t": 108})
+        for i in range(32):
+            t.step({"t": 1}, end=["t"] if i == 31 else [])
+        for i, n in enumerate([8, 2, 30, 17, 2, 3, 40, 2, 5, 22]):
+            t.step({"p": n}, end=["p"] if i == 9 else [])
+        t.step({"a": 60})
+        t.step({"a": 1, "b": 33})
+        t.step({"a": 1, "b": 2, "c": 64}, want={"c": [63, 0]})
+        t.step({"b": 35, "a": 1, "d": 5}, end=["c"])
+        t.step({"a": 37, "d": 2}, end=["b"])
+        t.step({"d": 83, "e": 3}, end=["a"])
+        t.step({"e": 1}, end=["d"])
+        t.step({"e": 36}, end=["e"])
+        assert all(t.done[k] == len(ids) for k, ids in reqs.items())
+        # live tokens, each request rounded up to 64: 192 at most while one request lives, and in the mixed part
+        # 128 + 64 + 64 + 64 = 320 at its peak: five pages of 64
+        rows = replay(path, dtype, t.steps, 320, tmp, v)
         plain = {k: plain_impl.all_logits(cfg, rounded(weights, dtype), ids) for k, ids in reqs.items()}
-        for i, s in enumerate(steps):
-            at = 0
-            for e in s["entries"]:
-                k = e["id"]
-                start = [w for w in where[k] if w[0] == i][0][1]
-                for w in e["want"]:
-                    close(rows[i][at:at + 1], plain[k][start + w:start + w + 1], dtype, f"step {i} request {k} place {w}")
-                    at += 1
+        for i, expect in enumerate(t.expect):
+            want = torch.stack([plain[k][pos] for k, pos in expect])
+            close(rows[i], want, dtype, f"step {i} ({', '.join(sorted({k for k, _ in expect}))})")
 
 
 def test_replay_past_the_files_max_position():
