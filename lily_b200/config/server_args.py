@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import argparse
 import dataclasses
+import typing
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -59,28 +60,34 @@ class ServerArgs:
             if v is not None and v < 1:
                 raise ValueError(f"{name} must be positive")
 
-    # ---- CLI binding (lily/server_args.py:145-174) ---------------------------
+    # ---- command line: one --flag per field, its type read from the field's annotation ----
+    # (the reference builds its flags from the fields as well, lily/server_args.py:145-174)
 
-    @staticmethod
-    def add_cli_args(parser: argparse.ArgumentParser) -> None:
-        for f in dataclasses.fields(ServerArgs):
-            flag = "--" + f.name.replace("_", "-")
-            default = f.default if f.default is not dataclasses.MISSING else None
-            if isinstance(default, bool):
-                parser.add_argument(flag, action="store_true", default=default)
-            elif f.name == "cuda_graph_bs":
-                parser.add_argument(flag, type=int, nargs="+", default=default)
-            elif isinstance(default, int) or f.type in ("Optional[int]", Optional[int]):
-                parser.add_argument(flag, type=int, default=default)
-            elif isinstance(default, float) or f.type in ("Optional[float]", Optional[float]):
-                parser.add_argument(flag, type=float, default=default)
+    @classmethod
+    def _flag_kinds(cls):
+        """(field name, scalar type, takes a list, default) for every field."""
+        hints = typing.get_type_hints(cls)
+        for f in dataclasses.fields(cls):
+            kind, many = hints[f.name], False
+            if typing.get_origin(kind) is typing.Union:                       # Optional[T]
+                kind = next(a for a in typing.get_args(kind) if a is not type(None))
+            if typing.get_origin(kind) in (list, typing.List):
+                kind, many = typing.get_args(kind)[0], True
+            yield f.name, kind, many, (None if f.default is dataclasses.MISSING else f.default)
+
+    @classmethod
+    def add_cli_args(cls, parser: argparse.ArgumentParser) -> None:
+        for name, kind, many, default in cls._flag_kinds():
+            flag = "--" + name.replace("_", "-")
+            if kind is bool:
+                parser.add_argument(flag, action="store_true", default=bool(default))
             else:
-                parser.add_argument(flag, type=str, default=default)
+                parser.add_argument(flag, type=kind, default=default, **({"nargs": "+"} if many else {}))
 
     @classmethod
     def from_cli_args(cls, args: argparse.Namespace) -> "ServerArgs":
-        names = {f.name for f in dataclasses.fields(cls)}
-        return cls(**{k: v for k, v in vars(args).items() if k in names})
+        given = vars(args)
+        return cls(**{name: given[name] for name, *_ in cls._flag_kinds() if name in given})
 
     @classmethod
     def parse(cls, argv: Optional[List[str]] = None) -> "ServerArgs":

@@ -117,15 +117,19 @@ class Engine:
         return self._tokenizer
 
     def generate_text(self, prompt: str, max_new_tokens: int = 64, chat: bool = True) -> str:
+        """Text in, text out, greedy, for a model folder that holds a tokenizer: the prompt goes through the
+        tokenizer's chat template when it has one and ``chat`` is set (the helper of lily/engine.py:133-142)."""
         tok = self._tok()
-        if chat and getattr(tok, "chat_template", None):
-            ids = tok.apply_chat_template([{"role": "user", "content": prompt}], add_generation_prompt=True, tokenize=True)
-            if not isinstance(ids, list):
-                ids = ids["input_ids"]
+        use_template = chat and bool(getattr(tok, "chat_template", None))
+        if use_template:
+            encoded = tok.apply_chat_template([{"role": "user", "content": prompt}], tokenize=True,
+                                              add_generation_prompt=True)
+            encoded = encoded["input_ids"] if hasattr(encoded, "keys") else encoded
         else:
-            ids = tok.encode(prompt)
-        out = self.generate_greedy(list(ids), max_new_tokens, ignore_eos=False)
-        return tok.decode(out, skip_special_tokens=True)
+            encoded = tok.encode(prompt)
+        produced = self.generate([[int(t) for t in encoded]],
+                                 SamplingParams(max_new_tokens=max_new_tokens, ignore_eos=False))[0]["output_ids"]
+        return tok.decode(produced, skip_special_tokens=True)
 
     def kv_available(self) -> int:
         """Tokens the free pages of the pool can hold."""

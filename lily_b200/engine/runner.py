@@ -25,6 +25,7 @@ from lily_b200.config.model_config import read_model_dir
 from lily_b200.config.registry import resolve_architecture
 from lily_b200.config.server_args import ServerArgs
 from lily_b200.engine.batch import FUTURE, StepBatch, StepEntry, Workspace, build_step_batch, order_entries
+from lily_b200.engine.profiler import DecodeProfiler
 from lily_b200.models.assembled import AssembledModel
 from lily_b200.parts.base import BuildContext, ModelSpec
 from lily_b200.weights.loader import CheckpointSource, load_model_weights
@@ -181,6 +182,7 @@ class ModelRunner:
         self._last_rows: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None
         self.seq_lens: Dict[int, int] = {}
         self._ring = _PinnedRing() if self.device.type == "cuda" else None
+        self.profiler = DecodeProfiler.from_env() if self.device.type == "cuda" else None
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
@@ -325,6 +327,8 @@ class ModelRunner:
         """Runs one step and returns float32 logits ``[sum(len(e.want)), vocab]`` on the device.
         (A step replayed from a graph returns a view of the graph's output, valid until the next
         step of the same batch bucket.)"""
+        if self.profiler is not None:
+            self.profiler.before_step(len(entries) if all(len(e.tokens) == 1 for e in entries) else None)
         bucket = self._graph_bucket(entries)
         if bucket is not None:
             logits = self._decode_with_graph(entries, bucket)

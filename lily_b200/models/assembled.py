@@ -89,12 +89,12 @@ class AssembledModel:
 
     def tensors(self) -> Dict[str, TensorSpec]:
         s = self.spec
-        out = {s.embed_name: TensorSpec((s.vocab_size, s.hidden_size))}
+        out = {s.embed_name: TensorSpec((s.vocab_size, s.hidden_size), short_rows=True)}
         for b in self.blocks:
             out.update(b.tensors())
         out.update(self.final_norm.tensors())
         if s.head_name is not None:
-            out[s.head_name] = TensorSpec((s.vocab_size, s.hidden_size))
+            out[s.head_name] = TensorSpec((s.vocab_size, s.hidden_size), short_rows=True)
         return out
 
     def ignorable(self, name: str) -> bool:

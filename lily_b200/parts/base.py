@@ -52,11 +52,14 @@ class TensorSpec:
           "table":  integer tables; held as int32.
     init  how the random-weights mode draws it: "normal" N(0, std), "gain" 1 + N(0, jitter),
           "zeros".
+    short_rows  vocabulary tables: a checkpoint saved before the vocabulary was padded holds fewer rows; they
+          are taken and the missing rows are zero (lily/layers/vocab_embedding.py:29-35).
     """
 
     shape: Tuple[int, ...]
     role: str = "matrix"
     init: str = "normal"
+    short_rows: bool = False      # the checkpoint may hold fewer rows than ``shape[0]``; the rest is zero
 
 
 # --------------------------------------------------------------------------- needs of a mixer

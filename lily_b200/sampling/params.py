@@ -6,7 +6,7 @@ caller's parameters carry over, and ``stop`` raises when set because nothing her
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Union
+from typing import ClassVar, Dict, List, Optional, Union
 
 
 @dataclass
@@ -29,19 +29,21 @@ class SamplingParams:
     logprobs: bool = False
     top_logprobs: Optional[int] = None
 
+    # what each number may be: (field, lowest, lowest allowed itself?, highest, highest allowed itself?)
+    _RANGES: ClassVar[tuple] = (("max_new_tokens", 1, True, None, True), ("temperature", 0.0, True, None, True),
+               ("top_p", 0.0, False, 1.0, True), ("min_p", 0.0, True, 1.0, False),
+               ("repetition_penalty", 0.0, False, None, True))
+
     def __post_init__(self) -> None:
-        if self.max_new_tokens < 1:
-            raise ValueError("max_new_tokens must be positive")
-        if self.temperature < 0:
-            raise ValueError("temperature must be non-negative")
-        if not (0 < self.top_p <= 1):
-            raise ValueError("top_p must be in (0, 1]")
-        if self.top_k < -1 or self.top_k == 0:
-            raise ValueError("top_k must be -1 or a positive integer")
-        if not (0 <= self.min_p < 1):
-            raise ValueError("min_p must be in [0, 1)")
-        if self.repetition_penalty <= 0:
-            raise ValueError("repetition_penalty must be positive")
+        for name, low, low_ok, high, high_ok in self._RANGES:
+            v = getattr(self, name)
+            below = v < low or (v == low and not low_ok)
+            above = high is not None and (v > high or (v == high and not high_ok))
+            if below or above:
+                span = f"{'[' if low_ok else '('}{low}, {'inf' if high is None else high}{']' if high_ok and high is not None else ')'}"
+                raise ValueError(f"{name} = {v!r} lies outside {span}")
+        if self.top_k != -1 and self.top_k < 1:
+            raise ValueError(f"top_k = {self.top_k!r}: -1 keeps every token, a positive number the k most probable")
         if self.stop:
             raise ValueError("stop strings need a detokenizer; this engine is token in, token out "
                              "(use stop_token_ids)")
@@ -49,13 +51,15 @@ class SamplingParams:
             raise ValueError("top_logprobs must be between 1 and 64")
         if self.n != 1:
             raise ValueError("n must be 1; submit the prompt n times with different seeds")
-        if self.logit_bias is not None:
-            self.logit_bias = {int(k): float(v) for k, v in self.logit_bias.items()}
+        if self.logit_bias:
+            self.logit_bias = {int(token): float(bias) for token, bias in dict(self.logit_bias).items()}
+        else:
+            self.logit_bias = None
 
     @property
     def greedy(self) -> bool:
-        """No randomness: a single deterministic token is produced."""
-        return self.temperature == 0 or self.top_k == 1
+        """Whether the most probable token is taken (temperature 0, or only one token kept)."""
+        return self.top_k == 1 or self.temperature == 0
 
     @property
     def plain(self) -> bool:

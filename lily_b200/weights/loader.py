@@ -70,12 +70,20 @@ class CheckpointSource:
         return self.where[name].tensor(name)
 
 
+def fits(spec: TensorSpec, stored: tuple) -> bool:
+    """Whether a stored tensor of this shape serves: the expected shape, or, for a table that allows it, fewer rows."""
+    want = tuple(spec.shape)
+    if stored == want:
+        return True
+    return bool(spec.short_rows and len(stored) == len(want) and stored[1:] == want[1:] and 0 < stored[0] < want[0])
+
+
 def check(expected: Dict[str, TensorSpec], present: Dict[str, Tuple[torch.dtype, tuple]],
           ignorable: Callable[[str], bool], where: str) -> None:
     missing = sorted(n for n in expected if n not in present)
     unexpected = sorted(n for n in present if n not in expected and not ignorable(n))
     wrong = sorted((n, tuple(present[n][1]), tuple(spec.shape)) for n, spec in expected.items()
-                   if n in present and tuple(present[n][1]) != tuple(spec.shape))
+                   if n in present and not fits(spec, tuple(present[n][1])))
     if missing or unexpected or wrong:
         raise WeightsError(missing, unexpected, wrong, where)
 
@@ -93,6 +101,11 @@ def load_model_weights(model, source, compute_dtype: torch.dtype, device) -> int
         t = source.get(name)
         want = kept_dtype(expected[name], t.dtype, compute_dtype)
         out = t.to(device=device, dtype=want)
+        rows = expected[name].shape[0] if expected[name].shape else 0
+        if out.dim() and out.shape[0] < rows:                       # a short vocabulary table: the rest is zero
+            full = torch.zeros((rows, *out.shape[1:]), dtype=want, device=device)
+            full[:out.shape[0]].copy_(out)
+            out = full
         moved += out.numel() * out.element_size()
         return out
 

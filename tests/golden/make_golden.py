@@ -29,8 +29,8 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
 
-SEEDS = {"tiny_qwen3": 11, "tiny_llama": 12, "odd_qwen3": 13, "odd_llama": 14}
-PROMPT_LEN = {"tiny_qwen3": 40, "tiny_llama": 70, "odd_qwen3": 33, "odd_llama": 48}
+SEEDS = {"tiny_qwen3": 11, "tiny_llama": 12, "odd_qwen3": 13, "odd_llama": 14, "partial_qwen3": 15, "partial_llama": 16}
+PROMPT_LEN = {"tiny_qwen3": 40, "tiny_llama": 70, "odd_qwen3": 33, "odd_llama": 48, "partial_qwen3": 45, "partial_llama": 52}
 PORTIONS = (8, 2, 30, 17, 43)
 
 
@@ -79,7 +79,9 @@ def reference_logits(ref_root: str, model_dir: str, ids, portions=None) -> torch
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2 or not os.path.isfile(os.path.join(sys.argv[1], "lily", "engine.py")):
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/lily-checkout")
+    ref_root = sys.argv[1]
     from safetensors.torch import save_file
 
     import plain_impl

@@ -1,6 +1,8 @@
 """Plain, slow implementation of the Llama / Qwen3 dense decoder, for tests only.
 
-Whole sequences, no cache, float32 on the CPU, one function per part.  It is
+Whole sequences, no cache, one function per part; float32 on the CPU unless the
+weights lie on another device (it follows them) or ``precision(torch.float64)`` is
+in force (the rounding-free yardstick for large layer sizes).  It is
 written from the formulas of CodeMan62/lily (each function cites the file and
 lines it restates) and shares no code with ``lily_b200``: it reads the raw
 ``config.json`` dictionary and the checkpoint's own tensor names
@@ -21,6 +23,26 @@ import torch
 
 Tensor = torch.Tensor
 
+_COMPUTE = [torch.float32]
+
+
+class precision:
+    """``with precision(torch.float64):`` sums and activations in that dtype (the rotation angles stay float32,
+    as lily/layers/rotary.py:49-56 computes them)."""
+
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        _COMPUTE.append(self.dtype)
+
+    def __exit__(self, *exc):
+        _COMPUTE.pop()
+
+
+def _c(t: Tensor) -> Tensor:
+    return t.to(_COMPUTE[-1])
+
 
 # --------------------------------------------------------------------------- config
 
@@ -29,7 +51,8 @@ def read_config(cfg: dict) -> dict:
 
     lily/models/model_config.py:85-170 (head_dim default :98, kv heads :99,
     rope_theta and rope_parameters :101-105, ``type`` alias :108-109, eps :148,
-    tie :147, max positions :128,153, partial rotary :151-152, bias :156).
+    tie :147, max positions :128,153, partial rotary :151-152 (the key itself, else
+    the one inside rope_parameters), bias :156).
     QK-norm is switched by the architecture name, lily/models/qwen3.py:17-37.
     """
     text = cfg.get("text_config", cfg)
@@ -57,7 +80,8 @@ def read_config(cfg: dict) -> dict:
         eps=text.get("rms_norm_eps", 1e-6),
         theta=float(theta),
         rope_scaling=rope_scaling,
-        rotary_dim=int(head_dim * float(text.get("partial_rotary_factor", 1.0))),
+        rotary_dim=int(head_dim * float(text.get("partial_rotary_factor",
+                                                 (rope_params or {}).get("partial_rotary_factor", 1.0)))),
         tie=bool(text.get("tie_word_embeddings", cfg.get("tie_word_embeddings", False))),
         bias=bool(text.get("attention_bias", False)),
         act=text.get("hidden_act", "silu"),
@@ -70,9 +94,9 @@ def read_config(cfg: dict) -> dict:
 def rms_norm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
     """lily/layers/layernorm.py:37-44: variance over the last axis in float32,
     ``x * rsqrt(var + eps)``, then the weight."""
-    xf = x.to(torch.float32)
+    xf = _c(x)
     var = xf.pow(2).mean(dim=-1, keepdim=True)
-    return weight.to(torch.float32) * (xf * torch.rsqrt(var + eps))
+    return _c(weight) * (xf * torch.rsqrt(var + eps))
 
 
 # --------------------------------------------------------------------------- rotary
@@ -112,8 +136,8 @@ def model_inv_freq(c: dict) -> Tensor:
 
 def rope_cos_sin(positions: Tensor, inv_freq: Tensor):
     """lily/layers/rotary.py:52-56: angle = position * inv_freq in float32."""
-    freqs = torch.outer(positions.to(torch.float32), inv_freq)
-    return freqs.cos(), freqs.sin()
+    freqs = torch.outer(positions.to(torch.float32), inv_freq.to(positions.device))
+    return _c(freqs.cos()), _c(freqs.sin())
 
 
 def apply_rope_neox(x: Tensor, cos: Tensor, sin: Tensor, rotary_dim: int) -> Tensor:
@@ -142,7 +166,7 @@ def causal_attention(q: Tensor, k: Tensor, v: Tensor, scale: float,
     kk = k.repeat_interleave(rep, dim=1)
     vv = v.repeat_interleave(rep, dim=1)
     scores = torch.einsum("qhd,khd->hqk", q, kk) * scale
-    pos = torch.arange(t)
+    pos = torch.arange(t, device=q.device)
     seen = pos[None, :] <= pos[:, None]
     if window is not None:
         seen &= pos[None, :] > pos[:, None] - window
@@ -160,9 +184,9 @@ def attention_part(x: Tensor, w: Dict[str, Tensor], prefix: str, c: dict, cos: T
     nq, nkv, d = c["heads"], c["kv_heads"], c["head_dim"]
 
     def proj(name, inp):
-        out = inp @ w[f"{prefix}.{name}.weight"].float().t()
+        out = inp @ _c(w[f"{prefix}.{name}.weight"]).t()
         b = w.get(f"{prefix}.{name}.bias")
-        return out if b is None else out + b.float()
+        return out if b is None else out + _c(b)
 
     q = proj("q_proj", x).view(t, nq, d)
     k = proj("k_proj", x).view(t, nkv, d)
@@ -180,9 +204,9 @@ def attention_part(x: Tensor, w: Dict[str, Tensor], prefix: str, c: dict, cos: T
 
 def swiglu_part(x: Tensor, w: Dict[str, Tensor], prefix: str) -> Tensor:
     """lily/models/llama.py:42-47: ``down(silu(gate(x)) * up(x))``, no bias."""
-    g = x @ w[f"{prefix}.gate_proj.weight"].float().t()
-    u = x @ w[f"{prefix}.up_proj.weight"].float().t()
-    return (torch.nn.functional.silu(g) * u) @ w[f"{prefix}.down_proj.weight"].float().t()
+    g = x @ _c(w[f"{prefix}.gate_proj.weight"]).t()
+    u = x @ _c(w[f"{prefix}.up_proj.weight"]).t()
+    return (torch.nn.functional.silu(g) * u) @ _c(w[f"{prefix}.down_proj.weight"]).t()
 
 
 # --------------------------------------------------------------------------- block and model
@@ -201,9 +225,10 @@ def hidden_states(cfg: dict, w: Dict[str, Tensor], token_ids: Sequence[int]) -> 
     c = read_config(cfg)
     if c["act"] != "silu":
         raise ValueError(c["act"])  # lily/models/llama.py:39-40
-    ids = torch.tensor(list(token_ids), dtype=torch.long)
-    r = w["model.embed_tokens.weight"].float()[ids]
-    cos, sin = rope_cos_sin(torch.arange(len(ids)), model_inv_freq(c))
+    table = w["model.embed_tokens.weight"]
+    ids = torch.tensor(list(token_ids), dtype=torch.long, device=table.device)
+    r = _c(table[ids])
+    cos, sin = rope_cos_sin(torch.arange(len(ids), device=table.device), model_inv_freq(c))
     for layer in range(c["layers"]):
         r = decoder_block(r, w, layer, c, cos, sin)
     return rms_norm(r, w["model.norm.weight"], c["eps"])
@@ -214,7 +239,7 @@ def all_logits(cfg: dict, w: Dict[str, Tensor], token_ids: Sequence[int]) -> Ten
     a tied head reads the embedding table (lily/models/llama.py:175-176)."""
     c = read_config(cfg)
     head = w["model.embed_tokens.weight"] if c["tie"] else w["lm_head.weight"]
-    return hidden_states(cfg, w, token_ids) @ head.float().t()
+    return hidden_states(cfg, w, token_ids) @ _c(head).t()
 
 
 def greedy_generate(cfg: dict, w: Dict[str, Tensor], prompt: Sequence[int], n: int) -> List[int]:

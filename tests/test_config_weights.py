@@ -144,6 +144,33 @@ def test_loader_lists_missing_unexpected_and_wrong_shapes_in_one_error():
         CheckpointSource(tempfile.mkdtemp())
 
 
+def test_short_vocabulary_tables_are_padded_with_zeros():
+    """A checkpoint saved with fewer vocabulary rows than config.json's vocab_size loads; the missing rows of the
+    embedding and of the head are zero (lily/layers/vocab_embedding.py:29-35).  More rows, or another width, do not."""
+    import kernel_refs
+    cfg = tiny_models.TINY_LLAMA
+    w = tiny_models.make_weights(cfg, 2)
+    w["model.embed_tokens.weight"] = w["model.embed_tokens.weight"][:380].clone()
+    w["lm_head.weight"] = w["lm_head.weight"][:377].clone()
+    arch = resolve_architecture(cfg["architectures"])
+    spec = arch.build_spec(arch.config_from_dict(cfg, {}, architecture=arch.name))
+    ctx = BuildContext(torch.device("cpu"), torch.float32, kernel_refs, max_position=8)
+    with tempfile.TemporaryDirectory() as tmp:
+        tiny_models.write_model_dir(tmp, cfg, w)
+        model = AssembledModel(spec, ctx)
+        load_model_weights(model, CheckpointSource(tmp), torch.float32, "cpu")
+    assert model.embed.shape == (384, 128) and model.head.shape == (384, 128)
+    assert torch.equal(model.embed[:380], w["model.embed_tokens.weight"]) and float(model.embed[380:].abs().max()) == 0
+    assert torch.equal(model.head[:377], w["lm_head.weight"]) and float(model.head[377:].abs().max()) == 0
+    w["lm_head.weight"] = torch.zeros(385, 128)
+    w["model.embed_tokens.weight"] = torch.zeros(380, 127)
+    with tempfile.TemporaryDirectory() as tmp:
+        tiny_models.write_model_dir(tmp, cfg, w)
+        with pytest.raises(WeightsError) as e:
+            load_model_weights(AssembledModel(spec, ctx), CheckpointSource(tmp), torch.float32, "cpu")
+    assert [n for n, _, _ in e.value.wrong_shape] == ["lm_head.weight", "model.embed_tokens.weight"]
+
+
 def test_kept_dtypes():
     mat, vec, tab = TensorSpec((2, 2)), TensorSpec((2,), role="vector"), TensorSpec((2,), role="table")
     bf, f32 = torch.bfloat16, torch.float32

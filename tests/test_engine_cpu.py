@@ -17,7 +17,7 @@ from harness import make_runner, model_dir, run_mixed, run_portions, run_whole
 TOL = 2e-5
 
 
-@pytest.fixture(scope="module", params=["tiny_qwen3", "tiny_llama", "odd_qwen3", "odd_llama"])
+@pytest.fixture(scope="module", params=["tiny_qwen3", "tiny_llama", "odd_qwen3", "odd_llama", "partial_qwen3", "partial_llama"])
 def setup(request):
     cfg = tiny_models.CONFIGS[request.param]
     with tempfile.TemporaryDirectory() as tmp:

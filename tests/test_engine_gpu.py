@@ -35,7 +35,7 @@ def close(got, want, dtype, what=""):
     assert float(err.mean()) < MEAN_TOL[dtype] * scale, f"{what}: mean error {float(err.mean()):.3e} (logits up to {scale:.2f})"
 
 
-@pytest.fixture(scope="module", params=["tiny_qwen3", "tiny_llama", "odd_qwen3", "odd_llama"])
+@pytest.fixture(scope="module", params=["tiny_qwen3", "tiny_llama", "odd_qwen3", "odd_llama", "partial_qwen3", "partial_llama"])
 def setup(request):
     cfg = tiny_models.CONFIGS[request.param]
     with tempfile.TemporaryDirectory() as tmp:
@@ -185,3 +185,89 @@ def test_long_decoding_with_four_live_requests(setup, dtype):
     got = run_mixed(runner, reqs, plan)
     for name, ids in reqs.items():
         close(got[name], plain_impl.all_logits(cfg, rounded(weights, dtype), ids), dtype, name)
+
+
+@pytest.mark.parametrize("graphs", [True, False], ids=["graphs", "eager"])
+@pytest.mark.parametrize("live", [20, 70])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["mid_8kv", "random"])
+def test_many_live_requests(which, dtype, live, graphs, monkeypatch):
+    """20 and 70 requests of ragged lengths (5 to 560 tokens) decoding side by side for 44 steps, through captured
+    graphs and without them; a third of them end on the way and others take their slots and pages.  Every decoded
+    row is held to the plain implementation, and the forms the attention took are the ones meant for these sizes:
+    graph buckets past 8, products of 17 to 64 tokens, key ranges merged inside clusters or through scratch and a
+    combine kernel, the attention started from the qkv product or behind the rotation kernel."""
+    import random
+    from lily_b200.csrc import ops
+    from lily_b200.engine.batch import StepEntry
+    if which == "mid_8kv":
+        cfg = dict(tiny_models.MID_QWEN3, num_attention_heads=16, num_key_value_heads=8)
+    else:
+        cfg = dict(tiny_models.random_config(0), max_position_embeddings=1024)     # 20 heads over 4, width 328
+    r = random.Random(live)
+    v = cfg["vocab_size"]
+    plans = []
+    real_plan = ops.plan_decode_attention
+    monkeypatch.setattr(ops, "plan_decode_attention", lambda *a: plans.append(real_plan(*a)) or plans[-1])
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 35, tmp)
+        dev_weights = {k: t.cuda() for k, t in rounded(weights, dtype).items()}
+        steps, swap_at = 44, 15
+        first = [r.choice([5, 17, 64, 130, 300, 517, 560]) + r.randint(0, 3) for _ in range(live)]
+        later = [r.choice([9, 70, 200]) for _ in range(live // 3)]
+        seqs = [tiny_models.random_tokens(n + steps, v, 1000 + i) for i, n in enumerate(first)]
+        newcomers = [tiny_models.random_tokens(n + steps - swap_at, v, 5000 + i) for i, n in enumerate(later)]
+        leaving = list(range(0, live, 3))[:len(newcomers)]
+        need = lambda group: sum(-(-len(ids) // 64) for ids in group)
+        # the pool holds the first set whole, or those who stay and the newcomers: what the leavers give back is
+        # what the newcomers get (the free list hands out the page given back last)
+        pages = max(need(seqs), need([ids for i, ids in enumerate(seqs) if i not in leaving] + newcomers))
+        runner = make_runner(path, dtype=dtype, device="cuda", page_size=64, max_tokens=pages * 64, max_requests=live,
+                             context_length=1024, disable_cuda_graph=not graphs)
+        slots = [runner.open_request() for _ in seqs]
+        for at in range(0, live, 7):                                # prompts go in seven requests a step
+            runner.step([StepEntry(slots[i], seqs[i][:first[i]], []) for i in range(at, min(at + 7, live))])
+        at_pos = list(first)
+        rows = [[] for _ in seqs]
+        for s in range(steps):
+            entries = [StepEntry(slots[i], [seqs[i][at_pos[i]]], [0]) for i in range(len(seqs)) if slots[i] is not None]
+            index = [i for i in range(len(seqs)) if slots[i] is not None]
+            if s == swap_at:
+                # every third request ends; as many new ones bring their prompts beside the others' decoded tokens
+                for i in leaving:
+                    runner.close_request(slots[i])
+                    slots[i] = None
+                entries = [e for e, i in zip(entries, index) if slots[i] is not None]
+                index = [i for i in index if slots[i] is not None]
+                for j, ids in enumerate(newcomers):
+                    seqs.append(ids)
+                    slots.append(runner.open_request())
+                    at_pos.append(0)
+                    rows.append([])
+                    entries.append(StepEntry(slots[-1], ids[:later[j]], [later[j] - 1]))
+                    index.append(len(seqs) - 1)
+            out = runner.step(entries).float()
+            for row, (i, e) in enumerate(zip(index, entries)):
+                rows[i].append((at_pos[i] + len(e.tokens) - 1, out[row].clone()))
+                at_pos[i] += len(e.tokens)
+        for i, slot in enumerate(slots):
+            if slot is not None:
+                runner.close_request(slot)
+        assert runner.cache.held_pages() == [0] and runner.cache.slots.available == live
+        for i, ids in enumerate(seqs):
+            want = plain_impl.all_logits(cfg, dev_weights, ids)
+            got = torch.stack([t for _, t in rows[i]])
+            close(got.cpu(), want[[p for p, _ in rows[i]]].cpu(), dtype, f"request {i}")
+        assert (runner.graph_steps == steps - 1) if graphs else (runner.graph_steps == 0)      # all but the mixed step
+        decode = [p for p in plans if p.arm != "single"]
+        assert decode, plans
+        if which == "mid_8kv":            # 8 kv heads: 160 and 560 (request, kv head) pairs
+            arms = {p.arm for p in decode}
+            if dtype == "bfloat16" and live == 20:
+                assert arms == {"cluster"}, arms                                   # merged inside clusters
+            else:
+                assert arms == {"wave"} and all(p.scratch_floats > 0 for p in decode), arms     # scratch and the combine kernel
+            if live == 70:
+                assert not any(p.fused for p in decode)                            # too many blocks: the rotation kernel runs first
+            elif dtype == "bfloat16":
+                assert any(p.fused for p in decode)

@@ -168,3 +168,24 @@ def test_command_line_generates():
                              cwd=ROOT, capture_output=True, text=True, timeout=600)
         assert out.returncode == 0, out.stderr[-2000:]
         assert json.loads(out.stdout.strip().splitlines()[-1])["output_ids"] == plain_impl.greedy_generate(cfg, weights, p, 6)
+
+
+def test_the_step_profile_names_this_packages_kernels(monkeypatch):
+    """LILY_B200_PROFILE_BS arms the step function: after the window a table says where a decode step's time went."""
+    monkeypatch.setenv("LILY_B200_PROFILE_BS", "3")
+    monkeypatch.setenv("LILY_B200_PROFILE_STEPS", "6")
+    cfg = tiny_models.MID_QWEN3
+    with tempfile.TemporaryDirectory() as tmp:
+        monkeypatch.setenv("LILY_B200_PROFILE_OUT", tmp)
+        path, _ = model_dir(cfg, 5, tmp)
+        from lily_b200 import SamplingParams
+        eng = engine(path, "bfloat16", max_total_tokens=1024)
+        prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], n) for n in (20, 33, 41)]
+        eng.generate(prompts, SamplingParams(max_new_tokens=16, ignore_eos=True))
+        table = eng.runner.profiler.tables[3]
+        assert open(os.path.join(tmp, "decode_step_bs3.txt")).read().strip() == table
+    lines = table.splitlines()
+    assert "batch 3" in lines[0] and "over 6 steps" in lines[0]
+    assert any("attention_mma_kernel" in ln for ln in lines) and any("add_rmsnorm" in ln for ln in lines)
+    per_step = float(lines[2].split()[0])
+    assert 10 < per_step < 5000                     # microseconds of device time a step

@@ -408,6 +408,12 @@ def test_attention_decode_from_the_projection(planes, splits, nq, nkv, d, page, 
     torch.testing.assert_close(one.float(), two.float(), **last_bit, msg="the cache after the step")
     assert float((one.float() - two.float()).abs().gt(0).float().mean()) < 1e-3        # and nearly everywhere the same bits
     torch.testing.assert_close(got.float(), want.float(), **last_bit)
+    # and against the plain statement of the fused step itself (float32 inside, rounded once)
+    plain_cache, plain_out = cache.clone(), torch.zeros_like(want)
+    ref.attention_decode_fused(qkv, qg, kg, 1e-6, cos, sin, plain_cache, table, seq_t, plain_out, None, splits, nq, nkv, d, rd,
+                                page, d ** -0.5, window)
+    torch.testing.assert_close(one.float(), plain_cache.float(), **last_bit, msg="the cache against the plain statement")
+    torch.testing.assert_close(got.float(), plain_out.float(), atol=2e-2, rtol=2e-2)
     # a layer that reads another layer's cache: nothing is written
     kept = two.clone()
     o.attention_decode_fused(qkv * 0.5 if planes > 1 else qkv, qg, kg, 1e-6, cos, sin, kept, table, seq_t, got, scratch, splits,

@@ -40,17 +40,31 @@ def case(dtype, nq, nkv, d, page, seqs, seed):
     return cache, table, q, torch.tensor(seqs, device=DEV, dtype=torch.int32)
 
 
-@pytest.mark.parametrize("dtype,nq,nkv,d,page,splits", [
-    (torch.bfloat16, 32, 8, 128, 64, 6),     # tensor-core kernels
-    (torch.float32, 6, 2, 48, 16, 4),        # CUDA-core kernels
-    (torch.bfloat16, 8, 2, 64, 16, 1),       # one split: no scratch at all
+@pytest.mark.parametrize("dtype,nq,nkv,d,page,splits,through_scratch", [
+    (torch.bfloat16, 32, 8, 128, 64, 6, False),    # tensor-core kernels; these few pairs merge inside clusters
+    (torch.bfloat16, 32, 8, 128, 64, 20, True),    # more ranges than a cluster has blocks: the array and the combine kernel
+    (torch.float32, 6, 2, 48, 16, 4, True),        # CUDA-core kernels
+    (torch.bfloat16, 8, 2, 64, 16, 1, False),      # one split: no scratch at all
 ])
-def test_static_scratch_entry_matches_the_allocating_one(dtype, nq, nkv, d, page, splits):
+def test_static_scratch_entry_matches_the_allocating_one(dtype, nq, nkv, d, page, splits, through_scratch):
     from lily_b200.csrc import ops
     lib, fn = entry()
     code = 1 if dtype == torch.bfloat16 else 0
     tol = dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
     stream = torch.cuda.current_stream().cuda_stream
+    if through_scratch:
+        # which form runs is the kernels' own choice: make sure this case is one that goes through the array
+        pairs = 5 * nkv * -(-(nq // nkv) // 16)
+        assert not (ops.uses_tensor_cores(dtype, d) and pairs <= ops.decode_clusters(d, splits, nq // nkv))
+        # leave NaN in the array (a call whose queries are NaN): the calls below must overwrite all they read
+        cache, table, q, seq_t = case(dtype, nq, nkv, d, page, [700, 3, 1025, 64, 333], 9)
+        junk = torch.zeros_like(q)
+        rc = fn(torch.full_like(q, float("nan")).data_ptr(), cache.data_ptr(), junk.data_ptr(), table.data_ptr(),
+                table.shape[1], seq_t.data_ptr(), 5, splits, nq, nkv, d, page, 0, d ** -0.5, code, stream)
+        assert rc == 0, lib.lily_last_error().decode()
+        torch.cuda.synchronize()
+        assert bool(torch.isnan(junk.float()).any())
+    free_before = None
     # two calls in a row share the array: the second must not see what the first left
     for seqs, seed in (([700, 3, 1025, 64, 333], 1), ([5, 1999, 130], 2)):
         cache, table, q, seq_t = case(dtype, nq, nkv, d, page, seqs, seed)
@@ -64,8 +78,14 @@ def test_static_scratch_entry_matches_the_allocating_one(dtype, nq, nkv, d, page
                 len(seqs), splits, nq, nkv, d, page, 0, d ** -0.5, code, stream)
         assert rc == 0, lib.lily_last_error().decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_allocated() == before                 # nothing taken from torch's allocator ...
         torch.testing.assert_close(got.float(), want.float(), **tol)
+        if free_before is None:
+            free_before = torch.cuda.mem_get_info()[0]                 # ... nor, once warm, from the device itself
+            rc = fn(q.data_ptr(), cache.data_ptr(), got.data_ptr(), table.data_ptr(), table.shape[1], seq_t.data_ptr(),
+                    len(seqs), splits, nq, nkv, d, page, 0, d ** -0.5, code, stream)
+            torch.cuda.synchronize()
+            assert rc == 0 and torch.cuda.mem_get_info()[0] == free_before
 
 
 def test_sizes_beyond_the_static_scratch_are_refused():

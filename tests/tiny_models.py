@@ -93,6 +93,45 @@ ODD_LLAMA = {
     "torch_dtype": "float32",
 }
 
+# Rotation over a part of each head only: the first half of 32 features (the key beside the other sizes), and the
+# first quarter of 64 with the factor given inside rope_parameters together with llama3 scaling.
+PARTIAL_QWEN3 = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "model_type": "qwen3",
+    "num_hidden_layers": 2,
+    "hidden_size": 80,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 2,
+    "head_dim": 32,
+    "partial_rotary_factor": 0.5,
+    "intermediate_size": 136,
+    "vocab_size": 300,
+    "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True,
+    "max_position_embeddings": 384,
+    "torch_dtype": "float32",
+}
+
+PARTIAL_LLAMA = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "num_hidden_layers": 2,
+    "hidden_size": 128,
+    "num_attention_heads": 2,
+    "num_key_value_heads": 1,
+    "head_dim": 64,
+    "intermediate_size": 200,
+    "vocab_size": 500,
+    "rope_parameters": {"rope_theta": 50000.0, "rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0,
+                        "high_freq_factor": 2.0, "original_max_position_embeddings": 32,
+                        "partial_rotary_factor": 0.25},
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 512,
+    "torch_dtype": "float32",
+}
+
 # Head size 128 and widths in multiples of 128, small enough for the CPU: the sizes at which the
 # tensor-core attention, the tcgen05 gate/up kernel and the weight-streaming decode product run
 # inside the engine (the tiny configurations above mostly take the CUDA-core kernels).
@@ -138,7 +177,8 @@ def random_config(seed: int) -> dict:
     return cfg
 
 
-CONFIGS = {"tiny_qwen3": TINY_QWEN3, "tiny_llama": TINY_LLAMA, "odd_qwen3": ODD_QWEN3, "odd_llama": ODD_LLAMA}
+CONFIGS = {"tiny_qwen3": TINY_QWEN3, "tiny_llama": TINY_LLAMA, "odd_qwen3": ODD_QWEN3, "odd_llama": ODD_LLAMA,
+           "partial_qwen3": PARTIAL_QWEN3, "partial_llama": PARTIAL_LLAMA}
 
 
 def make_weights(cfg: dict, seed: int, std: float = 0.02, norm_jitter: float = 0.01,
