@@ -183,7 +183,7 @@ def test_the_step_profile_names_this_packages_kernels(monkeypatch):
         prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], n) for n in (20, 33, 41)]
         eng.generate(prompts, SamplingParams(max_new_tokens=16, ignore_eos=True))
         table = eng.runner.profiler.tables[3]
-        assert open(os.path.join(tmp, "decode_step_bs3.txt")).read().strip() == table
+        assert open(os.path.join(tmp, "decode_step_bs3.txt")).read().strip() == table.strip()
     lines = table.splitlines()
     assert "batch 3" in lines[0] and "over 6 steps" in lines[0]
     assert any("attention_mma_kernel" in ln for ln in lines) and any("add_rmsnorm" in ln for ln in lines)

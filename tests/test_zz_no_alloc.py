@@ -56,11 +56,12 @@ def test_static_scratch_entry_matches_the_allocating_one(dtype, nq, nkv, d, page
         # which form runs is the kernels' own choice: make sure this case is one that goes through the array
         pairs = 5 * nkv * -(-(nq // nkv) // 16)
         assert not (ops.uses_tensor_cores(dtype, d) and pairs <= ops.decode_clusters(d, splits, nq // nkv))
-        # leave NaN in the array (a call whose queries are NaN): the calls below must overwrite all they read
+        # leave NaN in the array (a call over a cache whose values are NaN): the calls below must overwrite all they read
         cache, table, q, seq_t = case(dtype, nq, nkv, d, page, [700, 3, 1025, 64, 333], 9)
+        cache[:, 1] = float("nan")
         junk = torch.zeros_like(q)
-        rc = fn(torch.full_like(q, float("nan")).data_ptr(), cache.data_ptr(), junk.data_ptr(), table.data_ptr(),
-                table.shape[1], seq_t.data_ptr(), 5, splits, nq, nkv, d, page, 0, d ** -0.5, code, stream)
+        rc = fn(q.data_ptr(), cache.data_ptr(), junk.data_ptr(), table.data_ptr(), table.shape[1], seq_t.data_ptr(), 5,
+                splits, nq, nkv, d, page, 0, d ** -0.5, code, stream)
         assert rc == 0, lib.lily_last_error().decode()
         torch.cuda.synchronize()
         assert bool(torch.isnan(junk.float()).any())
