@@ -10,6 +10,7 @@ from L2, results as achieved GB/s or TFLOP/s and as a fraction of the measured p
     python -m lily_b200.bench.kbench rope --tokens 2048
     python -m lily_b200.bench.kbench linear --tokens 8 --n 4096 --k 12288          (library product)
     python -m lily_b200.bench.kbench linear_split --tokens 8 --n 4096 --k 12288    (this package's decode product)
+    python -m lily_b200.bench.kbench swiglu_skinny --tokens 8 --n 24576 --k 4096   (decode gate/up product + SiLU*mul)
     python -m lily_b200.bench.kbench gemm_tc --tokens 2048 --n 6144 --k 4096       (tcgen05 product)
     python -m lily_b200.bench.kbench gemm_tc_silu --tokens 2048 --n 24576 --k 4096 (tcgen05 product + SiLU*mul)
 
@@ -83,7 +84,7 @@ def time_ms(fns, reps, warmup=3, graph=False):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attention_decode", "attention_decode_fused", "attention_prefill", "add_rmsnorm", "silu_mul", "rope", "linear", "linear_split", "gemm_tc", "gemm_tc_silu"])
+    ap.add_argument("kernel", choices=["attention_decode", "attention_decode_fused", "attention_prefill", "add_rmsnorm", "silu_mul", "rope", "linear", "linear_split", "gemm_tc", "gemm_tc_silu", "swiglu_skinny", "swiglu_library"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
@@ -198,7 +199,14 @@ def main() -> int:
         for _ in range(a.copies):
             x = torch.randn(a.tokens, a.k, device=dev, generator=g).to(dt)
             w = torch.randn(a.n, a.k, device=dev, generator=g).to(dt)
-            if a.kernel == "linear_split":
+            if a.kernel == "swiglu_skinny":          # n is the fused matrix's height, 2 x intermediate
+                need = ops.swiglu_skinny_need(a.tokens, a.n // 2, a.k, dt, 128)
+                scratch = torch.empty(need[0], device=dev)
+                counters = torch.zeros(need[1], device=dev, dtype=torch.int32)
+                fns.append(lambda x=x, w=w, scratch=scratch, counters=counters: ops.swiglu_skinny(x, w, 128, scratch, counters))
+            elif a.kernel == "swiglu_library":       # what it replaces: the library product and the SiLU*mul kernel
+                fns.append(lambda x=x, w=w: ops.silu_mul(ops.linear(x, w), block=128))
+            elif a.kernel == "linear_split":
                 fns.append(lambda x=x, w=w: ops.linear_split(x, w, splits=a.splits or None))
             elif a.kernel == "gemm_tc":
                 fns.append(lambda x=x, w=w: ops.gemm_tc(x, w))

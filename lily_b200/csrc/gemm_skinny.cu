@@ -17,6 +17,8 @@
 // Requires K % 64 == 0; N and M are free (M <= 64).
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace lily {
 namespace skinny {
 
@@ -24,7 +26,9 @@ constexpr int KB = 64;            // granule of k: K must be a multiple of it, s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+    // the hint lets L2 fetch the 256-byte line pair: a warp comes back for the other half of the pair with its next
+    // tile, and DRAM serves longer bursts (measured on a B200: 8 x 4096 x 12288 in 17.8 us with the hint, 19.0 without)
+    asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
@@ -183,6 +187,244 @@ static int launch(const __nv_bfloat16* x, const __nv_bfloat16* w, float* parts, 
     return 0;
 }
 
+
+// ---------------------------------------------------------------------------- gate/up product with SiLU*mul
+//
+// out[m][o] = silu(x[m] . gate[o]) * (x[m] . up[o]) for up to 8 tokens, the fused gate/up matrix streamed once.
+//
+// The fused matrix holds runs of `run` gate rows followed by the `run` up rows of the same outputs.  A warp owns 8
+// outputs: the 16-row side of its mma tile is their 8 gate rows followed by their 8 up rows, so that a lane ends up
+// with the gate and the up sum of the same (output, token) in its own accumulator and forms SiLU*mul in registers.
+//
+// The work is cut into units of (block of 8 * WARPS outputs, 64 k).  The units, row block after row block, are dealt
+// out in equal contiguous stretches to a grid that is resident all at once (one block a SM), so every
+// block streams the same number of bytes whatever the matrix's height: no ragged second round of blocks.  A stretch
+// ends where it ends, usually in the middle of a row block's k range; a row block is therefore finished by two or
+// three blocks.  Each leaves its partial sums in scratch and counts itself in; the one that counts in last adds all
+// the partial sums up, in the order of their k ranges and not of their arrival, applies SiLU*mul and writes bfloat16.
+// Nobody waits for anybody (no spinning), and the counter goes back to zero for the next launch.
+template <int WARPS, int STAGES, bool XSMEM, int KT>
+__global__ void __launch_bounds__(WARPS * 32)
+skinny_swiglu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                     __nv_bfloat16* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
+                     int M, int I, int K, int run, int row_blocks, int max_seg, int x_slots) {
+    static_assert(!XSMEM || KT == 64, "x is staged in shared memory in blocks of 64 k");
+    constexpr int PIECES = KT / 8, PITCH = KT * 2, TILE = 16 * PITCH, COPIES = KT / 16, OUTS = 8 * WARPS;
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int s_arrived;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    unsigned char* ring = smem + (size_t)warp * STAGES * TILE;
+    unsigned char* xs = smem + (size_t)WARPS * STAGES * TILE;          // [8 tokens][x_slots * 8 pieces], pieces swizzled
+    const int kblocks = K / KT;
+    const long long units = (long long)row_blocks * kblocks;
+    const long long G = gridDim.x;
+    const long long u0 = (long long)blockIdx.x * units / G, u1 = (long long)(blockIdx.x + 1) * units / G;
+    const int n = (int)(u1 - u0);
+    if (n <= 0) {                                       // more blocks than units: nothing to do, but keep the chain going
+        pdl_wait();
+        pdl_launch_dependents();
+        return;
+    }
+    const bool x_by_unit = n <= kblocks;                // x is staged per unit of the stretch, else for every k block once
+    const int chunks = x_slots * 8;
+
+    // the weight stream: copy i of a lane moves piece (32 i + lane) % PIECES of tile row (32 i + lane) / PIECES
+    int issue_rb = (int)(u0 / kblocks), issue_kb = (int)(u0 % kblocks), issued = 0;
+    const __nv_bfloat16* src[COPIES];
+    uint32_t dst[COPIES];
+    auto rows_of = [&](int rb) {
+#pragma unroll
+        for (int i = 0; i < COPIES; ++i) {
+            const int r = (32 * i + lane) / PIECES, piece = (32 * i + lane) % PIECES;
+            const int o = min(rb * OUTS + warp * 8 + (r & 7), I - 1);
+            const size_t row = (size_t)(o / run) * 2 * run + (o % run) + (size_t)(r >> 3) * run;
+            src[i] = w + row * K + piece * 8;
+            dst[i] = (uint32_t)(r * PITCH + (((piece & ~7) | ((piece ^ r) & 7)) << 4));
+        }
+    };
+    rows_of(issue_rb);
+    auto issue = [&]() {                                // the next unit of the stretch
+        const uint32_t base = smem_u32(ring + (issued % STAGES) * TILE);
+#pragma unroll
+        for (int i = 0; i < COPIES; ++i) cp_async16(base + dst[i], src[i] + (size_t)issue_kb * KT);
+        ++issued;
+        if (++issue_kb == kblocks) {
+            issue_kb = 0;
+            rows_of(++issue_rb);
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {              // the weights depend on no kernel: they start before the wait
+        if (issued < n) issue();
+        cp_async_commit();
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+
+    // x of the k blocks this stretch meets; rows beyond M are zero.  (Without XSMEM the lanes read their share of
+    // x from global memory, 64 k ahead: x is small and stays in the caches, and all shared memory goes to the rings.)
+    const int first_kb = (int)(u0 % kblocks);
+    const int staged = XSMEM ? (x_by_unit ? n : kblocks) : 0;
+    for (int i = tid; i < 8 * staged * 8; i += WARPS * 32) {
+        const int r = i / (staged * 8), rest = i % (staged * 8), slot = rest / 8, piece = rest % 8;
+        const int kb = x_by_unit ? (first_kb + slot) % kblocks : slot;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < M) v = *reinterpret_cast<const uint4*>(x + (size_t)r * K + (size_t)kb * KT + piece * 8);
+        const int ch = slot * 8 + piece;
+        *reinterpret_cast<uint4*>(xs + ((size_t)r * chunks + (ch ^ (r & 7))) * 16) = v;
+    }
+    if (XSMEM) __syncthreads();
+
+    // a lane's share of x for 64 k: token g, for each of the four k16 steps the pairs at 2c and 2c + 8
+    const __nv_bfloat16* xrow = x + (size_t)min(g, M - 1) * K + 2 * c;
+    uint32_t xf[8], xnext[8];
+    auto load_x = [&](size_t k0, uint32_t (&f)[8]) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t* p = reinterpret_cast<const uint32_t*>(xrow + k0 + kk * 16);
+            f[2 * kk] = g < M ? __ldg(p) : 0u;
+            f[2 * kk + 1] = g < M ? __ldg(p + 4) : 0u;
+        }
+    };
+    if (!XSMEM) load_x((size_t)first_kb * KT, xnext);
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int rb = (int)(u0 / kblocks), kb = first_kb;
+    for (int i = 0; i < n; ++i) {
+        cp_async_wait<STAGES - 2>();
+        __syncwarp();
+        if (issued < n) issue();
+        cp_async_commit();
+        const uint32_t tile = smem_u32(ring + (i % STAGES) * TILE);
+        const int slot = x_by_unit ? i : kb;
+#pragma unroll
+        for (int q = 0; q < KT / 64; ++q) {             // 64 k at a time
+            if (!XSMEM) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) xf[j] = xnext[j];
+                // the next 64 k: of this unit, or the first of the next unit
+                if (q + 1 < KT / 64) load_x((size_t)kb * KT + (q + 1) * 64, xnext);
+                else if (i + 1 < n) load_x((size_t)(kb + 1 == kblocks ? 0 : kb + 1) * KT, xnext);
+            }
+#pragma unroll
+            for (int kq = 0; kq < 4; ++kq) {
+                const int kk = q * 4 + kq;
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                const int r = lane & 15, ch = kk * 2 + (lane >> 4);
+                ldmatrix_x4(tile + r * PITCH + (((ch & ~7) | ((ch ^ r) & 7)) << 4), a0, a1, a2, a3);
+                if (XSMEM) {
+                    const int rr = lane & 7, xch = slot * 8 + kk * 2 + ((lane >> 3) & 1);
+                    ldmatrix_x4(smem_u32(xs + ((size_t)rr * chunks + (xch ^ (rr & 7))) * 16), b0, b1, b2, b3);
+                } else {
+                    b0 = xf[2 * kq];
+                    b1 = xf[2 * kq + 1];
+                }
+                mma_bf16(acc, a0, a1, a2, a3, b0, b1);
+            }
+        }
+        const bool row_block_ends = kb == kblocks - 1;
+        if (row_block_ends || i == n - 1) {
+            // which blocks share this row block: block b holds unit u when b = ceil((u + 1) G / units) - 1
+            const long long lo = (long long)rb * kblocks, hi = lo + kblocks - 1;
+            const int b_first = (int)(((lo + 1) * G + units - 1) / units - 1);
+            const int b_last = (int)(((hi + 1) * G + units - 1) / units - 1);
+            const int nseg = b_last - b_first + 1, myseg = (int)blockIdx.x - b_first;
+            bool finish = nseg == 1;
+            if (!finish) {
+                float4* mine = reinterpret_cast<float4*>(scratch) + ((size_t)rb * max_seg + myseg) * (WARPS * 32) + tid;
+                *mine = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                __threadfence();
+                __syncthreads();
+                if (tid == 0) s_arrived = atomicAdd(&counters[rb], 1);
+                __syncthreads();
+                finish = s_arrived == nseg - 1;
+                if (finish) {
+                    __threadfence();
+                    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                    const float4* all = reinterpret_cast<const float4*>(scratch) + (size_t)rb * max_seg * (WARPS * 32) + tid;
+                    for (int s = 0; s < nseg; ++s) {            // in the order of the k ranges, whoever came last
+                        const float4 v = __ldcg(all + (size_t)s * (WARPS * 32));
+                        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+                    }
+                    if (tid == 0) counters[rb] = 0;             // ready for the next launch
+                }
+                __syncthreads();                                // s_arrived is free again
+            }
+            if (finish) {
+                // acc[0], acc[1]: gate sums of output o for tokens 2c, 2c + 1; acc[2], acc[3]: the up sums
+                const int o = rb * OUTS + warp * 8 + g;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int tok = 2 * c + e;
+                    const float gate = acc[e], up = acc[2 + e];
+                    if (o < I && tok < M) out[(size_t)tok * I + o] = __float2bfloat16_rn(gate / (1.f + __expf(-gate)) * up);
+                }
+            }
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        }
+        if (++kb == kblocks) {
+            kb = 0;
+            ++rb;
+        }
+    }
+}
+
+struct SwigluPlan {
+    int grid, row_blocks, max_seg, x_slots;
+    bool xsmem;
+    size_t smem, scratch_floats;
+};
+
+// One block of 16 warps a SM, five tiles of 16 rows x 64 k in each warp's ring (160 KB, 128 KB of it in flight).
+// Measured on a B200, 8 x 24576 x 4096: 38.0 us; eight warps and two blocks a SM 41.3; deeper rings (up to 192 KB in
+// flight, x read from global memory to make room) 40.0 to 41.7; tiles of 128 and 256 k 40.5 to 40.7.
+constexpr int SWIGLU_WARPS = 16, SWIGLU_STAGES = 5, SWIGLU_KT = 64;
+
+// The grid and the scratch for a shape, or grid 0 when the kernel does not take it.  x of a block's stretch is
+// staged in shared memory beside the rings when it fits (the faster form), else the lanes read it from global memory.
+static SwigluPlan swiglu_plan(int M, int I, int K, int run) {
+    SwigluPlan p = {};
+    if (M < 1 || M > 8 || K < SWIGLU_KT || K % SWIGLU_KT != 0 || I < 8 || run < 8 || run % 8 != 0 || I % run != 0) return p;
+    static const bool x_global = [] {
+        const char* v = getenv("LILY_B200_SWIGLU_X");          // "global": never stage x in shared memory (for tests)
+        return v && v[0] == 'g';
+    }();
+    const int outs = 8 * SWIGLU_WARPS, kblocks = K / SWIGLU_KT;
+    p.row_blocks = (I + outs - 1) / outs;
+    const long long units = (long long)p.row_blocks * kblocks;
+    long long grid = sm_count();
+    if (grid > units) grid = units;
+    p.grid = (int)grid;
+    const long long longest = (units + grid - 1) / grid, shortest = units / grid;
+    const size_t rings = (size_t)SWIGLU_WARPS * SWIGLU_STAGES * 16 * SWIGLU_KT * 2;
+    p.x_slots = (int)(longest <= kblocks ? longest : kblocks);
+    p.xsmem = !x_global && rings + (size_t)8 * p.x_slots * 128 <= (size_t)226 * 1024;
+    if (!p.xsmem) p.x_slots = 0;
+    p.max_seg = (int)(kblocks / (shortest > 0 ? shortest : 1) + 2);
+    p.smem = rings + (size_t)8 * p.x_slots * 128;
+    p.scratch_floats = (size_t)p.row_blocks * p.max_seg * SWIGLU_WARPS * 32 * 4;
+    return p;
+}
+
+template <bool XSMEM>
+static int launch_swiglu(const SwigluPlan& p, const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* out,
+                         float* scratch, int* counters, int M, int I, int K, int run, cudaStream_t stream) {
+    auto kern = skinny_swiglu_kernel<SWIGLU_WARPS, SWIGLU_STAGES, XSMEM, SWIGLU_KT>;
+    static size_t granted = 48 * 1024;
+    if (p.smem > granted) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+        if (e != cudaSuccess) {
+            set_error("skinny_swiglu: cannot get %zu bytes of shared memory: %s", p.smem, cudaGetErrorString(e));
+            return 2;
+        }
+        granted = p.smem;
+    }
+    launch_pdl(kern, dim3(p.grid), dim3(SWIGLU_WARPS * 32), p.smem, stream, x, w, out, scratch, counters, M, I, K, run,
+               p.row_blocks, p.max_seg, p.x_slots);
+    return 0;
+}
+
 }  // namespace skinny
 }  // namespace lily
 
@@ -227,5 +469,35 @@ LILY_API int lily_skinny_gemm(const void* x, const void* w, float* parts, int M,
     else rc = skinny::launch<8, 2, 4, 5, 64>(xp, wp, parts, M, N, K, ksplit, stream);
     if (rc) return rc;
     LILY_CHECK_LAUNCH("skinny_gemm");
+    return 0;
+}
+
+// Whether the fused gate/up product takes this shape, and what it needs: `scratch_floats` float32 of scratch and
+// `counters` int32 that are zero before the first launch (the kernel leaves them zero).
+LILY_API int lily_skinny_swiglu_need(int M, int I, int K, int run, size_t* scratch_floats, int* counters) {
+    const skinny::SwigluPlan p = skinny::swiglu_plan(M, I, K, run);
+    if (p.grid == 0) return 0;
+    if (scratch_floats) *scratch_floats = p.scratch_floats;
+    if (counters) *counters = p.row_blocks;
+    return 1;
+}
+
+// out [M, I] bfloat16 = silu(x . gate^T) * (x . up^T); w [2 I, K] holds runs of `run` gate rows and the `run` up
+// rows of the same outputs (run == I: all gate rows, then all up rows).
+LILY_API int lily_skinny_swiglu(const void* x, const void* w, void* out, float* scratch, int* counters, int M, int I,
+                                int K, int run, cudaStream_t stream) {
+    if (M == 0 || I == 0) return 0;
+    const skinny::SwigluPlan p = skinny::swiglu_plan(M, I, K, run);
+    LILY_REQUIRE(p.grid > 0, "skinny_swiglu: does not take M=%d I=%d K=%d run=%d (1 to 8 tokens, K a multiple of 64, "
+                 "I a multiple of run, run a multiple of 8)", M, I, K, run);
+    LILY_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && scratch != nullptr && counters != nullptr,
+                 "skinny_swiglu: operands must be 16-byte aligned and scratch and counters given");
+    const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+    const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
+    __nv_bfloat16* op = (__nv_bfloat16*)out;
+    const int rc = p.xsmem ? skinny::launch_swiglu<true>(p, xp, wp, op, scratch, counters, M, I, K, run, stream)
+                           : skinny::launch_swiglu<false>(p, xp, wp, op, scratch, counters, M, I, K, run, stream);
+    if (rc) return rc;
+    LILY_CHECK_LAUNCH("skinny_swiglu");
     return 0;
 }

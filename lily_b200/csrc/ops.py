@@ -32,6 +32,7 @@ _SIGNATURES = {
     "lily_qk_norm_rope_write": [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                 _i, _i, _i, _i, _i, _sz, _vp],
     "lily_skinny_gemm": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "lily_skinny_swiglu": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "lily_cast": [_vp, _i, _vp, _i, _sz, _vp],
     "lily_gemm_fp32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
@@ -70,6 +71,8 @@ def library():
         lib.lily_skinny_gemm_max_rows.restype = _i
         lib.lily_skinny_gemm_splits.argtypes = [_i, _i, _i]
         lib.lily_skinny_gemm_splits.restype = _i
+        lib.lily_skinny_swiglu_need.argtypes = [_i, _i, _i, _i, ctypes.POINTER(_sz), ctypes.POINTER(_i)]
+        lib.lily_skinny_swiglu_need.restype = _i
         lib.lily_attention_prefill_mma_rows.restype = _i
         lib.lily_attention_prefill_tc_rows.restype = _i
         lib.lily_attention_prefill_tc_takes.argtypes = [_i, _i]
@@ -356,6 +359,44 @@ def linear_auto(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
         if parts is not None:
             return parts
     return linear(x, weight, bias)
+
+
+def swiglu_skinny_need(tokens: int, intermediate: int, hidden: int, dtype: torch.dtype,
+                       block: Optional[int] = None) -> Optional[Tuple[int, int]]:
+    """(float32 of scratch, int32 counters) that ``swiglu_skinny`` wants for this shape, or None when it does not
+    take it (more than 8 tokens, not bfloat16, K not a multiple of 64): the caller then forms the product and
+    SiLU*mul separately.  ``LILY_B200_SWIGLU=library`` always answers None."""
+    if dtype != torch.bfloat16 or _LIBRARY_SWIGLU:
+        return None
+    floats, counters = _sz(0), _i(0)
+    if not library().lily_skinny_swiglu_need(int(tokens), int(intermediate), int(hidden), int(block or intermediate),
+                                             ctypes.byref(floats), ctypes.byref(counters)):
+        return None
+    return int(floats.value), int(counters.value)
+
+
+_LIBRARY_SWIGLU = os.environ.get("LILY_B200_SWIGLU", "") == "library"
+
+
+def swiglu_skinny(x: torch.Tensor, gate_up: torch.Tensor, block: Optional[int], scratch: torch.Tensor,
+                  counters: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(x . gate^T) * (x . up^T)`` [tokens, I] for up to 8 tokens in one kernel that streams the fused
+    gate/up matrix [2 I, K] once (rows in alternating runs of ``block`` gate and up rows; None: all gate, then all
+    up).  ``scratch`` (float32) and ``counters`` (int32, zero before the first call; the kernel leaves them zero)
+    are sized by ``swiglu_skinny_need``."""
+    _dev(x, gate_up, scratch, counters, out)
+    m, k = x.shape
+    inter = gate_up.shape[0] // 2
+    need = swiglu_skinny_need(m, inter, k, x.dtype, block)
+    if need is None or gate_up.dtype != torch.bfloat16 or gate_up.shape[1] != k:
+        raise KernelError(f"swiglu_skinny: x {tuple(x.shape)} {x.dtype} against {tuple(gate_up.shape)} {gate_up.dtype}")
+    if scratch.dtype != torch.float32 or scratch.numel() < need[0] or counters.dtype != torch.int32 or counters.numel() < need[1]:
+        raise KernelError(f"swiglu_skinny: {need[0]} float32 of scratch and {need[1]} int32 counters needed")
+    if out is None:
+        out = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
+    _call("lily_skinny_swiglu", _p(x), _p(gate_up), _p(out), _p(scratch), _p(counters), m, inter, k, int(block or inter),
+          _stream())
+    return out
 
 
 def logits(x: torch.Tensor, head: torch.Tensor) -> torch.Tensor:

@@ -61,6 +61,16 @@ class Workspace:
             self._buffers[name] = buf
         return buf
 
+    def counters(self, name: str, count: int) -> torch.Tensor:
+        """int32 counters that are zero when first handed out; kernels that use them leave them zero."""
+        buf = self._buffers.get("int:" + name)
+        if buf is None or buf.numel() < count:
+            if torch.device(self.device).type == "cuda" and torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(f"workspace {name!r} must be sized before a graph is captured")
+            buf = torch.zeros((max(count, 1),), dtype=torch.int32, device=self.device)
+            self._buffers["int:" + name] = buf
+        return buf
+
 
 @dataclass
 class StepBatch:

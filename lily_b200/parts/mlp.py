@@ -5,7 +5,9 @@ gate and up are one matrix ``[2 * inter, hidden]`` so that one product feeds the
 is a multiple of 128, the rows alternate between 128 gate rows and the 128 up rows of the same
 outputs: a 256-row tile of the product then holds both halves of 128 outputs, and for more than a
 few tokens the tcgen05 kernel applies SiLU*mul in its epilogue, so the ``[tokens, 2 * inter]``
-intermediate never reaches memory.  Otherwise gate rows come first, then up rows.
+intermediate never reaches memory.  Otherwise gate rows come first, then up rows.  For up to 8
+tokens (decode) one weight-streaming kernel forms both sums and SiLU*mul from either layout; the
+reference streams these products through its own kernel as well (lily/csrc/bf16_skinny.cu:45-96).
 """
 
 from __future__ import annotations
@@ -58,10 +60,13 @@ class SwiGLU(FeedForward):
     def forward(self, x, batch):
         ops = self.ctx.ops
         product = ops.linear_auto                                # partial sums for a few tokens, else [M, N]
-        if self.block and x.shape[0] >= ops.TC_MIN_ROWS and ops.gemm_tc_takes(x, self.w_gate_up):
+        few = ops.swiglu_skinny_need(x.shape[0], self.spec.intermediate_size, self.spec.hidden_size, x.dtype, self.block)
+        if few is not None and batch.workspace is not None:
+            # a few tokens: one kernel streams the fused matrix and applies SiLU*mul to its own sums
+            act = ops.swiglu_skinny(x, self.w_gate_up, self.block, batch.workspace.floats("swiglu", few[0]),
+                                    batch.workspace.counters("swiglu", few[1]))
+        elif self.block and x.shape[0] >= ops.TC_MIN_ROWS and ops.gemm_tc_takes(x, self.w_gate_up):
             act = ops.gemm_tc(x, self.w_gate_up, silu_mul_block=True)
-        elif self.block:
-            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, block=self.block)
         else:
-            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype)
+            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, block=self.block)
         return product(act, self.w_down)

@@ -1,6 +1,8 @@
 """Each CUDA kernel alone against its plain PyTorch statement (tests/kernel_refs.py), at sizes
 other than the engine's: odd widths, head sizes in steps of 16, any grouping, windows, page edges."""
 
+import os
+
 import pytest
 import torch
 
@@ -133,6 +135,46 @@ def test_skinny_gemm_partial_sums(m, n, k):
     assert ops().linear_split(torch.zeros(65, k, device=DEV).bfloat16(), w) is None
     assert ops().linear_split(torch.zeros(2, 72, device=DEV).bfloat16(), torch.zeros(8, 72, device=DEV).bfloat16()) is None
     assert ops().linear_split(x.float(), w.float()) is None
+
+
+@pytest.mark.parametrize("x_from", ["shared memory when it fits", "global memory"])
+@pytest.mark.parametrize("m,inter,k,run", [(8, 12288, 4096, 128), (1, 12288, 4096, 128), (5, 1408, 512, 128), (8, 200, 64, None),
+                                           (3, 264, 1088, 8), (7, 25600, 5120, 128), (8, 352, 128, None), (2, 128, 12288, 64)])
+def test_skinny_swiglu(m, inter, k, run, x_from):
+    """The gate/up product with SiLU*mul in one weight-streaming kernel against the plain statement: tall and low
+    matrices (row blocks finished by one block or by several, whose stretches end anywhere), deep k (more units a
+    block than a row block has), both layouts of the fused matrix, 1 to 8 tokens, x staged in shared memory or read
+    from global memory; twice over the same scratch, and a token's result does not depend on its neighbours."""
+    import subprocess, sys
+    if x_from == "global memory":
+        # the kernel's other form is chosen by an environment variable read once: ask a fresh process
+        code = (f"import torch, sys; sys.path.insert(0, {os.path.dirname(os.path.abspath(__file__))!r}); "
+                f"import test_kernels_gpu as t; t.test_skinny_swiglu({m}, {inter}, {k}, {run}, 'as the environment says')")
+        done = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, LILY_B200_SWIGLU_X="global"),
+                              capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+        return
+    o = ops()
+    g = torch.Generator(device=DEV).manual_seed(12)
+    x = torch.randn(m, k, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(2 * inter, k, device=DEV, generator=g) * k ** -0.5).bfloat16()
+    need = o.swiglu_skinny_need(m, inter, k, torch.bfloat16, run)
+    assert need is not None
+    scratch = torch.full((need[0],), float("nan"), device=DEV)
+    counters = torch.zeros(need[1], device=DEV, dtype=torch.int32)
+    got = o.swiglu_skinny(x, w, run, scratch, counters)
+    gu = x.double() @ w.double().t()
+    want = ref.silu_mul(gu.float(), torch.float32, block=run)
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+    assert float((got.float() - want).abs().mean()) < 2e-3
+    assert int(counters.abs().sum()) == 0
+    again = o.swiglu_skinny(x, w, run, scratch, counters)
+    assert torch.equal(again, got) and int(counters.abs().sum()) == 0
+    alone = o.swiglu_skinny(x[:1].contiguous(), w, run, scratch, counters)
+    assert torch.equal(alone[0], got[0])
+    assert o.swiglu_skinny_need(9, inter, k, torch.bfloat16, run) is None
+    assert o.swiglu_skinny_need(m, inter, k, torch.float32, run) is None
+    assert o.swiglu_skinny_need(m, inter, k + 8, torch.bfloat16, run) is None
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 6144, 4096), (300, 1000, 136), (65, 331, 200), (1, 24, 8),

@@ -137,7 +137,9 @@ def test_swiglu_part(dtype, hidden, inter, tokens):
     part = build_part("feed_forward", SwiGLUSpec(hidden, inter), "m", ctx(dtype))
     part.load(loader(w, dtype))
     x = rnd(g, tokens, hidden).to(dtype)
-    out = part.forward(x.to(DEV), None)
+    from types import SimpleNamespace
+    step = SimpleNamespace(workspace=Workspace(DEV))              # what the part asks of a step: scratch for its kernels
+    out = part.forward(x.to(DEV), step)
     if out.dim() == 3:
         out = out.sum(0)
     torch.testing.assert_close(out.float().cpu(), plain_impl.swiglu_part(x.float(), w, "m"), **tol(dtype))
