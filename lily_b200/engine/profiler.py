@@ -3,8 +3,14 @@
 ``LILY_B200_PROFILE_BS=1,8`` arms the step function: the first all-decode step with that many
 requests opens a window over the next ``LILY_B200_PROFILE_STEPS`` (default 20) such steps, and
 when it closes a table goes to the log and, with ``LILY_B200_PROFILE_OUT=<folder>``, to
-``<folder>/decode_step_bs<N>.txt``: each kernel's device time per step, its share and its launches
-per step, summed over every launch of the window (kernels inside replayed CUDA graphs included).
+``<folder>/decode_step_bs<N>.txt``: for each kernel its launches per step and two times per step,
+summed over every launch of the window (kernels inside replayed CUDA graphs included).  ``own`` is
+the time from the end of whatever ran before it (or its own start, if later) to its own end: the
+kernels of a step are launched so that one may start while its predecessor drains (programmatic
+dependent launch), and a kernel that waits inside for its predecessor would otherwise be charged
+for that wait; the ``own`` column adds up to the time the device was busy.  ``resident`` is the
+plain start-to-end duration.  (The window opens at the second step of its batch size: the first
+may capture a CUDA graph.)
 The reference has the same switch for its server (lily/profiler.py:20-66, hooked at
 lily/scheduler/scheduler.py:455-456).
 
@@ -33,6 +39,7 @@ class DecodeProfiler:
         self.tables: Dict[int, str] = {}
         self._prof = None
         self._bs = self._n = 0
+        self._seen = set()
 
     @classmethod
     def from_env(cls) -> Optional["DecodeProfiler"]:
@@ -46,6 +53,9 @@ class DecodeProfiler:
         """Called by the step function before every step; ``decode_requests`` is the batch size of an
         all-decode step and None for any other."""
         if self._prof is None:
+            if decode_requests in self.pending and decode_requests not in self._seen:
+                self._seen.add(decode_requests)         # this step may capture its graph: the next one opens the window
+                return
             if decode_requests in self.pending:
                 from torch.profiler import ProfilerActivity, profile
                 self.pending.discard(decode_requests)
@@ -71,24 +81,34 @@ class DecodeProfiler:
                 f.write(table + "\n")
         self._prof = None
 
-    def _kernel_times(self) -> List[Tuple[float, int, str]]:
-        """(microseconds, launches, name) per kernel over the window."""
-        total: Dict[str, float] = defaultdict(float)
-        count: Dict[str, int] = defaultdict(int)
+    def _kernel_times(self) -> List[Tuple[float, float, int, str]]:
+        """(own microseconds, resident microseconds, launches, name) per kernel over the window."""
+        spans = []
         for ev in self._prof.events():
             if ev.device_type.name == "CPU":
                 continue
-            us = float(getattr(ev, "device_time_total", 0.0) or getattr(ev, "cuda_time_total", 0.0))
-            if us > 0:
-                total[ev.name] += us
-                count[ev.name] += 1
-        return sorted(((t, count[n], n) for n, t in total.items()), reverse=True)
+            start, end = float(ev.time_range.start), float(ev.time_range.end)
+            if end > start:
+                spans.append((start, end, ev.name))
+        spans.sort()
+        own: Dict[str, float] = defaultdict(float)
+        resident: Dict[str, float] = defaultdict(float)
+        count: Dict[str, int] = defaultdict(int)
+        busy_until = 0.0
+        for start, end, name in spans:
+            own[name] += max(0.0, end - max(start, busy_until))
+            resident[name] += end - start
+            count[name] += 1
+            busy_until = max(busy_until, end)
+        return sorted(((own[n], resident[n], count[n], n) for n in own), reverse=True)
 
     @staticmethod
-    def table(items: List[Tuple[float, int, str]], steps: int, batch: int, rows: int = 40) -> str:
-        whole = sum(t for t, _, _ in items) or 1.0
+    def table(items: List[Tuple[float, float, int, str]], steps: int, batch: int, rows: int = 40) -> str:
+        whole = sum(t for t, _, _, _ in items) or 1.0
         lines = [f"decode step at batch {batch}: device time per step over {steps} steps",
-                 f"{'us/step':>9} {'%':>5} {'launches':>8}  kernel",
-                 f"{whole / steps:9.1f} {100.0:5.1f} {sum(c for _, c, _ in items) / steps:8.1f}  all kernels"]
-        lines += [f"{t / steps:9.1f} {100 * t / whole:5.1f} {c / steps:8.1f}  {name[:110]}" for t, c, name in items[:rows]]
+                 f"{'own us':>9} {'%':>5} {'resident':>9} {'launches':>8}  kernel",
+                 f"{whole / steps:9.1f} {100.0:5.1f} {sum(r for _, r, _, _ in items) / steps:9.1f} "
+                 f"{sum(c for _, _, c, _ in items) / steps:8.1f}  all kernels"]
+        lines += [f"{t / steps:9.1f} {100 * t / whole:5.1f} {r / steps:9.1f} {c / steps:8.1f}  {name[:100]}"
+                  for t, r, c, name in items[:rows]]
         return "\n".join(lines)
