@@ -3,12 +3,15 @@ tokens a second at 2,048 tokens, for the Qwen3-8B layer sizes with random weight
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
 
-Prints one JSON line.  A step is one decode step of the whole batch.  ``value`` times K steps of
-the engine's step function plus the sampler on the device (CUDA events, W untimed steps first);
-``e2e`` times the same number of tokens through ``Engine.generate`` (scheduler, host token lists in,
-host token lists out).  The method is the reference's own (bench/bench.py:104-172 there: random
-ids, a batched prefill, warm-up and timed decode steps).  The weights (15 GB) are larger than the
-126 MB L2, so nothing is flushed between steps.
+Prints one JSON line.  A step is one decode step of the whole batch.  After W untimed steps, ``value``
+times K steps of the engine's step function plus the argmax kernel on the device (CUDA events) and
+``e2e`` times K steps of the scheduler behind ``Engine`` on the host (token lists in, token lists out,
+the overlap schedule as in serving), in alternating rounds (medians are reported) under one record of
+the SM clocks, sampled through NVML every 10 ms and tagged by region; ``e2e.host_ms_per_step`` is what
+the host itself spends on a step.  ``--impl reference`` measures the unmodified reference the same way
+(``baseline/reference_arm.py``).  The method is the reference's own (bench/bench.py:104-172 there:
+random ids, a batched prefill, warm-up and timed decode steps).  The weights (15 GB) are larger than
+the 126 MB L2, so nothing is flushed between steps.
 """
 
 from __future__ import annotations
