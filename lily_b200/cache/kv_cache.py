@@ -124,6 +124,10 @@ class KVCacheManager:
     def block_table(self, group: int, slot: int) -> List[int]:
         return self.groups[group].tables.tables[slot].pages
 
+    def table_stamp(self, group: int, slot: int) -> int:
+        """A number that changes whenever the request's block table in this group does (and that no other table has)."""
+        return self.groups[group].tables.tables[slot].stamp
+
     def free_pages(self) -> int:
         return min((g.tables.pool.available for g in self.groups), default=self.num_pages)
 

@@ -16,6 +16,8 @@ with the device tensors.
 
 from __future__ import annotations
 
+import itertools
+
 from typing import Dict, List, Optional
 
 
@@ -86,11 +88,16 @@ class BlockTable:
     """Pages of one request in one group.  ``pages[i]`` holds positions
     ``[i * page_size, (i + 1) * page_size)``; 0 after the window has passed them."""
 
-    __slots__ = ("pages", "first_live")
+    __slots__ = ("pages", "first_live", "stamp")
+    _stamps = itertools.count(1)
 
     def __init__(self):
         self.pages: List[int] = []
         self.first_live = 0          # index of the first page not yet given back
+        self.stamp = next(BlockTable._stamps)      # a new number whenever the table changes; no two tables share one
+
+    def touch(self) -> None:
+        self.stamp = next(BlockTable._stamps)
 
     def live_pages(self) -> List[int]:
         return [p for p in self.pages[self.first_live:] if p]
@@ -123,6 +130,7 @@ class GroupTables:
         need = pages_for(new_len, self.page_size) - len(t.pages)
         if need > 0:
             t.pages.extend(self.pool.alloc(need))
+            t.touch()
 
     def pass_window(self, slot: int, seq_len: int) -> int:
         """Gives back the pages no later query can see: with ``seq_len`` positions cached, the
@@ -135,6 +143,8 @@ class GroupTables:
         gone = [p for p in t.pages[t.first_live:first_needed] if p]
         for i in range(t.first_live, first_needed):
             t.pages[i] = 0
+        if first_needed > t.first_live:
+            t.touch()
         t.first_live = max(t.first_live, first_needed)
         self.pool.free(gone)
         return len(gone)

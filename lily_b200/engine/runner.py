@@ -84,7 +84,19 @@ class _DecodeGraph:
             max_decode_len=runner.context_len,          # the mixers plan for the longest sequence a replay may bring
             workspace=Workspace(runner.device),         # scratch of its own: the graph holds its address
             future_tokens=runner.future_tokens)
-        self.fill([], [], [[] for _ in self.widths], [])
+        # views of the pinned copy, field by field; what never changes is written once, here
+        self._np = self.host.numpy()
+        offsets = [0]
+        for n in self.sizes:
+            offsets.append(offsets[-1] + n)
+        field = lambda i: self._np[offsets[i]:offsets[i + 1]]
+        self._tokens, self._positions, self._prefix, self._seq, self._slots = field(0), field(1), field(4), field(5), field(6)
+        field(2)[:] = range(b)                                # token_req
+        field(3)[:] = range(b + 1)                            # cu_seqlens
+        field(7)[:] = range(b)                                # logit rows
+        self._tables = [field(8 + i).reshape(b, w) for i, w in enumerate(self.widths)]
+        self._rows: List[List[int]] = [[0] * b for _ in self.widths]       # the stamp of the table each row holds
+        self.fill([], [], [[] for _ in self.widths], [], [[] for _ in self.widths])
         self.static.copy_(self.host)
         stream = torch.cuda.Stream(device=runner.device)
         stream.wait_stream(torch.cuda.current_stream())
@@ -101,28 +113,34 @@ class _DecodeGraph:
         self.kernels = counter["count"] - before        # this package's kernels in one replay
         self._counter = counter
 
-    def fill(self, tokens: Sequence[int], prefix: Sequence[int], tables, slots: Sequence[int]) -> None:
-        """Writes a decode batch (padded to the bucket) into the pinned host copy."""
-        b, n = self.bucket, len(tokens)
-        pad = b - n
-        flat: List[int] = list(tokens) + [0] * pad
-        flat += list(prefix) + [0] * pad                      # positions
-        flat += list(range(b))                                # token_req
-        flat += list(range(b + 1))                            # cu_seqlens
-        flat += list(prefix) + [0] * pad                      # prefix_lens
-        flat += [p + 1 for p in prefix] + [1] * pad           # seq_lens
-        flat += list(slots) + [0] * pad                       # slots: read when sampled tokens are stored by slot
-        flat += list(range(b))                                # logit rows
-        for g, w in zip(tables, self.widths):
-            for t in g:
-                flat += list(t) + [0] * (w - len(t))
-            flat += [0] * (w * pad)
+    def fill(self, tokens: Sequence[int], prefix: Sequence[int], tables, slots: Sequence[int], stamps) -> None:
+        """Writes a decode batch (padded to the bucket) into the pinned host copy.  The short fields are written
+        whole; of the block tables only the rows that changed since the last step (``stamps[g][r]`` is the cache
+        manager's stamp of the table in row r: a request gains a page once every ``page_size`` steps)."""
+        n = len(tokens)
         if self.copied is not None:
-            self.copied.synchronize()
-        self.host.copy_(torch.tensor(flat, dtype=torch.int32))
+            self.copied.synchronize()                       # the copy that read the host buffer last has finished
+        self._tokens[:n] = tokens
+        self._tokens[n:] = 0
+        self._positions[:n] = prefix
+        self._positions[n:] = 0
+        self._prefix[:] = self._positions
+        self._seq[:] = self._positions
+        self._seq += 1
+        self._slots[:n] = slots
+        self._slots[n:] = 0
+        for view, held, group, stamp in zip(self._tables, self._rows, tables, stamps):
+            for r in range(self.bucket):
+                now = stamp[r] if r < n else 0
+                if held[r] == now:
+                    continue
+                pages = group[r] if r < n else ()
+                view[r, :len(pages)] = pages
+                view[r, len(pages):] = 0
+                held[r] = now
 
-    def run(self, tokens, prefix, tables, slots) -> torch.Tensor:
-        self.fill(tokens, prefix, tables, slots)
+    def run(self, tokens, prefix, tables, slots, stamps) -> torch.Tensor:
+        self.fill(tokens, prefix, tables, slots, stamps)
         self.static.copy_(self.host, non_blocking=True)
         self.copied = torch.cuda.Event()
         self.copied.record()
@@ -317,11 +335,13 @@ class ModelRunner:
         graph = self._graphs.get(bucket)
         if graph is None:
             graph = self._graphs[bucket] = _DecodeGraph(self, bucket)
-        tables = [[self.cache.block_table(g, e.slot) for e in entries] for g in range(len(self.cache.groups))]
+        groups = range(len(self.cache.groups))
+        tables = [[self.cache.block_table(g, e.slot) for e in entries] for g in groups]
+        stamps = [[self.cache.table_stamp(g, e.slot) for e in entries] for g in groups]
         self.graph_steps += 1
         self._last_rows = (graph.batch.logit_rows, graph.batch.token_req, graph.batch.slots)
         return graph.run([e.wire_tokens[0] for e in entries], [self.seq_lens[e.slot] for e in entries], tables,
-                         [e.slot for e in entries])
+                         [e.slot for e in entries], stamps)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one step and returns float32 logits ``[sum(len(e.want)), vocab]`` on the device.

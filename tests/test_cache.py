@@ -109,3 +109,29 @@ def test_random_orders_never_lose_or_share_a_page(seed, window):
     for s in list(live):
         m.close_request(s)
     assert m.held_pages() == [0] and m.slots.available == 5
+
+
+def test_table_stamps_change_with_the_table_and_are_never_shared():
+    """What the decode graphs rely on to rewrite only the block-table rows that changed: a stamp that moves when a
+    page is taken or given back, stays while nothing changes, and differs between two requests that had the same
+    slot one after the other."""
+    cache = KVCacheManager([(CacheNeed(2, 16, None), 1), (CacheNeed(2, 16, 24), 1)], [], page_size=8, num_pages=12,
+                           max_requests=2, max_context=96, device=None)
+    a = cache.open_request()
+    first = [cache.table_stamp(g, a) for g in (0, 1)]
+    cache.grow(a, 5)
+    one_page = [cache.table_stamp(g, a) for g in (0, 1)]
+    assert all(x != y for x, y in zip(first, one_page))
+    cache.grow(a, 8)                                       # still the same page
+    cache.advance(a, 8)
+    assert [cache.table_stamp(g, a) for g in (0, 1)] == one_page
+    cache.grow(a, 40)
+    grown = [cache.table_stamp(g, a) for g in (0, 1)]
+    cache.advance(a, 40)                                   # the window of 24 has passed the first two pages
+    assert cache.table_stamp(0, a) == grown[0] and cache.table_stamp(1, a) != grown[1]
+    seen = set(first + one_page + grown + [cache.table_stamp(1, a)])
+    cache.close_request(a)
+    b = cache.open_request()
+    assert b == a
+    cache.grow(b, 40)
+    assert not {cache.table_stamp(0, b), cache.table_stamp(1, b)} & seen

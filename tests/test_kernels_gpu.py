@@ -137,23 +137,27 @@ def test_skinny_gemm_partial_sums(m, n, k):
     assert ops().linear_split(x.float(), w.float()) is None
 
 
-@pytest.mark.parametrize("x_from", ["shared memory when it fits", "global memory"])
-@pytest.mark.parametrize("m,inter,k,run", [(8, 12288, 4096, 128), (1, 12288, 4096, 128), (5, 1408, 512, 128), (8, 200, 64, None),
-                                           (3, 264, 1088, 8), (7, 25600, 5120, 128), (8, 352, 128, None), (2, 128, 12288, 64)])
-def test_skinny_swiglu(m, inter, k, run, x_from):
+SWIGLU_SHAPES = [(8, 12288, 4096, 128), (1, 12288, 4096, 128), (5, 1408, 512, 128), (8, 200, 64, None),
+                 (3, 264, 1088, 8), (7, 25600, 5120, 128), (8, 352, 128, None), (2, 128, 12288, 64)]
+
+
+def test_skinny_swiglu_with_x_from_global_memory():
+    """The kernel's other form (the lanes read x from global memory; taken when x of a block's stretch does not fit
+    beside the rings) on every shape: the form is chosen by an environment variable read once, so a fresh process."""
+    import subprocess, sys
+    code = (f"import sys; sys.path.insert(0, {os.path.dirname(os.path.abspath(__file__))!r}); import test_kernels_gpu as t\n"
+            "for shape in t.SWIGLU_SHAPES: t.test_skinny_swiglu(*shape)")
+    done = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, LILY_B200_SWIGLU_X="global"),
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+
+
+@pytest.mark.parametrize("m,inter,k,run", SWIGLU_SHAPES)
+def test_skinny_swiglu(m, inter, k, run):
     """The gate/up product with SiLU*mul in one weight-streaming kernel against the plain statement: tall and low
     matrices (row blocks finished by one block or by several, whose stretches end anywhere), deep k (more units a
-    block than a row block has), both layouts of the fused matrix, 1 to 8 tokens, x staged in shared memory or read
-    from global memory; twice over the same scratch, and a token's result does not depend on its neighbours."""
-    import subprocess, sys
-    if x_from == "global memory":
-        # the kernel's other form is chosen by an environment variable read once: ask a fresh process
-        code = (f"import torch, sys; sys.path.insert(0, {os.path.dirname(os.path.abspath(__file__))!r}); "
-                f"import test_kernels_gpu as t; t.test_skinny_swiglu({m}, {inter}, {k}, {run}, 'as the environment says')")
-        done = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, LILY_B200_SWIGLU_X="global"),
-                              capture_output=True, text=True, timeout=600)
-        assert done.returncode == 0, done.stderr[-2000:]
-        return
+    block than a row block has), both layouts of the fused matrix, 1 to 8 tokens; twice over the same scratch, and a
+    token's result does not depend on its neighbours."""
     o = ops()
     g = torch.Generator(device=DEV).manual_seed(12)
     x = torch.randn(m, k, device=DEV, generator=g).bfloat16()
