@@ -246,7 +246,7 @@ def run(a, cfg: Dict, context: int, prefill_tokens: int, clock_sampler, rounds: 
     points = {}
     if not a.skip_points:
         for b in (1, 64):
-            pms, _, _, _ = decode_point(b, min(steps, 32), warmup, 1)
+            pms, _, _, _ = decode_point(b, min(steps, 32), warmup, 3)      # medians over three rounds, as the other arm
             points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
     graphs = eng.runner.cuda_graph_runner is not None
     return {"ms": ms, "e2e_ms": host_ms, "mean_ctx": mean_ctx, "clocks": clocks, "points": points,

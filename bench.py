@@ -312,11 +312,12 @@ def main() -> int:
             for s in self.slots:
                 runner.close_request(s)
 
-    def decode_point(batch, k, w):
-        raw = RawBatch(batch, k + w)
+    def decode_point(batch, k, w, rounds=3):
+        """Median over ``rounds`` of k device-timed steps each, after w untimed ones."""
+        raw = RawBatch(batch, w + rounds * k)
         for _ in range(w):
             raw.one()
-        ms = device_timed(raw.one, k)
+        ms = statistics.median(device_timed(raw.one, k) for _ in range(rounds))
         raw.close()
         return ms
 
