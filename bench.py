@@ -4,7 +4,8 @@ tokens a second at 2,048 tokens, for the Qwen3-8B layer sizes with random weight
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
 
 Prints one JSON line.  A step is one decode step of the whole batch.  After W untimed steps, ``value``
-times K steps of the engine's step function plus the argmax kernel on the device (CUDA events) and
+times K steps of the engine's step function plus the argmax kernel on the device (CUDA events; the tokens
+stay on the device from step to step) and
 ``e2e`` times K steps of the scheduler behind ``Engine`` on the host (token lists in, token lists out,
 the overlap schedule as in serving), in alternating rounds (medians are reported) under one record of
 the SM clocks, sampled through NVML every 10 ms and tagged by region; ``e2e.host_ms_per_step`` is what
@@ -295,20 +296,26 @@ def main() -> int:
 
     # ---- decode: batch B, contexts ending at 4,096 --------------------------------------
     class RawBatch:
-        """``batch`` requests driven by hand through the step function and the argmax kernel."""
+        """``batch`` requests driven by hand through the step function and the argmax kernel.  The sampled tokens
+        stay on the device (the step function's ``FUTURE`` entries: the embedding kernel looks each request's last
+        token up where the argmax left it), so the steps queue behind one another without the host reading
+        anything back: what is timed is the device's work for a step."""
 
         def __init__(self, batch, total_steps):
-            self.start_len = CONTEXT - total_steps - 1
+            from lily_b200.engine.batch import FUTURE
+            self.start_len = CONTEXT - total_steps - 2
             self.slots = [runner.open_request() for _ in range(batch)]
             for s in self.slots:                             # prompts go in whole, one request a step
                 runner.step([StepEntry(s, ids(self.start_len), [])])
-            self.tokens = [ids(1)[0] for _ in range(batch)]
+            logits = runner.step([StepEntry(s, [ids(1)[0]], [0]) for s in self.slots])
+            runner.store_future(ops.argmax(logits))
+            self.entries = [StepEntry(s, [FUTURE], [0]) for s in self.slots]
 
         def one(self):
-            logits = runner.step([StepEntry(s, [t], [0]) for s, t in zip(self.slots, self.tokens)])
-            self.tokens = ops.argmax(logits).tolist()
+            runner.store_future(ops.argmax(runner.step(self.entries)))
 
         def close(self):
+            torch.cuda.synchronize()
             for s in self.slots:
                 runner.close_request(s)
 
@@ -360,7 +367,7 @@ def main() -> int:
         clocks.region = "idle"
     ms, e2e_ms = statistics.median(dev_ms), statistics.median(host_ms)
     graph_steps = runner.graph_steps - graph_before
-    mean_ctx = raw.start_len + warmup + (rounds * steps + 1) / 2
+    mean_ctx = raw.start_len + 1 + warmup + (rounds * steps + 1) / 2
     # what the host itself spends on a step of the entry point: with the device idle before each call, a call
     # launches one step and reads the tokens of the step before, which are there already
     host_only = []
