@@ -24,6 +24,7 @@ from lily_b200.cache.kv_cache import KVCacheManager, OutOfPages, bytes_per_token
 from lily_b200.config.model_config import read_model_dir
 from lily_b200.config.registry import resolve_architecture
 from lily_b200.config.server_args import ServerArgs
+from lily_b200.engine import check
 from lily_b200.engine.batch import FUTURE, StepBatch, StepEntry, Workspace, build_step_batch, order_entries
 from lily_b200.engine.profiler import DecodeProfiler
 from lily_b200.models.assembled import AssembledModel
@@ -274,6 +275,8 @@ class ModelRunner:
                              f"{self.cache.free_pages()} pages free")
         for slot, new_len in wants:
             self.cache.grow(slot, new_len)
+        if check.ENABLED:
+            check.check_entries(self, entries)
         order = order_entries(entries)
         ordered = [entries[i] for i in order]
         prefix = [self.seq_lens[e.slot] for e in ordered]
@@ -296,6 +299,8 @@ class ModelRunner:
         if self._ring is not None:
             self._ring.mark(ring_index)
         batch.future_tokens = self.future_tokens
+        if check.ENABLED:
+            check.check_batch(self, batch)
         return batch
 
     def store_future(self, tokens: torch.Tensor) -> None:
@@ -332,6 +337,8 @@ class ModelRunner:
             raise OutOfPages(f"decode step of {len(entries)} tokens does not fit: {self.cache.free_pages()} pages free")
         for slot, new_len in wants:
             self.cache.grow(slot, new_len)
+        if check.ENABLED:
+            check.check_entries(self, entries)
         graph = self._graphs.get(bucket)
         if graph is None:
             graph = self._graphs[bucket] = _DecodeGraph(self, bucket)
@@ -340,6 +347,10 @@ class ModelRunner:
         stamps = [[self.cache.table_stamp(g, e.slot) for e in entries] for g in groups]
         self.graph_steps += 1
         self._last_rows = (graph.batch.logit_rows, graph.batch.token_req, graph.batch.slots)
+        if check.ENABLED:
+            graph.fill([e.wire_tokens[0] for e in entries], [self.seq_lens[e.slot] for e in entries], tables,
+                       [e.slot for e in entries], stamps)
+            check.check_graph_fill(self, graph, len(entries))
         return graph.run([e.wire_tokens[0] for e in entries], [self.seq_lens[e.slot] for e in entries], tables,
                          [e.slot for e in entries], stamps)
 

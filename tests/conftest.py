@@ -5,6 +5,9 @@ import sys
 
 import pytest
 
+# every step of every test has what it hands to the kernels verified first (lily_b200/engine/check.py)
+os.environ.setdefault("LILY_B200_CHECK_STEPS", "1")
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 for p in (ROOT, os.path.dirname(os.path.abspath(__file__))):
     if p not in sys.path:

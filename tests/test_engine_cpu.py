@@ -104,3 +104,32 @@ def test_bfloat16_layouts_on_the_host(setup):
     for got in (run_whole(runner, ids), run_portions(runner, ids, [70, 3] + [1] * 17)):
         err = (got - want).abs()
         assert float(err.max()) < 2e-2 * scale and float(err.mean()) < 3e-3 * scale
+
+
+def test_step_checks_catch_what_the_kernels_would_trust(setup):
+    """With LILY_B200_CHECK_STEPS on (the tests switch it on) a page id beyond the pool, a page held twice, a
+    request whose length the cache manager does not know of, and a stale row are refused before anything runs."""
+    from lily_b200.engine import check
+    from lily_b200.engine.batch import StepEntry
+    assert check.ENABLED
+    cfg, _, path = setup
+    v = cfg["vocab_size"]
+    runner = make_runner(path, page_size=16, max_tokens=160)
+    a, b = runner.open_request(), runner.open_request()
+    runner.step([StepEntry(a, tiny_models.random_tokens(20, v, 1), []), StepEntry(b, tiny_models.random_tokens(5, v, 2), [])])
+    pages_a = runner.cache.groups[0].tables.tables[a].pages
+    pages_b = runner.cache.groups[0].tables.tables[b].pages
+    kept = pages_a[0]
+    pages_a[0] = runner.cache.num_pages + 7
+    with pytest.raises(check.StepCheckError, match="page id"):
+        runner.step([StepEntry(a, [1], [0])])
+    pages_a[0] = pages_b[0]
+    with pytest.raises(check.StepCheckError, match="held by slots"):
+        runner.step([StepEntry(a, [1], [0])])
+    pages_a[0] = kept
+    runner.seq_lens[b] += 40                     # the step function believes in positions nobody cached
+    with pytest.raises(check.StepCheckError, match="cache manager holds pages"):
+        check.check_entries(runner, [StepEntry(b, [1], [0])])
+    runner.seq_lens[b] -= 40
+    out = runner.step([StepEntry(a, [1], [0]), StepEntry(b, [2, 3], [1])])
+    assert out.shape == (2, v)
