@@ -189,3 +189,21 @@ def test_the_step_profile_names_this_packages_kernels(monkeypatch):
     assert any("attention_mma_kernel" in ln for ln in lines) and any("add_rmsnorm" in ln for ln in lines)
     per_step = float(lines[2].split()[0])
     assert 10 < per_step < 5000                     # microseconds of device time a step
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generated_tokens_are_the_prefill_paths_argmax(dtype):
+    """What the decode path generated (graphs, split-key attention, the decode products) against one teacher-forced
+    pass of the prefill path over the same tokens (lily_b200/bench/check_greedy.py): in float32 every token is the
+    argmax up to rounding, in bfloat16 a token may differ only where the two best logits are nearly tied."""
+    from lily_b200 import SamplingParams
+    from lily_b200.bench.check_greedy import check_greedy
+    cfg = tiny_models.MID_QWEN3
+    with tempfile.TemporaryDirectory() as tmp:
+        path, _ = model_dir(cfg, 64, tmp)
+        eng = engine(path, dtype, max_total_tokens=4096)
+        prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], 300 + n) for n in (5, 130, 200, 64, 333)]
+        outs = [o["output_ids"] for o in eng.generate(prompts, SamplingParams(max_new_tokens=48, ignore_eos=True))]
+        report = check_greedy(eng, prompts, outs)
+    assert report["tokens"] == 5 * 48
+    assert report["max_gap"] < (1e-4 if dtype == "float32" else 3e-2), report
