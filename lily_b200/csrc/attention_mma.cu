@@ -40,8 +40,32 @@ constexpr int THREADS = 128;
 // steps whose blocks have a SM each (one request over 16 key ranges: 15.1 -> 13.1 us alone, the step unchanged at 3.39 ms).
 #define LILY_DECODE_STAGES 2
 #endif
+// Also measured and not kept: asking the lines of the next two or four tiles into L2 (prefetch.global.L2, a line a
+// thread) while the block prepares its queries: the step of 8 requests went from 3.92 to 4.04 ms, of one from 3.30 to 3.43;
+// and asking the weights of the product behind the attention into L2 (cp.async.bulk.prefetch.L2, each block its share)
+// once a block's keys and values are in: 3.92 to 3.97 ms and 3.30 to 3.35 ms.
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Built with -DLILY_DECODE_TIMING, thread 0 of the first and of the last split of (request 0, kv head 0) stamp the
+// SM's cycle counter as they pass each phase of the decode kernel (lily_attention_decode_timing reads the stamps).
+#ifdef LILY_DECODE_TIMING
+__device__ unsigned long long g_decode_stamps[2][16];
+__device__ unsigned long long g_decode_spans[4096][2];      // per block: the global timer (ns) at entry and at exit
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define DECODE_SPAN(which) do { const unsigned b__ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); \
+                                if (DECODE && threadIdx.x == 0 && b__ < 4096) g_decode_spans[b__][which] = global_ns(); } while (0)
+#define DECODE_STAMP(slot) do { if (DECODE && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && \
+                                    (blockIdx.z == 0 || blockIdx.z == gridDim.z - 1)) \
+                                    g_decode_stamps[blockIdx.z == 0 ? 0 : 1][slot] = (unsigned long long)clock64(); } while (0)
+#else
+#define DECODE_STAMP(slot) do {} while (0)
+#define DECODE_SPAN(which) do {} while (0)
+#endif
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
     const int n = valid ? 16 : 0;     // 0 source bytes: the 16 destination bytes are zero-filled
@@ -88,7 +112,7 @@ __host__ __device__ constexpr size_t stage_bytes(bool decode) {
     return decode && merge > stages ? merge : stages;
 }
 // Output sums a block of a cluster of `splits` blocks merges: its share of rows x D.
-__host__ __device__ inline int cluster_share(int rows, int d, int splits) { return (rows * d + splits - 1) / splits; }
+__host__ __device__ inline int cluster_share(int rows, int d, int splits) { return ((rows * d + splits - 1) / splits + 3) / 4 * 4; }
 
 template <int D, bool DECODE, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS, D <= 128 ? 3 : 1)
@@ -105,6 +129,8 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
     unsigned char* q_s = k_s + (STAGES - 1) * BN * D * 2;           // [BM][D], BM <= BN
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
+    DECODE_STAMP(0);
+    DECODE_SPAN(0);
     // Prefill waits here for the kernel before it (which wrote q and this step's keys).  Decode
     // waits further down: the block table, the lengths and every cached key but the one of this
     // step were there before that kernel began, so the first key tiles stream in while it runs.
@@ -183,8 +209,10 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
                 ++early;
             }
         }
+        DECODE_STAMP(1);
         pdl_wait();
         pdl_launch_dependents();
+        DECODE_STAMP(2);
     }
 
     // ---- queries to shared memory (zero rows beyond nrows), then to A fragments -------------
@@ -208,72 +236,85 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         const bool owner = a.write_kv && kbeg <= pos0 && pos0 < kend;
         const int jobs = nrows + (owner ? 2 : 0);                      // the query heads, then the key, then the value
         const bool whole = cs == nullptr || a.rd == D;                 // no rotation, or over the whole head
-        for (int job = warp; job < jobs; job += THREADS / 32) {
-            const bool is_q = job < nrows, is_v = job == nrows + 1;
-            const int head = is_q ? head0 + job : a.nq + (is_v ? a.nkv : 0) + kvh;
-            const size_t src = (size_t)tok0 * width + (size_t)head * D;
-            const void* gain = is_q ? a.q_gain : (is_v ? nullptr : a.k_gain);
-            __nv_bfloat16* cached = nullptr;
-            if (!is_q) {
-                const int page = table[pos0 >> page_shift];
-                cached = const_cast<__nv_bfloat16*>(kv_head) + (size_t)page * page_stride + (is_v ? (size_t)a.nkv * head_stride : 0) +
-                         (size_t)(pos0 & page_mask) * D;
+        constexpr int WARPS = THREADS / 32;
+        auto head_of = [&](int job) { return job < nrows ? head0 + job : a.nq + (job == nrows + 1 ? a.nkv : 0) + kvh; };
+        // where this step's key goes (the value lies nkv heads further)
+        __nv_bfloat16* own_key = owner ? const_cast<__nv_bfloat16*>(kv_head) + (size_t)table[pos0 >> page_shift] * page_stride +
+                                             (size_t)(pos0 & page_mask) * D : nullptr;
+        if (whole && warp < jobs) {
+            // A lane holds E neighbouring features; the feature half a head further is in lane ^ 16, same place.
+            // Everything a warp reads is asked for before the first sum: gains, angles, and the planes (up to eight
+            // each) of two heads at a time, so that the block with the key and the value (six heads over four
+            // warps where four query heads share a kv head) waits for memory once and not twice.
+            constexpr int E = D / 32;
+            const int e0 = lane * E, t0 = e0 - (lane >= 16 ? D / 2 : 0);
+            const size_t step = a.qkv_stride / 2;
+            float gain_q[E], gain_k[E], cos_r[E], sin_r[E];
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                gain_q[j] = gain_k[j] = 1.f;
+                if (a.q_gain) {
+                    gain_q[j] = a.gain_f32 ? ((const float*)a.q_gain)[e0 + j] : __bfloat162float(((const __nv_bfloat16*)a.q_gain)[e0 + j]);
+                    gain_k[j] = a.gain_f32 ? ((const float*)a.k_gain)[e0 + j] : __bfloat162float(((const __nv_bfloat16*)a.k_gain)[e0 + j]);
+                }
+                cos_r[j] = cs ? cs[t0 + j] : 1.f;
+                sin_r[j] = cs ? sn[t0 + j] : 0.f;
             }
-            auto gain_at = [&](int i) -> float {
-                return a.gain_f32 ? ((const float*)gain)[i] : __bfloat162float(((const __nv_bfloat16*)gain)[i]);
-            };
-            if (whole) {
-                // a lane holds E neighbouring features; the feature half a head further is in lane ^ 16, same place
-                constexpr int E = D / 32;
-                const int e0 = lane * E;
-                float x[E];
+            auto ask = [&](int job, float2 (&v)[8][E / 2]) {
+                const size_t src = (size_t)tok0 * width + (size_t)head_of(job) * D + e0;
                 if (a.qkv_f32) {
-                    const float2* p = reinterpret_cast<const float2*>((const float*)a.qkv + src + e0);
-                    const size_t step = a.qkv_stride / 2;
+                    const float2* p = reinterpret_cast<const float2*>((const float*)a.qkv + src);
 #pragma unroll
-                    for (int j = 0; j < E; ++j) x[j] = 0.f;
-                    for (int pl = 0; pl < a.qkv_planes; pl += 8) {     // up to eight planes' loads in flight before the first sum
-                        float2 v[8][E / 2];
+                    for (int u = 0; u < 8; ++u)
 #pragma unroll
-                        for (int u = 0; u < 8; ++u)
-#pragma unroll
-                            for (int j = 0; j < E / 2; ++j)
-                                v[u][j] = pl + u < a.qkv_planes ? p[(size_t)(pl + u) * step + j] : make_float2(0.f, 0.f);
-#pragma unroll
-                        for (int u = 0; u < 8; ++u)                    // summed in the order of the planes
-#pragma unroll
-                            for (int j = 0; j < E / 2; ++j) {
-                                x[2 * j] += v[u][j].x;
-                                x[2 * j + 1] += v[u][j].y;
-                            }
-                    }
+                        for (int j = 0; j < E / 2; ++j) v[u][j] = u < a.qkv_planes ? p[(size_t)u * step + j] : make_float2(0.f, 0.f);
                 } else {
-                    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>((const __nv_bfloat16*)a.qkv + src + e0);
+                    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>((const __nv_bfloat16*)a.qkv + src);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+#pragma unroll
+                        for (int j = 0; j < E / 2; ++j) v[u][j] = u == 0 ? __bfloat1622float2(p[j]) : make_float2(0.f, 0.f);
+                }
+            };
+            auto finish = [&](int job, const float2 (&v)[8][E / 2]) {
+                const bool is_q = job < nrows, is_v = job == nrows + 1;
+                float x[E];
+#pragma unroll
+                for (int j = 0; j < E; ++j) x[j] = 0.f;
+#pragma unroll
+                for (int u = 0; u < 8; ++u)                            // summed in the order of the planes
 #pragma unroll
                     for (int j = 0; j < E / 2; ++j) {
-                        const float2 v = __bfloat1622float2(p[j]);
-                        x[2 * j] = v.x;
-                        x[2 * j + 1] = v.y;
+                        x[2 * j] += v[u][j].x;
+                        x[2 * j + 1] += v[u][j].y;
                     }
+                if (a.qkv_f32 && a.qkv_planes > 8) {
+                    const float2* p = reinterpret_cast<const float2*>((const float*)a.qkv + (size_t)tok0 * width + (size_t)head_of(job) * D + e0);
+                    for (int pl = 8; pl < a.qkv_planes; ++pl)
+#pragma unroll
+                        for (int j = 0; j < E / 2; ++j) {
+                            const float2 more = p[(size_t)pl * step + j];
+                            x[2 * j] += more.x;
+                            x[2 * j + 1] += more.y;
+                        }
                 }
-                if (gain) {
+                if (a.q_gain && !is_v) {
                     float ssq = 0.f;
 #pragma unroll
                     for (int j = 0; j < E; ++j) ssq += x[j] * x[j];
                     const float inv = rsqrtf(warp_sum(ssq) / (float)D + a.eps);
 #pragma unroll
-                    for (int j = 0; j < E; ++j) x[j] = (x[j] * inv) * gain_at(e0 + j);
+                    for (int j = 0; j < E; ++j) x[j] = (x[j] * inv) * (is_q ? gain_q[j] : gain_k[j]);
                 }
                 if (cs && !is_v) {
-                    const int t0 = e0 - (lane >= 16 ? D / 2 : 0);      // this lane's place in the tables
 #pragma unroll
                     for (int j = 0; j < E; ++j) {
                         const float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
-                        const float cc = cs[t0 + j], ss = sn[t0 + j];
                         const float x1 = lane < 16 ? x[j] : other, x2 = lane < 16 ? other : x[j];
-                        x[j] = lane < 16 ? x1 * cc - x2 * ss : x2 * cc + x1 * ss;
+                        x[j] = lane < 16 ? x1 * cos_r[j] - x2 * sin_r[j] : x2 * cos_r[j] + x1 * sin_r[j];
                     }
                 }
+                __nv_bfloat16* cached = is_q ? nullptr : own_key + (is_v ? (size_t)a.nkv * head_stride : 0);
 #pragma unroll
                 for (int j = 0; j < E / 2; ++j) {
                     const uint32_t two = pack_bf16(x[2 * j], x[2 * j + 1]);
@@ -281,8 +322,24 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
                     if (is_q) *reinterpret_cast<uint32_t*>(q_s + swz<D>(job, i >> 3) + (i & 7) * 2) = two;
                     else *reinterpret_cast<uint32_t*>(cached + i) = two;
                 }
-                continue;
+            };
+            for (int job = warp; job < jobs; job += 2 * WARPS) {
+                float2 v0[8][E / 2], v1[8][E / 2];
+                const bool second = job + WARPS < jobs;
+                ask(job, v0);
+                if (second) ask(job + WARPS, v1);
+                finish(job, v0);
+                if (second) finish(job + WARPS, v1);
             }
+        } else if (!whole)
+        for (int job = warp; job < jobs; job += WARPS) {
+            const bool is_q = job < nrows, is_v = job == nrows + 1;
+            const size_t src = (size_t)tok0 * width + (size_t)head_of(job) * D;
+            const void* gain = is_q ? a.q_gain : (is_v ? nullptr : a.k_gain);
+            __nv_bfloat16* cached = is_q ? nullptr : own_key + (is_v ? (size_t)a.nkv * head_stride : 0);
+            auto gain_at = [&](int i) -> float {
+                return a.gain_f32 ? ((const float*)gain)[i] : __bfloat162float(((const __nv_bfloat16*)gain)[i]);
+            };
             auto put = [&](int i, float v) {
                 const __nv_bfloat16 b = __float2bfloat16_rn(v);
                 if (is_q) *reinterpret_cast<__nv_bfloat16*>(q_s + swz<D>(job, i >> 3) + (i & 7) * 2) = b;
@@ -335,6 +392,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         *reinterpret_cast<uint4*>(q_s + swz<D>(r, ch)) = val;
     }
     __syncthreads();
+    DECODE_STAMP(3);
     uint32_t qf[KSTEPS][4];
     {
         const int rbase = DECODE ? 0 : warp * 16;
@@ -364,6 +422,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         const int buf = t % STAGES;
         cp_async_wait<STAGES - 2>();
         __syncthreads();                                    // tile t has landed; tile t-1's readers are done
+        if (t == 0) DECODE_STAMP(4);
         if (t + STAGES - 1 < ntiles) load_tile(t + STAGES - 1, (t + STAGES - 1) % STAGES);
         cp_async_commit();
         const unsigned char* kt = k_s + buf * BN * D * 2;
@@ -456,6 +515,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         }
     }
 
+    DECODE_STAMP(5);
     // sums over the four threads that share a row
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
@@ -497,72 +557,89 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         mml[(warp * 16 + row_hi) * 2 + 1] = l_hi;
     }
     __syncthreads();
+    DECODE_STAMP(6);
     const float ln2 = 0.6931471805599453f;
     // CLUSTER: the blocks of the cluster hold the splits of one (request, kv head); each sends every other its
     // share of the merged sums through distributed shared memory, and after one cluster barrier each block
-    // finishes its share of the output, so that neither scratch in global memory nor a combine kernel is needed
+    // finishes its share of the output, so that neither scratch in global memory nor a combine kernel is needed.
+    // Sums travel and are merged four neighbouring features at a time (shares are multiples of four).
     cg::cluster_group cluster = cg::this_cluster();
     const int splits = a.splits, me = blockIdx.z;
     const int share = cluster_share(min(16, group), D, splits);
     float* recv_o = reinterpret_cast<float*>(smem_raw + stage_bytes<D, STAGES>(true));     // [splits][share]
     float* recv_ml = recv_o + (size_t)splits * share;                                        // [splits][16][2]
-    for (int i = tid; i < nrows * D; i += THREADS) {
-        const int r = i / D, col = i % D;
-        float mx = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mml[(w * 16 + r) * 2]);
-        float acc = 0.f, den = 0.f;
+    for (int i4 = tid; i4 < nrows * (D / 4); i4 += THREADS) {
+        const int r = i4 / (D / 4), col = (i4 % (D / 4)) * 4, i = r * D + col;
+        float mw[4], mx = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float mw = mml[(w * 16 + r) * 2];
-            if (mw > -INFINITY) {
-                const float f = exp2f(mw - mx);
-                acc += mo[(w * 16 + r) * D + col] * f;
+            mw[w] = mml[(w * 16 + r) * 2];
+            mx = fmaxf(mx, mw[w]);
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float den = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            if (mw[w] > -INFINITY) {
+                const float f = exp2f(mw[w] - mx);
+                const float4 v = *reinterpret_cast<const float4*>(mo + (w * 16 + r) * D + col);
+                acc.x += v.x * f;
+                acc.y += v.y * f;
+                acc.z += v.z * f;
+                acc.w += v.w * f;
                 den += mml[(w * 16 + r) * 2 + 1] * f;
             }
         }
         const int head = head0 + r;
         if (CLUSTER) {
             const int owner = i / share;
-            cluster.map_shared_rank(recv_o, owner)[me * share + (i - owner * share)] = acc;
-            if (col < splits) {                            // column p of the row tells block p the row's (max, sum)
-                float* ml = cluster.map_shared_rank(recv_ml, col) + (me * 16 + r) * 2;
-                ml[0] = mx;
-                ml[1] = den;
-            }
+            *reinterpret_cast<float4*>(cluster.map_shared_rank(recv_o, owner) + me * share + (i - owner * share)) = acc;
+            if (col / 4 < splits)                          // group p of four columns tells block p the row's (max, sum)
+                *reinterpret_cast<float2*>(cluster.map_shared_rank(recv_ml, col / 4) + (me * 16 + r) * 2) = make_float2(mx, den);
         } else if (a.splits > 1) {
             const size_t base = ((size_t)tok0 * a.nq + head) * a.splits + blockIdx.z;
-            a.part_o[base * D + col] = acc;
+            *reinterpret_cast<float4*>(a.part_o + base * D + col) = acc;
             if (col == 0) {
                 a.part_ml[base * 2] = mx * ln2;             // back to natural-log units for the combine kernel
                 a.part_ml[base * 2 + 1] = den;
             }
         } else {
-            ((__nv_bfloat16*)a.out)[((size_t)tok0 * a.nq + head) * D + col] =
-                __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+            const float inv = den > 0.f ? 1.f / den : 0.f;
+            *reinterpret_cast<uint2*>((__nv_bfloat16*)a.out + ((size_t)tok0 * a.nq + head) * D + col) =
+                make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         }
     }
+    DECODE_STAMP(7);
     if (CLUSTER) {
         cluster.sync();                                     // every block's sums have arrived; nobody is written to after this
-        for (int slot = tid; slot < share; slot += THREADS) {
+        DECODE_STAMP(8);
+        for (int slot = tid * 4; slot < share; slot += THREADS * 4) {
             const int i = me * share + slot;
             if (i >= nrows * D) break;
             const int r = i / D, col = i % D;
             float mx = -INFINITY;
             for (int sp = 0; sp < splits; ++sp) mx = fmaxf(mx, recv_ml[(sp * 16 + r) * 2]);
-            float acc = 0.f, den = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float den = 0.f;
             for (int sp = 0; sp < splits; ++sp) {           // in the order of the splits, whichever block merges
-                const float ms = recv_ml[(sp * 16 + r) * 2];
-                if (ms > -INFINITY) {
-                    const float f = exp2f(ms - mx);
-                    acc += recv_o[sp * share + slot] * f;
-                    den += recv_ml[(sp * 16 + r) * 2 + 1] * f;
+                const float2 ml = *reinterpret_cast<const float2*>(recv_ml + (sp * 16 + r) * 2);
+                if (ml.x > -INFINITY) {
+                    const float f = exp2f(ml.x - mx);
+                    const float4 v = *reinterpret_cast<const float4*>(recv_o + sp * share + slot);
+                    acc.x += v.x * f;
+                    acc.y += v.y * f;
+                    acc.z += v.z * f;
+                    acc.w += v.w * f;
+                    den += ml.y * f;
                 }
             }
-            ((__nv_bfloat16*)a.out)[((size_t)tok0 * a.nq + head0 + r) * D + col] =
-                __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+            const float inv = den > 0.f ? 1.f / den : 0.f;
+            *reinterpret_cast<uint2*>((__nv_bfloat16*)a.out + ((size_t)tok0 * a.nq + head0 + r) * D + col) =
+                make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         }
     }
+    DECODE_STAMP(9);
+    DECODE_SPAN(1);
 }
 
 // Raises the kernel's dynamic shared memory limit to `bytes` if it is lower (never lowers it).
@@ -699,6 +776,19 @@ using namespace lily;
 // CUDA-core kernels otherwise.
 LILY_API int lily_attention_mma_supports(int d) { return d == 64 || d == 128 || d == 192 || d == 256; }
 LILY_API int lily_attention_prefill_mma_rows() { return 64; }
+
+#ifdef LILY_DECODE_TIMING
+// The cycle stamps of the last decode launch: [first split, last split][phase].  Phases: 0 entry, 1 early tiles asked
+// for, 2 the kernel before has finished, 3 queries in shared memory, 4 first tile landed, 5 all tiles done, 6 the
+// four warps' results in shared memory, 7 sent to the cluster (or written), 8 the cluster's barrier passed, 9 exit.
+LILY_API int lily_attention_decode_timing(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, mma::g_decode_stamps, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : 1;
+}
+// Entry and exit times (ns) of the first `blocks` blocks (x fastest, then y, then z) of the last decode launch.
+LILY_API int lily_attention_decode_spans(unsigned long long* out, int blocks) {
+    return cudaMemcpyFromSymbol(out, mma::g_decode_spans, sizeof(unsigned long long) * 2 * (blocks < 4096 ? blocks : 4096)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 LILY_API int lily_attention_prefill_mma(const void* q, const void* kv, void* out, const int* block_table,
                                         int bt_stride, const int* cu_seqlens, const int* prefix_lens,
