@@ -50,10 +50,12 @@ def main() -> int:
     eng = Engine(EngineConfig("<random>", dtype="bfloat16", device="cuda:0", context_length=a.context,
                               max_running_requests=most, server_args={"page_size": 64, "random_seed": 0}), runner=runner)
     g = torch.Generator().manual_seed(1)
-    new_tokens = a.steps + 12
     h, layers = cfg["hidden_size"], a.layers
     weights = 2 * (layers * (h * (32 + 16) * 128 + 32 * 128 * h + 3 * h * cfg["intermediate_size"]) + cfg["vocab_size"] * h)
     for batch in a.batch:
+        # the first request decodes while the later ones are still being admitted, a portion of prompts a step:
+        # it must still be there when the last one has joined and the window has passed
+        new_tokens = a.steps + 12 + -(-batch * a.context // args.chunked_prefill_size)
         prompts = [torch.randint(0, cfg["vocab_size"], (a.context - new_tokens - 1,), generator=g).tolist() for _ in range(batch)]
         eng.generate(prompts, SamplingParams(max_new_tokens=new_tokens, ignore_eos=True))
         table = runner.profiler.tables.get(batch)

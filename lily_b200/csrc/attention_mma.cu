@@ -43,14 +43,15 @@ constexpr int THREADS = 128;
 // Also measured and not kept: asking the lines of the next two or four tiles into L2 (prefetch.global.L2, a line a
 // thread) while the block prepares its queries: the step of 8 requests went from 3.92 to 4.04 ms, of one from 3.30 to 3.43;
 // and asking the weights of the product behind the attention into L2 (cp.async.bulk.prefetch.L2, each block its share)
-// once a block's keys and values are in: 3.92 to 3.97 ms and 3.30 to 3.35 ms.
+// once a block's keys and values are in: 3.92 to 3.97 ms and 3.30 to 3.35 ms; and a final merge with a thread for each
+// (four features, split) and shuffles over the splits instead of a loop: 3.90 to 3.94 ms and 3.28 to 3.32 ms.
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-// Built with -DLILY_DECODE_TIMING, thread 0 of the first and of the last split of (request 0, kv head 0) stamp the
-// SM's cycle counter as they pass each phase of the decode kernel (lily_attention_decode_timing reads the stamps).
+// Built with -DLILY_DECODE_TIMING, thread 0 of each of the first 16 splits of (request 0, kv head 0) stamps the
+// SM's cycle counter as it passes each phase of the decode kernel (lily_attention_decode_timing reads the stamps).
 #ifdef LILY_DECODE_TIMING
-__device__ unsigned long long g_decode_stamps[2][16];
+__device__ unsigned long long g_decode_stamps[16][16];
 __device__ unsigned long long g_decode_spans[4096][2];      // per block: the global timer (ns) at entry and at exit
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
@@ -59,9 +60,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 #define DECODE_SPAN(which) do { const unsigned b__ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); \
                                 if (DECODE && threadIdx.x == 0 && b__ < 4096) g_decode_spans[b__][which] = global_ns(); } while (0)
-#define DECODE_STAMP(slot) do { if (DECODE && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && \
-                                    (blockIdx.z == 0 || blockIdx.z == gridDim.z - 1)) \
-                                    g_decode_stamps[blockIdx.z == 0 ? 0 : 1][slot] = (unsigned long long)clock64(); } while (0)
+#define DECODE_STAMP(slot) do { if (DECODE && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z < 16) \
+                                    g_decode_stamps[blockIdx.z][slot] = (unsigned long long)clock64(); } while (0)
 #else
 #define DECODE_STAMP(slot) do {} while (0)
 #define DECODE_SPAN(which) do {} while (0)
@@ -778,11 +778,11 @@ LILY_API int lily_attention_mma_supports(int d) { return d == 64 || d == 128 || 
 LILY_API int lily_attention_prefill_mma_rows() { return 64; }
 
 #ifdef LILY_DECODE_TIMING
-// The cycle stamps of the last decode launch: [first split, last split][phase].  Phases: 0 entry, 1 early tiles asked
+// The cycle stamps of the last decode launch: [split (the first 16)][phase] (16 x 16 numbers).  Phases: 0 entry, 1 early tiles asked
 // for, 2 the kernel before has finished, 3 queries in shared memory, 4 first tile landed, 5 all tiles done, 6 the
 // four warps' results in shared memory, 7 sent to the cluster (or written), 8 the cluster's barrier passed, 9 exit.
 LILY_API int lily_attention_decode_timing(unsigned long long* out) {
-    return cudaMemcpyFromSymbol(out, mma::g_decode_stamps, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : 1;
+    return cudaMemcpyFromSymbol(out, mma::g_decode_stamps, sizeof(unsigned long long) * 256) == cudaSuccess ? 0 : 1;
 }
 // Entry and exit times (ns) of the first `blocks` blocks (x fastest, then y, then z) of the last decode launch.
 LILY_API int lily_attention_decode_spans(unsigned long long* out, int blocks) {
