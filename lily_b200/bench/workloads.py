@@ -95,6 +95,7 @@ def main() -> int:
     for i, p in enumerate(prompts):
         sched.add_request(f"w{i}", p, SamplingParams(max_new_tokens=new_tokens, ignore_eos=True, temperature=a.temperature,
                                                      top_k=a.top_k, top_p=a.top_p, seed=i))
+    runner.capture_decode_graphs(range(1, requests + 1))      # as a server would: no step of the run pays for a capture
     torch.cuda.synchronize()
     start = time.perf_counter()
     steps = decode_only_steps = 0

@@ -72,6 +72,12 @@ class Engine:
         out = self.generate([list(prompt_ids)], SamplingParams(max_new_tokens=max_new_tokens, ignore_eos=ignore_eos))
         return out[0]["output_ids"]
 
+    @torch.inference_mode()
+    def capture_decode_graphs(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
+        """Captures the CUDA graphs of decode steps with these numbers of requests now (default: every bucket up to
+        ``max_running_requests``) rather than at the first step of each size; returns the buckets captured."""
+        return self.runner.capture_decode_graphs(batch_sizes)
+
     # ---- many sequences, through the scheduler ------------------------------------------
 
     def new_scheduler(self) -> Scheduler:

@@ -39,6 +39,7 @@ class DecodeProfiler:
         self.tables: Dict[int, str] = {}
         self._prof = None
         self._bs = self._n = 0
+        self._elapsed = 0.0
         self._seen = set()
 
     @classmethod
@@ -72,7 +73,7 @@ class DecodeProfiler:
     def _close(self) -> None:
         torch.cuda.synchronize()
         self._prof.__exit__(None, None, None)
-        table = self.table(self._kernel_times(), self._n, self._bs)
+        table = self.table(self._kernel_times(), self._n, self._bs, elapsed=self._elapsed)
         self.tables[self._bs] = table
         logger.info("%s", table)
         if self.out_dir:
@@ -91,6 +92,7 @@ class DecodeProfiler:
             if end > start:
                 spans.append((start, end, ev.name))
         spans.sort()
+        self._elapsed = (max(e for _, e, _ in spans) - spans[0][0]) if spans else 0.0
         own: Dict[str, float] = defaultdict(float)
         resident: Dict[str, float] = defaultdict(float)
         count: Dict[str, int] = defaultdict(int)
@@ -103,9 +105,10 @@ class DecodeProfiler:
         return sorted(((own[n], resident[n], count[n], n) for n in own), reverse=True)
 
     @staticmethod
-    def table(items: List[Tuple[float, float, int, str]], steps: int, batch: int, rows: int = 40) -> str:
+    def table(items: List[Tuple[float, float, int, str]], steps: int, batch: int, rows: int = 40, elapsed: float = 0.0) -> str:
         whole = sum(t for t, _, _, _ in items) or 1.0
-        lines = [f"decode step at batch {batch}: device time per step over {steps} steps",
+        idle = f" ({elapsed / steps:.1f} us a step from the first kernel's start to the last one's end)" if elapsed else ""
+        lines = [f"decode step at batch {batch}: device time per step over {steps} steps{idle}",
                  f"{'own us':>9} {'%':>5} {'resident':>9} {'launches':>8}  kernel",
                  f"{whole / steps:9.1f} {100.0:5.1f} {sum(r for _, r, _, _ in items) / steps:9.1f} "
                  f"{sum(c for _, _, c, _ in items) / steps:8.1f}  all kernels"]

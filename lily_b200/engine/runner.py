@@ -319,6 +319,23 @@ class ModelRunner:
             return None
         return next(b for b in self.graph_buckets if b >= len(entries))
 
+    def capture_decode_graphs(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
+        """Captures the decode graphs for these batch sizes now (default: every bucket) instead of at the first step
+        that needs each, and returns the buckets captured.  A capture runs the model three times on padded rows that
+        belong to no request, so it needs no live request and disturbs none; a server that wants no pause at the
+        first step of each batch size calls this once after loading (the reference captures all of its buckets when
+        the runner is built: lily/model_executor/cuda_graph_runner.py:93,147-149)."""
+        if not self.use_graphs:
+            return []
+        want = self.graph_buckets if batch_sizes is None else sorted(
+            {next(b for b in self.graph_buckets if b >= n) for n in batch_sizes if 1 <= n <= self.graph_buckets[-1]})
+        done = []
+        for bucket in want:
+            if bucket not in self._graphs:
+                self._graphs[bucket] = _DecodeGraph(self, bucket)
+                done.append(bucket)
+        return done
+
     def _decode_with_graph(self, entries: Sequence[StepEntry], bucket: int) -> torch.Tensor:
         """A step of one token per request, each wanting its logits, through a captured graph."""
         vocab = self.spec.vocab_size

@@ -10,6 +10,7 @@ import torch
 import plain_impl
 import tiny_models
 from harness import make_runner, model_dir, run_mixed, run_portions, run_whole
+from lily_b200.engine.batch import StepEntry
 
 pytestmark = pytest.mark.gpu
 
@@ -70,6 +71,27 @@ def test_head_size_128_paths_inside_the_engine(dtype):
             from lily_b200.csrc import ops
             assert ops.uses_tcgen05_attention(torch.bfloat16, cfg["head_dim"], 64, 130)     # the portions of 130 tokens and more
             assert ops.attention_tc_status() == 0 and ops.gemm_tc_status() == 0          # no bounded wait gave up
+
+
+def test_decode_graphs_captured_ahead():
+    """Capturing the decode graphs while a request is half way through its prompt disturbs neither its cache nor what
+    it decodes afterwards, and the steps that follow find their graphs there."""
+    cfg = tiny_models.MID_QWEN3
+    with tempfile.TemporaryDirectory() as tmp:
+        path, weights = model_dir(cfg, 35, tmp)
+        ids = tiny_models.random_tokens(200, cfg["vocab_size"], 7)
+        want = plain_impl.all_logits(cfg, rounded(weights, "bfloat16"), ids)
+        runner = make_runner(path, dtype="bfloat16", device="cuda", page_size=64, max_tokens=1024)
+        slot = runner.open_request()
+        first = runner.step([StepEntry(slot, ids[:150], list(range(150)))])
+        assert runner.capture_decode_graphs([1, 3]) == [1, 4] and runner.capture_decode_graphs([2, 4]) == [2]
+        graphs = dict(runner._graphs)
+        rest = [runner.step([StepEntry(slot, [t], [0])]).clone() for t in ids[150:]]     # a graph's logits live until its next replay
+        assert runner.graph_steps == 50 and runner._graphs == graphs            # nothing was captured on the way
+        close(torch.cat([first] + rest).cpu(), want, "bfloat16", "captured ahead")
+        runner.close_request(slot)
+        assert runner.cache.held_pages() == [0]
+        assert len(runner.capture_decode_graphs()) == len(runner.graph_buckets) - 3
 
 
 @pytest.mark.parametrize("seed", range(8))
