@@ -2,6 +2,7 @@
 requests, most of a request in one step and the last 32 tokens one by one, portions of changing
 size down to two tokens, and mixed batches over so few pages that they are used again."""
 
+import os
 import tempfile
 
 import pytest
@@ -285,7 +286,7 @@ def test_many_live_requests(which, dtype, live, graphs, monkeypatch):
         assert decode, plans
         if which == "mid_8kv":            # 8 kv heads: 160 and 560 (request, kv head) pairs
             arms = {p.arm for p in decode}
-            if dtype == "bfloat16" and live == 20:
+            if dtype == "bfloat16" and live == 20 and os.environ.get("LILY_B200_DECODE_CLUSTER") != "0":
                 assert arms == {"cluster"}, arms                                   # merged inside clusters
             else:
                 assert arms == {"wave"} and all(p.scratch_floats > 0 for p in decode), arms     # scratch and the combine kernel
