@@ -206,12 +206,73 @@ attention_simt_kernel(const AttnArgs a) {
     }
 }
 
-// Merges the partial results of the splits: grid (requests, query heads), threads over d.
+// Merges the partial results of the splits: grid (requests, query heads), threads over d.  With 9 to 256 splits the
+// block has four rows of threads and first brings every split's (max, sum) into shared memory, one a thread, and
+// forms the weights exp(m - max) there; each row of threads then sums every fourth split, loads that do not wait for
+// one another, and the first row adds the four partial sums up, in a fixed order.  (With dozens of splits the plain
+// loops are a chain of trips to L2: 22 us for 55 splits.)  Fewer splits (where the staging costs more than it saves:
+// a step of 64 requests with 4 splits each 10.44 -> 10.53 ms) and more take the plain loops, a column in the order of
+// the splits.
+constexpr int COMBINE_STAGED = 256, COMBINE_ROWS = 4, COMBINE_D = 256;
+static bool combine_staged(int splits, int d) { return splits > 8 && splits <= COMBINE_STAGED && d <= COMBINE_D; }
+
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          T* __restrict__ out, int nq, int d, int splits) {
+    __shared__ float w_s[COMBINE_STAGED], l_s[COMBINE_STAGED];
+    __shared__ float red[32];
+    __shared__ float sums[COMBINE_ROWS - 1][COMBINE_D];
     pdl_enter_small();
     const size_t base = ((size_t)blockIdx.x * nq + blockIdx.y) * splits;
+    if (blockDim.y > 1) {                                   // the launcher's choice: combine_staged(splits, d)
+        const int tid = threadIdx.y * blockDim.x + threadIdx.x, threads = blockDim.x * blockDim.y;
+        float mx = -INFINITY;
+        for (int s = tid; s < splits; s += threads) {
+            const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + s) * 2);
+            w_s[s] = ml.x;
+            l_s[s] = ml.y;
+            mx = fmaxf(mx, ml.x);
+        }
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if ((tid & 31) == 0) red[tid >> 5] = mx;
+        __syncthreads();
+        mx = red[0];
+        for (int w = 1; w < (threads + 31) / 32; ++w) mx = fmaxf(mx, red[w]);
+        for (int s = tid; s < splits; s += threads) w_s[s] = w_s[s] > -INFINITY ? expf(w_s[s] - mx) : 0.f;
+        __syncthreads();
+        const int rows = blockDim.y, row = threadIdx.y;
+        float part[COMBINE_D / 128];                          // blockDim.x is 128: a thread has up to two columns
+#pragma unroll
+        for (int j = 0; j < COMBINE_D / 128; ++j) {
+            const int c = threadIdx.x + j * 128;
+            float o = 0.f;
+            if (c < d) {
+#pragma unroll 4
+                for (int s = row; s < splits; s += rows) {
+                    const float v = part_o[(base + s) * d + c];
+                    if (w_s[s] != 0.f) o += v * w_s[s];        // a split without keys has weight 0 whatever it left
+                }
+                if (row > 0) sums[row - 1][c] = o;
+            }
+            part[j] = o;
+        }
+        __syncthreads();
+        if (row == 0) {
+            float denom = 0.f;
+            for (int s = 0; s < splits; ++s) denom += l_s[s] * w_s[s];
+            const float inv = denom > 0.f ? 1.f / denom : 0.f;
+#pragma unroll
+            for (int j = 0; j < COMBINE_D / 128; ++j) {
+                const int c = threadIdx.x + j * 128;
+                if (c < d) {
+                    float o = part[j];
+                    for (int r = 1; r < rows; ++r) o += sums[r - 1][c];
+                    out[((size_t)blockIdx.x * nq + blockIdx.y) * d + c] = from_float<T>(o * inv);
+                }
+            }
+        }
+        return;
+    }
     float mx = -INFINITY;
     for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
     float denom = 0.f;
@@ -295,11 +356,11 @@ LILY_API int lily_attention_combine(const float* scratch, void* out, int request
     if (requests == 0 || splits <= 1) return 0;
     const float* part_o = scratch;
     const float* part_ml = scratch + (size_t)requests * nq * splits * d;
-    dim3 cgrid(requests, nq);
+    dim3 cgrid(requests, nq), cblock(128, combine_staged(splits, d) ? COMBINE_ROWS : 1);
     if (dtype == kBF16)
-        launch_pdl(attention_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, nq, d, splits);
+        launch_pdl(attention_combine_kernel<__nv_bfloat16>, cgrid, cblock, 0, stream, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, nq, d, splits);
     else
-        launch_pdl(attention_combine_kernel<float>, cgrid, dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, (float*)out, nq, d, splits);
+        launch_pdl(attention_combine_kernel<float>, cgrid, cblock, 0, stream, (const float*)part_o, (const float*)part_ml, (float*)out, nq, d, splits);
     LILY_CHECK_LAUNCH("attention_combine");
     return 0;
 }
@@ -332,11 +393,11 @@ LILY_API int lily_attention_decode_simt(const void* q, const void* kv, void* out
     if (rc) return rc;
     LILY_CHECK_LAUNCH("attention_decode");
     if (splits > 1) {
-        dim3 cgrid(requests, nq);
+        dim3 cgrid(requests, nq), cblock(128, combine_staged(splits, d) ? COMBINE_ROWS : 1);
         if (dtype == kBF16)
-            launch_pdl(attention_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (__nv_bfloat16*)out, nq, d, splits);
+            launch_pdl(attention_combine_kernel<__nv_bfloat16>, cgrid, cblock, 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (__nv_bfloat16*)out, nq, d, splits);
         else
-            launch_pdl(attention_combine_kernel<float>, cgrid, dim3(128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (float*)out, nq, d, splits);
+            launch_pdl(attention_combine_kernel<float>, cgrid, cblock, 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (float*)out, nq, d, splits);
         LILY_CHECK_LAUNCH("attention_combine");
     }
     return 0;

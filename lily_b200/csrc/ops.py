@@ -533,7 +533,12 @@ def choose_decode_splits(num_decode: int, kv_heads: int, max_seq_len: int, sm_co
     most ranges that allow this are the fastest (measured on a B200, head size 128, 8 kv heads:
     batch 1 and 2: 16 ranges; 4: 10; 8: 6; 16: 3; 24: 2; sizes past 8 want a tenth of room to spare:
     24 pairs in clusters of 15, of which exactly 24 fit, took 21 us against 16 us in clusters of 13).
-    Without that (float32, other head sizes, more pairs than clusters of two): the single wave that
+    A cluster has at most 16 blocks, so a few long rows leave most of the device idle (one row of 131,072 keys:
+    128 blocks, 168 us, half of the memory's speed); where one full wave through scratch and the combine kernel
+    has a quarter more blocks than the clusters and the rows are long enough to pay for the extra kernel, the
+    wave is taken (55 ranges for that row: 97 us; measured crossovers, 8 kv heads: one row 30 k keys, two rows
+    20 k, three and four rows 16 k; five rows and more fill the device with clusters).
+    Without clusters (float32, other head sizes, more pairs than clusters of two): the single wave that
     comes closest to filling the device, and when the rows alone overfill it, about four waves
     (batch 64: 4 ranges).  The reference fixes 32 splits with a floor of 64 keys
     (lily/layers/attention/triton_backend.py:21, decode_attention.py:68,172)."""
@@ -542,9 +547,12 @@ def choose_decode_splits(num_decode: int, kv_heads: int, max_seq_len: int, sm_co
     limit = max(1, min(max_splits, max_seq_len // min_keys))
     pairs, held = num_decode * kv_heads, sm_count * blocks_per_sm
     if clusters is not None:
+        full = max(1, min(64, max_seq_len // min_keys, held // pairs))      # ranges that fill the device once
         for s in range(min(limit, 16), 1, -1):
             room = clusters(s)
             if pairs <= (room if s <= 8 else 0.9 * room):
+                if full * 4 >= s * 5 and max_seq_len >= max(16384, 512 * full + 4096):
+                    return full
                 return s
     one_wave = min(limit, held // pairs)
     if one_wave >= 1 and (pairs * one_wave >= 0.7 * held or one_wave == limit):

@@ -73,10 +73,12 @@ class Engine:
         return out[0]["output_ids"]
 
     @torch.inference_mode()
-    def capture_decode_graphs(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
+    def capture_decode_graphs(self, batch_sizes: Optional[Sequence[int]] = None,
+                              max_len: Optional[int] = None) -> List[int]:
         """Captures the CUDA graphs of decode steps with these numbers of requests now (default: every bucket up to
-        ``max_running_requests``) rather than at the first step of each size; returns the buckets captured."""
-        return self.runner.capture_decode_graphs(batch_sizes)
+        ``max_running_requests``) rather than at the first step of each size, for sequences of up to ``max_len``
+        positions (default: every length class up to the context length); returns the buckets captured."""
+        return self.runner.capture_decode_graphs(batch_sizes, max_len)
 
     # ---- many sequences, through the scheduler ------------------------------------------
 

@@ -63,13 +63,14 @@ class _PinnedRing:
 
 
 class _DecodeGraph:
-    """One captured decode step for up to ``bucket`` requests.  Its metadata lives in one static
-    int32 buffer that every replay overwrites; rows beyond the live requests point at slot 0 and
+    """One captured decode step for up to ``bucket`` requests of up to ``max_len`` positions.  Its metadata lives
+    in one static int32 buffer that every replay overwrites; rows beyond the live requests point at slot 0 and
     page 0, which no request owns (lily/model_executor/cuda_graph_runner.py:53-65,153-186 pads
     the same way)."""
 
-    def __init__(self, runner: "ModelRunner", bucket: int):
+    def __init__(self, runner: "ModelRunner", bucket: int, max_len: int):
         self.bucket = b = bucket
+        self.max_len = max_len
         self.widths = [runner.cache.max_pages_per_request for _ in runner.cache.groups]
         self.sizes = [b, b, b, b + 1, b, b, b, b] + [b * w for w in self.widths]
         total = sum(self.sizes)
@@ -81,8 +82,8 @@ class _DecodeGraph:
             num_tokens=b, num_requests=b, num_decode=b, token_ids=parts[0], positions=parts[1], token_req=parts[2],
             cu_seqlens=parts[3], prefix_lens=parts[4], seq_lens=parts[5], slots=parts[6], logit_rows=parts[7],
             block_tables=[parts[8 + i].view(b, w) for i, w in enumerate(self.widths)],
-            h_new_lens=[1] * b, h_prefix_lens=[0] * b, h_slots=[0] * b, max_seq_len=runner.context_len,
-            max_decode_len=runner.context_len,          # the mixers plan for the longest sequence a replay may bring
+            h_new_lens=[1] * b, h_prefix_lens=[0] * b, h_slots=[0] * b, max_seq_len=max_len,
+            max_decode_len=max_len,                     # the mixers plan for the longest sequence a replay may bring
             workspace=Workspace(runner.device),         # scratch of its own: the graph holds its address
             future_tokens=runner.future_tokens)
         # views of the pinned copy, field by field; what never changes is written once, here
@@ -205,12 +206,22 @@ class ModelRunner:
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
-        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}      # by (batch bucket, length class)
         self.use_graphs = self.device.type == "cuda" and not args.disable_cuda_graph and self.model.graph_safe
         max_bs = args.cuda_graph_max_bs or min(self.max_requests, 256)
         self.graph_buckets = sorted(set(args.cuda_graph_bs or
                                         [b for b in (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256) if b <= max_bs]
                                         + [max_bs]))
+        # A mixer plans a captured step for the longest sequence a replay may bring, and the best plan for a long
+        # sequence is a poor one for a short one (decode attention over 128 k keys wants many more key ranges than
+        # over 4 k).  So graphs also come in classes of sequence length: 16 k positions, then doubling up to the
+        # context length; a model with a context of 16 k or less has one class, as before.
+        self.length_classes = []
+        bound = 16384
+        while bound < self.context_len:
+            self.length_classes.append(bound)
+            bound *= 2
+        self.length_classes.append(self.context_len)
 
     # ---- construction ---------------------------------------------------------------
 
@@ -319,21 +330,30 @@ class ModelRunner:
             return None
         return next(b for b in self.graph_buckets if b >= len(entries))
 
-    def capture_decode_graphs(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
+    def _length_class(self, longest: int) -> int:
+        return next((c for c in self.length_classes if c >= longest), self.length_classes[-1])
+
+    def capture_decode_graphs(self, batch_sizes: Optional[Sequence[int]] = None,
+                              max_len: Optional[int] = None) -> List[int]:
         """Captures the decode graphs for these batch sizes now (default: every bucket) instead of at the first step
-        that needs each, and returns the buckets captured.  A capture runs the model three times on padded rows that
-        belong to no request, so it needs no live request and disturbs none; a server that wants no pause at the
-        first step of each batch size calls this once after loading (the reference captures all of its buckets when
-        the runner is built: lily/model_executor/cuda_graph_runner.py:93,147-149)."""
+        that needs each, and returns the buckets captured: for sequences of up to ``max_len`` positions, or, by
+        default, for every class of sequence length the context allows (one, up to a context of 16 k positions).
+        A capture runs the model three times on padded rows that belong to no request, so it needs no live request
+        and disturbs none; a server that wants no pause at the first step of each batch size calls this once after
+        loading (the reference captures all of its buckets when the runner is built:
+        lily/model_executor/cuda_graph_runner.py:93,147-149)."""
         if not self.use_graphs:
             return []
         want = self.graph_buckets if batch_sizes is None else sorted(
             {next(b for b in self.graph_buckets if b >= n) for n in batch_sizes if 1 <= n <= self.graph_buckets[-1]})
+        classes = self.length_classes if max_len is None else [self._length_class(max_len)]
         done = []
         for bucket in want:
-            if bucket not in self._graphs:
-                self._graphs[bucket] = _DecodeGraph(self, bucket)
-                done.append(bucket)
+            for cls in classes:
+                if (bucket, cls) not in self._graphs:
+                    self._graphs[(bucket, cls)] = _DecodeGraph(self, bucket, cls)
+                    if bucket not in done:
+                        done.append(bucket)
         return done
 
     def _decode_with_graph(self, entries: Sequence[StepEntry], bucket: int) -> torch.Tensor:
@@ -356,9 +376,10 @@ class ModelRunner:
             self.cache.grow(slot, new_len)
         if check.ENABLED:
             check.check_entries(self, entries)
-        graph = self._graphs.get(bucket)
+        key = (bucket, self._length_class(max(n for _, n in wants)))
+        graph = self._graphs.get(key)
         if graph is None:
-            graph = self._graphs[bucket] = _DecodeGraph(self, bucket)
+            graph = self._graphs[key] = _DecodeGraph(self, *key)
         groups = range(len(self.cache.groups))
         tables = [[self.cache.block_table(g, e.slot) for e in entries] for g in groups]
         stamps = [[self.cache.table_stamp(g, e.slot) for e in entries] for g in groups]

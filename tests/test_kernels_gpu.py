@@ -397,7 +397,7 @@ def test_attention_prefill_tcgen05_rising_scores():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("splits", [1, 3, 6, 7, 8, 12])
+@pytest.mark.parametrize("splits", [1, 3, 6, 7, 8, 12, 40, 300])         # 300: past what the combine kernel stages in shared memory
 @pytest.mark.parametrize("nq,nkv,d,page,window", [
     (4, 2, 16, 16, None), (8, 2, 32, 16, None), (6, 2, 48, 8, 40), (5, 1, 80, 32, None), (32, 8, 128, 64, None),
     (2, 2, 256, 16, 100), (40, 1, 32, 16, None), (16, 16, 64, 16, 7), (40, 2, 64, 16, None), (6, 2, 192, 32, 500),
@@ -413,6 +413,45 @@ def test_attention_decode(dtype, splits, nq, nkv, d, page, window):
     ops().attention_decode(q, cache, table, seq_t, got, scratch, splits, nq, nkv, d, page, d ** -0.5, window)
     ref.attention_decode(q, cache, table, seq_t, want, None, splits, nq, nkv, d, page, d ** -0.5, window)
     torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("requests,longest", [(1, 40000), (2, 30000), (4, 20000)])
+def test_attention_decode_of_a_few_long_rows(requests, longest):
+    """A few rows of tens of thousands of keys: the plan leaves the clusters (16 blocks a row at most) for one full
+    wave of ranges through scratch and the combine kernel, from the qkv product as the engine would run it; one far
+    key among them carries the row (its key is the query scaled up)."""
+    o = ops()
+    dtype, nq, nkv, d, page = torch.bfloat16, 32, 8, 128, 64
+    plan = o.plan_decode_attention(dtype, requests, nq, nkv, d, longest)
+    assert plan.arm == "wave" and plan.splits > 16 // requests + 8 and plan.fused and plan.scratch_floats > 0
+    seqs = [longest - 1777 * i for i in range(requests)]
+    cache, table, _, cu, pre = _attention_case(dtype, nq, nkv, d, page, [n - 1 for n in seqs], [1] * requests, None, seed=10)
+    g = torch.Generator(device=DEV).manual_seed(92)
+    qkv = torch.randn(3, requests, (nq + 2 * nkv) * d, device=DEV, generator=g) * 0.6
+    far = 12345                                                     # a position in the middle of some range
+    q_sum = qkv.sum(0)
+    for r in range(requests):
+        pg, off = int(table[r, far // page]), far % page
+        for h in range(nkv):
+            cache[pg, 0, h, off] = (q_sum[r].view(nq + 2 * nkv, d)[h * (nq // nkv)] * 3).to(dtype)
+    seq_t = torch.tensor(seqs, device=DEV, dtype=torch.int32)
+    scratch = torch.full((plan.scratch_floats,), float("nan"), device=DEV)
+    got, want = (torch.zeros(requests, nq * d, device=DEV, dtype=dtype) for _ in range(2))
+    one, two = cache.clone(), cache.clone()
+    o.attention_decode_fused(qkv, None, None, 1e-6, None, None, one, table, seq_t, got, scratch, plan.splits, nq, nkv, d, 0,
+                             page, d ** -0.5)
+    ref.attention_decode_fused(qkv, None, None, 1e-6, None, None, two, table, seq_t, want, None, plan.splits, nq, nkv, d, 0,
+                                page, d ** -0.5)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    torch.testing.assert_close(one.float(), two.float(), atol=2 ** -7, rtol=2 ** -7)
+    # the far key matters: without it the heads that look at it give another result
+    cache2 = cache.clone()
+    for r in range(requests):
+        cache2[int(table[r, far // page]), 0, :, far % page] = 0
+    other = torch.zeros_like(got)
+    o.attention_decode_fused(qkv, None, None, 1e-6, None, None, cache2, table, seq_t, other, scratch, plan.splits, nq, nkv, d, 0,
+                             page, d ** -0.5)
+    assert float((other.float() - got.float()).abs().max()) > 0.05
 
 
 @pytest.mark.parametrize("planes", [1, 3])
