@@ -1,4 +1,5 @@
-// Causal paged attention for prefill on the fifth-generation tensor cores (bfloat16, head size 128):
+// Causal paged attention for prefill on the fifth-generation tensor cores (bfloat16, head sizes 128 and 64;
+// the numbers below are for 128, where a row of Q, K or V is two 128-byte sub-tiles; 64 has one):
 // both products of a tile, S = Q K^T and O += P V, are tcgen05.mma instructions with their
 // accumulators in tensor memory, the operands arrive by TMA, and the softmax runs two threads per
 // query row straight out of tensor memory.  (The reference runs prefill attention through a
@@ -44,7 +45,7 @@ namespace fa {
 
 constexpr int BQ = 128;                   // query rows per block
 constexpr int BKV = 128;                  // keys per tile
-constexpr int D = 128;                    // head size
+// head sizes: 128 and 64 (the kernels are templates over D; a row of Q, K or V is D / 64 sub-tiles of 128 bytes)
 // P (the second product's A operand) either goes through shared memory, or, packed as bfloat16
 // pairs, into the tensor-memory columns of the S tile it was computed from; the latter leaves
 // shared memory to K, V and Q alone (a third K/V stage fits) and spares the async-proxy fence.
@@ -61,17 +62,19 @@ constexpr int STAGES = PARTS == 2 ? 3 : 2;
 #endif
 constexpr int SBUF = 2;                   // S accumulators (and P buffers)
 constexpr int SUB = 128 * 64 * 2;         // a [128 rows][64 elements] sub-tile with 128-byte rows: 16 KB
-constexpr int TILE = 2 * SUB;             // Q, one K stage, one V stage, one P buffer: 32 KB
+constexpr int tile_bytes(int d) { return d / 64 * SUB; }      // Q, one K stage, one V stage: 128 rows of d features
+constexpr int P_TILE = 2 * SUB;           // a P buffer in shared memory: 128 rows x 128 keys
 constexpr int BOX = 64 * 64 * 2;          // one TMA box of K or V: 8 KB
 constexpr int SOFTMAX_THREADS = PARTS * 128;
 constexpr int THREADS = 64 + SOFTMAX_THREADS;
 constexpr int NUM_BARS = 1 + 4 * STAGES + 3 * SBUF;
 // shared memory, all of it dynamic and 1024-byte aligned: Q | K stages | V stages | P buffers | mbarriers |
 // tensor-memory base and abort flag | the row maxima and sums that the two threads of a row exchange
-constexpr int OFF_BARS = (1 + 2 * STAGES + (P_TMEM ? 0 : SBUF)) * TILE;
-constexpr int OFF_MISC = OFF_BARS + 8 * NUM_BARS + 8;
-constexpr int OFF_XCH = OFF_MISC + 16;
-constexpr int SMEM = OFF_XCH + 2 * PARTS * BQ * 4;
+constexpr int off_p(int d) { return (1 + 2 * STAGES) * tile_bytes(d); }
+constexpr int off_bars(int d) { return off_p(d) + (P_TMEM ? 0 : SBUF) * P_TILE; }
+constexpr int off_misc(int d) { return off_bars(d) + 8 * NUM_BARS + 8; }
+constexpr int off_xch(int d) { return off_misc(d) + 16; }
+constexpr int smem_one(int d) { return off_xch(d) + 2 * PARTS * BQ * 4; }
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr float GROW_LOG2 = 8.f;          // the reference maximum moves when the true one is 2^8 ahead
 
@@ -208,13 +211,17 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Params p) {
+    static_assert(D == 64 || D == 128, "head sizes 64 and 128");
+    static_assert(D / PARTS % 32 == 0, "a softmax thread's share of a row of O comes in pieces of 32 columns");
+    constexpr int TILE = tile_bytes(D), DH = D / 64;
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
-    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem + OFF_MISC);
-    int& abort_s = *reinterpret_cast<int*>(smem + OFF_MISC + 4);
-    float* xch = reinterpret_cast<float*>(smem + OFF_XCH);      // [tile parity][half][row]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off_bars(D));
+    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem + off_misc(D));
+    int& abort_s = *reinterpret_cast<int*>(smem + off_misc(D) + 4);
+    float* xch = reinterpret_cast<float*>(smem + off_xch(D));   // [tile parity][half][row]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if ((smem_u32(smem) & 1023u) != 0) {                        // the swizzled tiles need it; never seen, but checked
         if (threadIdx.x == 0) atomicCAS(&g_status, 0, (11 << 24) | (int)((blockIdx.x + blockIdx.y * gridDim.x) & 0xFFFFFF));
@@ -281,8 +288,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const int kvh = head / (p.nq / p.nkv);
             const int* table = p.block_table + (size_t)req * p.bt_stride;
             mbar_expect_tx(q_full, TILE);
-            tma_load_3d(q_smem, &map_q, q_full, 0, head, q_begin + start);
-            tma_load_3d(q_smem + SUB, &map_q, q_full, 64, head, q_begin + start);
+            for (int dh = 0; dh < DH; ++dh) tma_load_3d(q_smem + dh * SUB, &map_q, q_full, dh * 64, head, q_begin + start);
             bool ok = true;
             int issued_k = 0, issued_v = 0;
             for (int j = 0; j < n && ok; ++j) {
@@ -299,14 +305,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (!ok) break;
                 mbar_expect_tx(k_full + 8 * s, TILE);
                 for (int h = 0; h < 2; ++h)
-                    for (int dh = 0; dh < 2; ++dh)
+                    for (int dh = 0; dh < DH; ++dh)
                         tma_load_4d(k_smem + s * TILE + dh * SUB + h * BOX, &map_kv, k_full + 8 * s, dh * 64, off[h], kvh, page[h]);
                 ++issued_k;
                 { FA_TIC(); ok = mbar_wait(v_empty + 8 * s, par ^ 1, abort_flag, 2); FA_TOC(1, true); }
                 if (!ok) break;
                 mbar_expect_tx(v_full + 8 * s, TILE);
                 for (int h = 0; h < 2; ++h)
-                    for (int dh = 0; dh < 2; ++dh)
+                    for (int dh = 0; dh < DH; ++dh)
                         tma_load_4d(v_smem + s * TILE + dh * SUB + h * BOX, &map_kv, v_full + 8 * s, dh * 64, off[h], p.nkv + kvh, page[h]);
                 ++issued_v;
             }
@@ -356,7 +362,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (ok) { FA_TIC(); ok = mbar_wait(v_full + 8 * s, (uint32_t)((j / STAGES) & 1), abort_flag, 6); FA_TOC(3, true); }
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t dv = desc_mn_major(v_smem + s * TILE), dp = desc_k_major(p_smem + b * TILE);
+                const uint64_t dv = desc_mn_major(v_smem + s * TILE), dp = desc_k_major(p_smem + b * P_TILE);
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; ++kk) {
                     const uint64_t db = dv + (uint64_t)(kk * 2048 >> 4);
@@ -505,7 +511,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (!ok) break;
                 }
                 // this thread's keys lie in sub-tile (part * COLS) / 64 of P: 128-byte rows, 16-byte pieces swizzled
-                unsigned char* prow = smem + (size_t)(1 + 2 * STAGES) * TILE + (size_t)b * TILE + (size_t)((part * COLS) / 64) * SUB + (size_t)row * 128;
+                unsigned char* prow = smem + (size_t)off_p(D) + (size_t)b * P_TILE + (size_t)((part * COLS) / 64) * SUB + (size_t)row * 128;
                 const int c0 = ((part * COLS) % 64) / 8;
 #pragma unroll
                 for (int c = 0; c < COLS / 8; ++c) {
@@ -572,24 +578,27 @@ constexpr int NH2 = 2;
 constexpr int KV2 = 2;                                   // K stages, V stages
 constexpr int THREADS2 = 64 + NH2 * BQ;
 constexpr int NUM_BARS2 = 1 + 4 * KV2 + 3 * NH2 + 1;   // the last one is the timing build's probe
-constexpr int OFF2_K = NH2 * TILE;
-constexpr int OFF2_V = OFF2_K + KV2 * TILE;
-constexpr int OFF2_BARS = OFF2_V + KV2 * TILE;
-constexpr int OFF2_MISC = OFF2_BARS + 8 * NUM_BARS2 + 8;
-constexpr int SMEM2 = OFF2_MISC + 16;
+constexpr int off2_k(int d) { return NH2 * tile_bytes(d); }
+constexpr int off2_v(int d) { return off2_k(d) + KV2 * tile_bytes(d); }
+constexpr int off2_bars(int d) { return off2_v(d) + KV2 * tile_bytes(d); }
+constexpr int off2_misc(int d) { return off2_bars(d) + 8 * NUM_BARS2 + 8; }
+constexpr int smem_two(int d) { return off2_misc(d) + 16; }
 
+template <int D>
 __global__ void __launch_bounds__(THREADS2, 1)
 attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Params p) {
+    static_assert(D == 64 || D == 128, "head sizes 64 and 128");
+    constexpr int TILE = tile_bytes(D), DH = D / 64;
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF2_BARS);
-    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem + OFF2_MISC);
-    int& abort_s = *reinterpret_cast<int*>(smem + OFF2_MISC + 4);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off2_bars(D));
+    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem + off2_misc(D));
+    int& abort_s = *reinterpret_cast<int*>(smem + off2_misc(D) + 4);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if ((smem_u32(smem) & 1023u) != 0) {
         if (threadIdx.x == 0) atomicCAS(&g_status, 0, (11 << 24) | (int)((blockIdx.x + blockIdx.y * gridDim.x) & 0xFFFFFF));
         return;
     }
-    const uint32_t q_smem = smem_u32(smem), k_smem = q_smem + OFF2_K, v_smem = q_smem + OFF2_V;
+    const uint32_t q_smem = smem_u32(smem), k_smem = q_smem + off2_k(D), v_smem = q_smem + off2_v(D);
     const uint32_t q_full = smem_u32(&bars[0]);
     const uint32_t k_full = q_full + 8, k_empty = k_full + 8 * KV2, v_full = k_empty + 8 * KV2, v_empty = v_full + 8 * KV2;
     const uint32_t s_full = v_empty + 8 * KV2, p_full = s_full + 8 * NH2, pv_done = p_full + 8 * NH2;   // one per head
@@ -642,7 +651,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
             const int* table = p.block_table + (size_t)req * p.bt_stride;
             mbar_expect_tx(q_full, NH2 * TILE);
             for (int h = 0; h < NH2; ++h)
-                for (int dh = 0; dh < 2; ++dh)
+                for (int dh = 0; dh < DH; ++dh)
                     tma_load_3d(q_smem + h * TILE + dh * SUB, &map_q, q_full, dh * 64, head0 + h, q_begin + start);
             bool ok = true;
             int issued_k = 0, issued_v = 0;
@@ -660,14 +669,14 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 if (!ok) break;
                 mbar_expect_tx(k_full + 8 * s, TILE);
                 for (int h = 0; h < 2; ++h)
-                    for (int dh = 0; dh < 2; ++dh)
+                    for (int dh = 0; dh < DH; ++dh)
                         tma_load_4d(k_smem + s * TILE + dh * SUB + h * BOX, &map_kv, k_full + 8 * s, dh * 64, off[h], kvh, page[h]);
                 ++issued_k;
                 ok = mbar_wait(v_empty + 8 * s, par ^ 1, abort_flag, 2);
                 if (!ok) break;
                 mbar_expect_tx(v_full + 8 * s, TILE);
                 for (int h = 0; h < 2; ++h)
-                    for (int dh = 0; dh < 2; ++dh)
+                    for (int dh = 0; dh < DH; ++dh)
                         tma_load_4d(v_smem + s * TILE + dh * SUB + h * BOX, &map_kv, v_full + 8 * s, dh * 64, off[h], p.nkv + kvh, page[h]);
                 ++issued_v;
             }
@@ -713,7 +722,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     const int reps = kind == 0 ? 4 : (kind == 3 ? 0 : (kind == 1 ? 1 : 4));
                     for (int r = 0; r < reps; ++r)
 #pragma unroll
-                        for (int kk = 0; kk < 8; ++kk) {
+                        for (int kk = 0; kk < D / 16; ++kk) {
                             const uint64_t inside = (uint64_t)(((kk >> 2) * SUB + (kk & 3) * 32) >> 4);
                             if (kind <= 1) umma(tmem, dq + inside, dk + inside, idesc_s, 1u);
                             else umma_ts(tmem_o, tmem + (uint32_t)(kk * 8), dv + (uint64_t)(kk * 2048 >> 4), idesc_o, 1u);
@@ -896,6 +905,27 @@ static EncodeTiled encoder() {
     return fn;
 }
 
+// Launches the kernel of head size D with one head or two heads a block (the shared memory limits are raised once).
+template <int D>
+static int launch(bool two, int nq, int tiles, cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_kv, const Params& p) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_one(D));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attention_prefill_tc2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_two(D));
+        if (e != cudaSuccess) {
+            set_error("attention_prefill_tc: cannot get %d bytes of shared memory: %s", smem_one(D), cudaGetErrorString(e));
+            return 2;
+        }
+        configured = true;
+    }
+    if (two)
+        launch_pdl(attention_prefill_tc2_kernel<D>, dim3(nq / 2, tiles), dim3(THREADS2), (size_t)smem_two(D), stream, map_q, map_kv, p);
+    else
+        launch_pdl(attention_prefill_tc_kernel<D>, dim3(nq, tiles), dim3(THREADS), (size_t)smem_one(D), stream, map_q, map_kv, p);
+    return 0;
+}
+
 }  // namespace fa
 }  // namespace lily
 
@@ -916,7 +946,7 @@ LILY_API int lily_attention_tc_timing(unsigned long long* out) {
 LILY_API int lily_attention_prefill_tc_rows() { return fa::BQ; }
 
 // Whether the tcgen05 kernel takes this head size and page size (bfloat16 only).
-LILY_API int lily_attention_prefill_tc_takes(int d, int page_size) { return d == fa::D && page_size > 0 && page_size % 64 == 0; }
+LILY_API int lily_attention_prefill_tc_takes(int d, int page_size) { return (d == 64 || d == 128) && page_size > 0 && page_size % 64 == 0; }
 
 // 0 while no wait has given up since the last call; else (code << 24 | block).  Codes: 1, 2 the
 // loader waiting for a free K or V stage; 3, 4, 6 the mma thread waiting for Q, K or V; 5 the mma
@@ -937,8 +967,8 @@ LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out,
                                        const int* tile_start, int tiles, int nq, int nkv, int d, int page_size, int window,
                                        float scale, int tokens, int num_pages, int heads_per_block, cudaStream_t stream) {
     if (tiles == 0) return 0;
-    LILY_REQUIRE(lily_attention_prefill_tc_takes(d, page_size), "attention_prefill_tc: head size %d, page size %d (takes %d and multiples of 64)",
-                 d, page_size, fa::D);
+    LILY_REQUIRE(lily_attention_prefill_tc_takes(d, page_size), "attention_prefill_tc: head size %d, page size %d (takes 64 or 128, and multiples of 64)",
+                 d, page_size);
     LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill_tc: %d query heads over %d kv heads", nq, nkv);
     LILY_REQUIRE(tiles <= 65535 && tokens > 0 && num_pages > 0, "attention_prefill_tc: tiles=%d tokens=%d pages=%d", tiles, tokens, num_pages);
     LILY_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)kv % 16 == 0) && ((uintptr_t)out % 16 == 0), "attention_prefill_tc: operands must be 16-byte aligned");
@@ -965,17 +995,6 @@ LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         LILY_REQUIRE(rc == CUDA_SUCCESS, "attention_prefill_tc: cuTensorMapEncodeTiled (cache) failed with %d", (int)rc);
     }
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(fa::attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::SMEM);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(fa::attention_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::SMEM2);
-        if (e != cudaSuccess) {
-            set_error("attention_prefill_tc: cannot get %d bytes of shared memory: %s", fa::SMEM, cudaGetErrorString(e));
-            return 2;
-        }
-        configured = true;
-    }
     fa::Params p{};
     p.block_table = block_table; p.cu_seqlens = cu_seqlens; p.prefix_lens = prefix_lens; p.tile_req = tile_req;
     p.tile_start = tile_start; p.out = (__nv_bfloat16*)out; p.bt_stride = bt_stride; p.tiles = tiles; p.nq = nq; p.nkv = nkv;
@@ -987,10 +1006,8 @@ LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out,
     LILY_REQUIRE(heads_per_block >= 0 && heads_per_block <= 2 && (heads_per_block != 2 || even),
                  "attention_prefill_tc: %d heads a block with %d query heads per kv head", heads_per_block, nq / nkv);
     const bool two = heads_per_block == 2 || (heads_per_block == 0 && even && (long)tiles * (nq / 2) >= sms);
-    if (two)
-        launch_pdl(fa::attention_prefill_tc2_kernel, dim3(nq / 2, tiles), dim3(fa::THREADS2), (size_t)fa::SMEM2, stream, map_q, map_kv, p);
-    else
-        launch_pdl(fa::attention_prefill_tc_kernel, dim3(nq, tiles), dim3(fa::THREADS), (size_t)fa::SMEM, stream, map_q, map_kv, p);
+    const int rc = d == 64 ? fa::launch<64>(two, nq, tiles, stream, map_q, map_kv, p) : fa::launch<128>(two, nq, tiles, stream, map_q, map_kv, p);
+    if (rc) return rc;
     LILY_CHECK_LAUNCH("attention_prefill_tc");
     return 0;
 }

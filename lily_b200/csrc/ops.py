@@ -431,7 +431,7 @@ TC_ATTENTION_MIN_TOKENS = 128
 
 def uses_tcgen05_attention(dtype: torch.dtype, d: int, page_size: int, new_tokens: int) -> bool:
     """Whether prefill attention of this precision, head size, page size and number of new tokens
-    runs on the tcgen05 kernel (bfloat16, head size 128, pages of a multiple of 64 positions)."""
+    runs on the tcgen05 kernel (bfloat16, head size 128 or 64, pages of a multiple of 64 positions)."""
     return (dtype == torch.bfloat16 and new_tokens >= TC_ATTENTION_MIN_TOKENS
             and bool(library().lily_attention_prefill_tc_takes(int(d), int(page_size))))
 

@@ -45,13 +45,14 @@ def setup(request):
         yield cfg, weights, path
 
 
+@pytest.mark.parametrize("head_dim", [128, 64])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_head_size_128_paths_inside_the_engine(dtype):
-    """Head size 128, widths in multiples of 128, page size 64: tensor-core attention (tcgen05 for
+def test_head_size_128_paths_inside_the_engine(dtype, head_dim):
+    """Head size 128 (and 64), widths in multiples of 128, page size 64: tensor-core attention (tcgen05 for
     portions of 128 tokens and more, mma.sync below that and for split-key decode through graphs),
     the tcgen05 gate/up kernel and the weight-streaming decode product, all through the step
     function, against the plain implementation."""
-    cfg = tiny_models.MID_QWEN3
+    cfg = dict(tiny_models.MID_QWEN3, head_dim=head_dim)
     with tempfile.TemporaryDirectory() as tmp:
         path, weights = model_dir(cfg, 33, tmp)
         v = cfg["vocab_size"]

@@ -333,12 +333,13 @@ def _tiles_of(news, rows):
     return (torch.tensor(treq, device=DEV, dtype=torch.int32), torch.tensor(tstart, device=DEV, dtype=torch.int32))
 
 
+@pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("nq,nkv,page,window", [(8, 2, 64, None), (4, 4, 128, None), (6, 1, 256, None), (4, 2, 64, 200),
                                                  (2, 1, 64, 100), (4, 2, 128, 129), (6, 2, 64, None), (3, 3, 64, 70)])
-def test_attention_prefill_tcgen05(nq, nkv, page, window):
-    """The tcgen05 kernel (tiles of 128 rows) against the plain statement: cached prefixes that end
-    inside a page and inside a key tile, portions shorter and longer than a tile, one token."""
-    o, d, dtype = ops(), 128, torch.bfloat16
+def test_attention_prefill_tcgen05(nq, nkv, page, window, d):
+    """The tcgen05 kernel (tiles of 128 rows; head sizes 128 and 64) against the plain statement: cached prefixes
+    that end inside a page and inside a key tile, portions shorter and longer than a tile, one token."""
+    o, dtype = ops(), torch.bfloat16
     rows = o.prefill_tile_rows(dtype, d, page, 10 ** 6)
     assert rows == 128 and o.uses_tcgen05_attention(dtype, d, page, 4096) and not o.uses_tcgen05_attention(dtype, d, 16, 4096)
     prefixes, news = [0, 17, 130, 5, 700, 64, 1000], [1, 70, 333, 200, 129, 2, 640]
@@ -369,10 +370,11 @@ def test_attention_prefill_tcgen05(nq, nkv, page, window):
     torch.testing.assert_close(got.float(), other.float(), **tol(dtype))
 
 
-def test_attention_prefill_tcgen05_rising_scores():
+@pytest.mark.parametrize("d", [128, 64])
+def test_attention_prefill_tcgen05_rising_scores(d):
     """Scores that grow by far more than 2^8 from one key tile to the next, for every row: the kernel
     must rescale the output in tensor memory each time (the path that ordinary data rarely takes)."""
-    o, d, dtype, nq, nkv, page = ops(), 128, torch.bfloat16, 4, 2, 64
+    o, dtype, nq, nkv, page = ops(), torch.bfloat16, 4, 2, 64
     g = torch.Generator(device=DEV).manual_seed(21)
     prefixes, news = [300, 0], [520, 700]
     cache, table, q, cu, pre = _attention_case(dtype, nq, nkv, d, page, prefixes, news, None, seed=22)
