@@ -200,7 +200,7 @@ def main() -> int:
             x = torch.randn(a.tokens, a.k, device=dev, generator=g).to(dt)
             w = torch.randn(a.n, a.k, device=dev, generator=g).to(dt)
             if a.kernel == "swiglu_skinny":          # n is the fused matrix's height, 2 x intermediate
-                need = ops.swiglu_skinny_need(a.tokens, a.n // 2, a.k, dt, 128)
+                need = ops.swiglu_skinny_need(a.tokens, a.n // 2, a.k, dt, 128, whenever_possible=True)
                 scratch = torch.empty(need[0], device=dev)
                 counters = torch.zeros(need[1], device=dev, dtype=torch.int32)
                 fns.append(lambda x=x, w=w, scratch=scratch, counters=counters: ops.swiglu_skinny(x, w, 128, scratch, counters))

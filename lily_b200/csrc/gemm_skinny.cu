@@ -473,13 +473,17 @@ LILY_API int lily_skinny_gemm(const void* x, const void* w, float* parts, int M,
 }
 
 // Whether the fused gate/up product takes this shape, and what it needs: `scratch_floats` float32 of scratch and
-// `counters` int32 that are zero before the first launch (the kernel leaves them zero).
+// `counters` int32 that are zero before the first launch (the kernel leaves them zero).  Returns 0 for a shape the
+// kernel does not take, 2 for one it takes but where the library product followed by SiLU*mul is the faster pair: wide
+// inputs whose x does not fit beside the rings, so that the lanes read it from global memory, a cost that grows with
+// the tokens (measured, x from global memory against the library: K = 5120, I = 25600: 84 / 94 us at 1 token, 86 / 95 at
+// 4, 95 / 96 at 8; K = 8192, I = 28672: 145 / 151 at 1, 152 / 149 at 4, 162 / 145 at 8), and 1 otherwise.
 LILY_API int lily_skinny_swiglu_need(int M, int I, int K, int run, size_t* scratch_floats, int* counters) {
     const skinny::SwigluPlan p = skinny::swiglu_plan(M, I, K, run);
     if (p.grid == 0) return 0;
     if (scratch_floats) *scratch_floats = p.scratch_floats;
     if (counters) *counters = p.row_blocks;
-    return 1;
+    return !p.xsmem && (long long)M * K > 3 * 8192 ? 2 : 1;
 }
 
 // out [M, I] bfloat16 = silu(x . gate^T) * (x . up^T); w [2 I, K] holds runs of `run` gate rows and the `run` up

@@ -362,15 +362,17 @@ def linear_auto(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
 
 
 def swiglu_skinny_need(tokens: int, intermediate: int, hidden: int, dtype: torch.dtype,
-                       block: Optional[int] = None) -> Optional[Tuple[int, int]]:
+                       block: Optional[int] = None, whenever_possible: bool = False) -> Optional[Tuple[int, int]]:
     """(float32 of scratch, int32 counters) that ``swiglu_skinny`` wants for this shape, or None when it does not
-    take it (more than 8 tokens, not bfloat16, K not a multiple of 64): the caller then forms the product and
-    SiLU*mul separately.  ``LILY_B200_SWIGLU=library`` always answers None."""
+    take it (more than 8 tokens, not bfloat16, K not a multiple of 64) or, unless ``whenever_possible``, when the
+    library product followed by SiLU*mul is the faster pair for it (several tokens of a very wide input): the caller
+    then forms the product and SiLU*mul separately.  ``LILY_B200_SWIGLU=library`` always answers None."""
     if dtype != torch.bfloat16 or _LIBRARY_SWIGLU:
         return None
     floats, counters = _sz(0), _i(0)
-    if not library().lily_skinny_swiglu_need(int(tokens), int(intermediate), int(hidden), int(block or intermediate),
-                                             ctypes.byref(floats), ctypes.byref(counters)):
+    verdict = library().lily_skinny_swiglu_need(int(tokens), int(intermediate), int(hidden), int(block or intermediate),
+                                                ctypes.byref(floats), ctypes.byref(counters))
+    if verdict == 0 or (verdict == 2 and not whenever_possible):
         return None
     return int(floats.value), int(counters.value)
 
@@ -387,7 +389,7 @@ def swiglu_skinny(x: torch.Tensor, gate_up: torch.Tensor, block: Optional[int], 
     _dev(x, gate_up, scratch, counters, out)
     m, k = x.shape
     inter = gate_up.shape[0] // 2
-    need = swiglu_skinny_need(m, inter, k, x.dtype, block)
+    need = swiglu_skinny_need(m, inter, k, x.dtype, block, whenever_possible=True)
     if need is None or gate_up.dtype != torch.bfloat16 or gate_up.shape[1] != k:
         raise KernelError(f"swiglu_skinny: x {tuple(x.shape)} {x.dtype} against {tuple(gate_up.shape)} {gate_up.dtype}")
     if scratch.dtype != torch.float32 or scratch.numel() < need[0] or counters.dtype != torch.int32 or counters.numel() < need[1]:

@@ -144,7 +144,7 @@ def linear_auto(x, weight, bias=None):
     return linear(x, weight, bias)
 
 
-def swiglu_skinny_need(tokens, intermediate, hidden, dtype, block=None):
+def swiglu_skinny_need(tokens, intermediate, hidden, dtype, block=None, whenever_possible=False):
     return (16, 4) if dtype == torch.bfloat16 and tokens <= 8 and hidden % 64 == 0 else None
 
 

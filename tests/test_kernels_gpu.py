@@ -162,7 +162,7 @@ def test_skinny_swiglu(m, inter, k, run):
     g = torch.Generator(device=DEV).manual_seed(12)
     x = torch.randn(m, k, device=DEV, generator=g).bfloat16()
     w = (torch.randn(2 * inter, k, device=DEV, generator=g) * k ** -0.5).bfloat16()
-    need = o.swiglu_skinny_need(m, inter, k, torch.bfloat16, run)
+    need = o.swiglu_skinny_need(m, inter, k, torch.bfloat16, run, whenever_possible=True)
     assert need is not None
     scratch = torch.full((need[0],), float("nan"), device=DEV)
     counters = torch.zeros(need[1], device=DEV, dtype=torch.int32)
@@ -177,6 +177,9 @@ def test_skinny_swiglu(m, inter, k, run):
     alone = o.swiglu_skinny(x[:1].contiguous(), w, run, scratch, counters)
     assert torch.equal(alone[0], got[0])
     assert o.swiglu_skinny_need(9, inter, k, torch.bfloat16, run) is None
+    # several tokens of an input too wide to stage beside the rings: the kernel takes it, the library pair is preferred
+    from_global = os.environ.get("LILY_B200_SWIGLU_X") == "global" or (m, inter, k) == (7, 25600, 5120)
+    assert (o.swiglu_skinny_need(m, inter, k, torch.bfloat16, run) is None) == (from_global and m * k > 3 * 8192)
     assert o.swiglu_skinny_need(m, inter, k, torch.float32, run) is None
     assert o.swiglu_skinny_need(m, inter, k + 8, torch.bfloat16, run) is None
 
