@@ -44,11 +44,15 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 // NT: 8-token tiles (M <= 8 * NT).  MT: 16-row tiles of w per warp.  WARPS per block.  KT: k per
-// tile (64: 128 contiguous bytes of each row per copy round).
-template <int NT, int MT, int WARPS, int STAGES, int KT>
+// tile (64: 128 contiguous bytes of each row per copy round).  XSMEM: the block's slice of x is staged in shared
+// memory; without it (a slice too long to fit beside the rings of two blocks a SM: deep products of wide models, or
+// 9 to 16 tokens) every lane reads its own fragments of x from global memory, one tile of k ahead: x is small and
+// stays in the caches, and all shared memory goes to the rings.
+template <int NT, int MT, int WARPS, int STAGES, int KT, bool XSMEM>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    float* __restrict__ parts, int M, int N, int K, int blocks_per_slice) {
+    static_assert(XSMEM || (KT == 64 && NT <= 2), "x from global memory: tiles of 64 k, up to 16 tokens");
     constexpr int ROWS = 16 * MT;                     // weight rows per warp
     constexpr int PIECES = KT / 8;                    // 16-byte pieces per row of a tile
     constexpr int PITCH = KT * 2;                     // bytes per row of a tile
@@ -92,13 +96,32 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 
     // stage this slice of x: rows beyond M are zero
     const int chunks = nkb * PIECES;
-    for (int i = tid; i < NT * 8 * chunks; i += WARPS * 32) {
-        const int r = i / chunks, ch = i % chunks;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < M) v = *reinterpret_cast<const uint4*>(x + (size_t)r * K + (size_t)kb0 * KT + ch * 8);
-        *reinterpret_cast<uint4*>(xs + ((size_t)r * chunks + (ch ^ (r & 7))) * 16) = v;
+    if (XSMEM) {
+        for (int i = tid; i < NT * 8 * chunks; i += WARPS * 32) {
+            const int r = i / chunks, ch = i % chunks;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < M) v = *reinterpret_cast<const uint4*>(x + (size_t)r * K + (size_t)kb0 * KT + ch * 8);
+            *reinterpret_cast<uint4*>(xs + ((size_t)r * chunks + (ch ^ (r & 7))) * 16) = v;
+        }
+        __syncthreads();
     }
-    __syncthreads();
+    // without XSMEM: a lane's fragments of x for 64 k and token tile nt: token 8 nt + g, for each of the four k16
+    // steps the pairs at 2c and 2c + 8
+    constexpr int XT = XSMEM ? 1 : NT;
+    uint32_t xf[XT][8], xnext[XT][8];
+    auto load_x = [&](int kb, uint32_t (&f)[XT][8]) {
+#pragma unroll
+        for (int nt = 0; nt < XT; ++nt) {
+            const int tok = nt * 8 + g;
+            const uint32_t* p = reinterpret_cast<const uint32_t*>(x + (size_t)min(tok, M - 1) * K + (size_t)(kb0 + kb) * KT + 2 * c);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                f[nt][2 * kk] = tok < M ? __ldg(p + kk * 8) : 0u;
+                f[nt][2 * kk + 1] = tok < M ? __ldg(p + kk * 8 + 4) : 0u;
+            }
+        }
+    };
+    if (!XSMEM && nkb > 0) load_x(0, xnext);
 
     float acc[MT][NT][4];
 #pragma unroll
@@ -112,6 +135,13 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         if (kb + STAGES - 1 < nkb) issue(kb + STAGES - 1);
         cp_async_commit();
         const uint32_t tile = smem_u32(ring + (kb % STAGES) * TILE);
+        if (!XSMEM) {
+#pragma unroll
+            for (int nt = 0; nt < XT; ++nt)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) xf[nt][j] = xnext[nt][j];
+            if (kb + 1 < nkb) load_x(kb + 1, xnext);
+        }
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
             uint32_t a[MT][4];
@@ -127,7 +157,14 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                 const int r = np * 16 + (lane & 7) + ((lane >> 4) << 3);
                 const int ch = kb * PIECES + kk * 2 + ((lane >> 3) & 1);
                 const int rr = NT == 1 ? (lane & 7) : r;              // one tile only: both halves read tokens 0-7
-                ldmatrix_x4(smem_u32(xs + ((size_t)rr * chunks + (ch ^ (rr & 7))) * 16), b0, b1, b2, b3);
+                if (XSMEM) {
+                    ldmatrix_x4(smem_u32(xs + ((size_t)rr * chunks + (ch ^ (rr & 7))) * 16), b0, b1, b2, b3);
+                } else {
+                    b0 = xf[2 * np < XT ? 2 * np : 0][2 * (kk & 3)];
+                    b1 = xf[2 * np < XT ? 2 * np : 0][2 * (kk & 3) + 1];
+                    b2 = xf[2 * np + 1 < XT ? 2 * np + 1 : 0][2 * (kk & 3)];
+                    b3 = xf[2 * np + 1 < XT ? 2 * np + 1 : 0][2 * (kk & 3) + 1];
+                }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     mma_bf16(acc[mt][2 * np], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
@@ -166,13 +203,26 @@ static size_t smem_bytes(const Shape& s, int tiles_per_slice) {
     return (size_t)s.warps * s.stages * 16 * s.mt * s.kt * 2 + (size_t)s.nt * 8 * tiles_per_slice * s.kt * 2;
 }
 
-template <int NT, int MT, int WARPS, int STAGES, int KT>
-static int launch(const __nv_bfloat16* x, const __nv_bfloat16* w, float* parts, int M, int N, int K, int ksplit,
-                  cudaStream_t stream) {
+// Two blocks a SM: what a block may take of the SM's shared memory.
+constexpr size_t kHalfSm = 112 * 1024;
+static size_t ring_bytes(const Shape& s) { return (size_t)s.warps * s.stages * 16 * s.mt * s.kt * 2; }
+// Whether the lanes read x from global memory: a slice of x that does not fit beside the rings, and few enough
+// tokens that the lanes' own loads of x (4 bytes each, a token's row per group of four lanes) cost less than they
+// save.  Measured against the library, us: K = 25600, N = 5120: 41.6 / 51.4 at 1 token, 45.0 / 49.3 at 2, 48.0 / 51.1 at
+// 4, 52.6 / 48.2 at 8; K = 8192, N = 10240: 28.4 / 34.3 at 1, 33.4 / 35.3 at 4, 37.3 / 34.2 at 8; K = 28672, N = 8192:
+// 74.5 / 79.7 at 1, 82.0 / 77.4 at 2; 16 tokens: twice the library's time everywhere.
+static bool x_from_global(const Shape& s, int tiles_per_slice, int M, int K) {
+    return s.nt <= 2 && smem_bytes(s, tiles_per_slice) > kHalfSm && (long long)M * K <= 2 * 25600;
+}
+
+template <int NT, int MT, int WARPS, int STAGES, int KT, bool XSMEM>
+static int launch_form(const __nv_bfloat16* x, const __nv_bfloat16* w, float* parts, int M, int N, int K, int ksplit,
+                       cudaStream_t stream) {
     const int tiles = K / KT;
     const int per = (tiles + ksplit - 1) / ksplit;
-    const size_t smem = smem_bytes(Shape{NT, MT, WARPS, STAGES, KT}, per);
-    auto kern = skinny_gemm_kernel<NT, MT, WARPS, STAGES, KT>;
+    const Shape sh{NT, MT, WARPS, STAGES, KT};
+    const size_t smem = XSMEM ? smem_bytes(sh, per) : ring_bytes(sh);
+    auto kern = skinny_gemm_kernel<NT, MT, WARPS, STAGES, KT, XSMEM>;
     static size_t granted = 48 * 1024;
     if (smem > granted) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -185,6 +235,17 @@ static int launch(const __nv_bfloat16* x, const __nv_bfloat16* w, float* parts, 
     dim3 grid((N + WARPS * 16 * MT - 1) / (WARPS * 16 * MT), ksplit);
     launch_pdl(kern, grid, dim3(WARPS * 32), smem, stream, x, w, parts, M, N, K, per);
     return 0;
+}
+
+template <int NT, int MT, int WARPS, int STAGES, int KT>
+static int launch(const __nv_bfloat16* x, const __nv_bfloat16* w, float* parts, int M, int N, int K, int ksplit,
+                  cudaStream_t stream) {
+    if constexpr (NT <= 2 && KT == 64) {
+        const int tiles = K / KT;
+        if (x_from_global(Shape{NT, MT, WARPS, STAGES, KT}, (tiles + ksplit - 1) / ksplit, M, K))
+            return launch_form<NT, MT, WARPS, STAGES, KT, false>(x, w, parts, M, N, K, ksplit, stream);
+    }
+    return launch_form<NT, MT, WARPS, STAGES, KT, true>(x, w, parts, M, N, K, ksplit, stream);
 }
 
 
@@ -448,7 +509,10 @@ LILY_API int lily_skinny_gemm_splits(int M, int N, int K) {
     int s = held / row_blocks;
     const int longest = tiles * sh.kt / 512 > 0 ? tiles * sh.kt / 512 : 1;      // slices of at least 512 k
     s = s < 1 ? 1 : (s > longest ? longest : s);
-    while (s < tiles && skinny::smem_bytes(sh, (tiles + s - 1) / s) > 112 * 1024) ++s;
+    // a slice of x that does not fit beside the rings: a few tokens read x from global memory instead; more
+    // tokens take more, shorter slices while those still fit one wave
+    if (!skinny::x_from_global(sh, (tiles + s - 1) / s, M, K))
+        while (s < tiles && skinny::smem_bytes(sh, (tiles + s - 1) / s) > skinny::kHalfSm) ++s;
     return row_blocks * s <= held ? s : 0;
 }
 

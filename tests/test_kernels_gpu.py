@@ -115,7 +115,9 @@ def test_linear_bf16_and_fp32_logits():
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (8, 6144, 4096), (8, 4096, 12288), (5, 331, 128), (16, 1000, 256),
-                                   (17, 136, 64), (33, 2000, 1024), (64, 4096, 1024), (3, 24576, 4096), (64, 24, 64)])
+                                   (17, 136, 64), (33, 2000, 1024), (64, 4096, 1024), (3, 24576, 4096), (64, 24, 64),
+                                   (8, 5120, 25600), (16, 4096, 12288),                                     # a long slice of x
+                                   (1, 5120, 25600), (2, 5120, 25600), (3, 10240, 8192), (3, 300, 16384)])   # x read from global memory
 def test_skinny_gemm_partial_sums(m, n, k):
     g = torch.Generator(device=DEV).manual_seed(11)
     x = torch.randn(m, k, device=DEV, generator=g).bfloat16()
@@ -124,7 +126,7 @@ def test_skinny_gemm_partial_sums(m, n, k):
     assert parts is not None and parts.dtype == torch.float32 and parts.shape[1:] == (m, n)
     auto = ops().linear_split(x, w)                     # the kernel's own rule may leave the shape to the library
     if auto is not None:
-        torch.testing.assert_close(auto.sum(0), parts.sum(0), atol=1e-3, rtol=1e-4)
+        torch.testing.assert_close(auto.sum(0), parts.sum(0), atol=2e-5 * (k ** 0.5) * 4, rtol=1e-4)       # other slices, other rounding
     want = x.double() @ w.double().t()
     got = parts.double().sum(0)
     assert float((got - want).abs().max()) < 2e-5 * (k ** 0.5) * 4      # float32 accumulation of exact products
