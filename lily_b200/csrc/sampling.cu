@@ -392,6 +392,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
         floor_key = max(floor_key, cut);
     }
     const float mp = min_p[r];
+    if (threadIdx.x < 32) sh.wsum[threadIdx.x] = 0;     // a block of fewer than 32 warps leaves the other slots empty
+    __syncthreads();
 
     // kept mass of each warp's contiguous segment of the slice (lanes interleaved, so the reads
     // coalesce), then the draw in vocabulary order: the segment in which the running mass passes the
@@ -564,7 +566,10 @@ LILY_API int lily_sample(const float* logits, const float* temperature, const in
         // a cluster of CL blocks per row
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(CL, rows);
-        cfg.blockDim = dim3(STHREADS);
+        // more blocks than the device holds at once (a block of 1,024 threads has a SM to itself): half the threads,
+        // so that two blocks share a SM and one computes while the other waits at a cluster barrier
+        // (vocabulary 151,936, temperature only: 64 rows 139 -> 96 us, 256 rows 486 -> 339 us; with top-p 1904 -> 1442 us)
+        cfg.blockDim = dim3((long)CL * rows > sm_count() ? STHREADS / 2 : STHREADS);
         cfg.dynamicSmemBytes = (size_t)cache_floats * 4;
         cfg.stream = stream;
         cudaLaunchAttribute attr[1];

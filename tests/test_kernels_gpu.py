@@ -609,13 +609,15 @@ def test_top_logprobs(vocab):
     assert rc.tolist() == counts.tolist()
 
 
-@pytest.mark.parametrize("vocab", [256, 1009, 151936])
-def test_sample_matches_filtered_distribution(vocab):
+@pytest.mark.parametrize("vocab,copies", [(256, 1), (1009, 1), (151936, 1), (151936, 4)])
+def test_sample_matches_filtered_distribution(vocab, copies):
+    """(Four copies of the cases at the large vocabulary: more blocks than the device holds at once, which the
+    launcher gives half the threads each.)"""
     import plain_impl
 
     g = torch.Generator(device=DEV).manual_seed(9)
     cases = [(0.7, -1, 1.0, 0.0), (1.0, 5, 1.0, 0.0), (1.3, -1, 0.6, 0.0), (0.9, 50, 0.8, 0.05), (1.0, -1, 1.0, 0.2),
-             (0.0, -1, 1.0, 0.0), (1.0, 1, 1.0, 0.0), (2.0, -1, 0.05, 0.0)]
+             (0.0, -1, 1.0, 0.0), (1.0, 1, 1.0, 0.0), (2.0, -1, 0.05, 0.0)] * copies
     rows = len(cases)
     logits = torch.randn(rows, vocab, device=DEV, generator=g) * 3
     t = torch.tensor([c[0] for c in cases], device=DEV)
