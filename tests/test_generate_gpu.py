@@ -191,6 +191,30 @@ def test_the_step_profile_names_this_packages_kernels(monkeypatch):
     assert 10 < per_step < 5000                     # microseconds of device time a step
 
 
+def test_a_long_request_beside_short_ones_through_the_engine():
+    """A prompt of more than 16 k positions beside short ones (context 40 k, 8 kv heads): the scheduler's decode steps
+    move from the graphs of the first class of sequence length to those of the second once the long request is among
+    them, its attention takes one full wave of key ranges, and every generated token is still the prefill path's argmax."""
+    from lily_b200 import SamplingParams
+    from lily_b200.bench.check_greedy import check_greedy
+    cfg = dict(tiny_models.MID_QWEN3, num_attention_heads=8, num_key_value_heads=8, max_position_embeddings=40000)
+    with tempfile.TemporaryDirectory() as tmp:
+        path, _ = model_dir(cfg, 65, tmp)
+        from lily_b200 import Engine, EngineConfig
+        eng = Engine(EngineConfig(path, dtype="bfloat16", max_total_tokens=24000, max_running_requests=4, context_length=40000))
+        prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], 400 + n) for n in (300, 16500, 40)]
+        outs = [o["output_ids"] for o in eng.generate(prompts, SamplingParams(max_new_tokens=32, ignore_eos=True))]
+        report = check_greedy(eng, prompts, outs)
+        long_classes = sorted({cls for _, cls in eng.runner._graphs})
+        short = [prompts[0], prompts[2]]                   # the short ones alone: the first class's graphs
+        again = [o["output_ids"] for o in eng.generate(short, SamplingParams(max_new_tokens=32, ignore_eos=True))]
+        classes = sorted({cls for _, cls in eng.runner._graphs})
+    assert report["tokens"] == 3 * 32 and report["max_gap"] < 3e-2, report
+    assert long_classes == [32768] and classes == [16384, 32768], (long_classes, classes)
+    # beside the long request or alone, through either class of graphs: the same tokens up to near-ties
+    assert sum(a != b for x, y in zip(again, (outs[0], outs[2])) for a, b in zip(x, y)) <= 2
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_generated_tokens_are_the_prefill_paths_argmax(dtype):
     """What the decode path generated (graphs, split-key attention, the decode products) against one teacher-forced
