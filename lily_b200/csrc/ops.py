@@ -536,10 +536,11 @@ def choose_decode_splits(num_decode: int, kv_heads: int, max_seq_len: int, sm_co
     batch 1 and 2: 16 ranges; 4: 10; 8: 6; 16: 3; 24: 2; sizes past 8 want a tenth of room to spare:
     24 pairs in clusters of 15, of which exactly 24 fit, took 21 us against 16 us in clusters of 13).
     A cluster has at most 16 blocks, so a few long rows leave most of the device idle (one row of 131,072 keys:
-    128 blocks, 168 us, half of the memory's speed); where one full wave through scratch and the combine kernel
-    has a quarter more blocks than the clusters and the rows are long enough to pay for the extra kernel, the
-    wave is taken (55 ranges for that row: 97 us; measured crossovers, 8 kv heads: one row 30 k keys, two rows
-    20 k, three and four rows 16 k; five rows and more fill the device with clusters).
+    128 blocks, 168 us, half of the memory's speed); from 16 k keys on, where one wave of ranges of at least 512
+    keys through scratch and the combine kernel has a quarter more blocks than the clusters, the wave is taken
+    (measured, 8 kv heads, clusters against the wave: one row of 16 k keys 28 / 23 us, of 24 k 38 / 27, of 131 k
+    168 / 88; two rows of 16 k 36 / 32; four rows of 16 k 53 / 51, of 8 k 31 / 32; five rows and more fill the
+    device with clusters).
     Without clusters (float32, other head sizes, more pairs than clusters of two): the single wave that
     comes closest to filling the device, and when the rows alone overfill it, about four waves
     (batch 64: 4 ranges).  The reference fixes 32 splits with a floor of 64 keys
@@ -549,11 +550,11 @@ def choose_decode_splits(num_decode: int, kv_heads: int, max_seq_len: int, sm_co
     limit = max(1, min(max_splits, max_seq_len // min_keys))
     pairs, held = num_decode * kv_heads, sm_count * blocks_per_sm
     if clusters is not None:
-        full = max(1, min(64, max_seq_len // min_keys, held // pairs))      # ranges that fill the device once
+        full = max(1, min(64, max_seq_len // 512, held // pairs))           # ranges that fill the device once
         for s in range(min(limit, 16), 1, -1):
             room = clusters(s)
             if pairs <= (room if s <= 8 else 0.9 * room):
-                if full * 4 >= s * 5 and max_seq_len >= max(16384, 512 * full + 4096):
+                if full * 4 >= s * 5 and max_seq_len >= 16384:
                     return full
                 return s
     one_wave = min(limit, held // pairs)

@@ -214,10 +214,10 @@ class ModelRunner:
                                         + [max_bs]))
         # A mixer plans a captured step for the longest sequence a replay may bring, and the best plan for a long
         # sequence is a poor one for a short one (decode attention over 128 k keys wants many more key ranges than
-        # over 4 k).  So graphs also come in classes of sequence length: 16 k positions, then doubling up to the
-        # context length; a model with a context of 16 k or less has one class, as before.
+        # over 4 k).  So graphs also come in classes of sequence length: 8 k positions, then doubling up to the
+        # context length; a model with a context of 8 k or less has one class.
         self.length_classes = []
-        bound = 16384
+        bound = 8192
         while bound < self.context_len:
             self.length_classes.append(bound)
             bound *= 2
@@ -337,7 +337,7 @@ class ModelRunner:
                               max_len: Optional[int] = None) -> List[int]:
         """Captures the decode graphs for these batch sizes now (default: every bucket) instead of at the first step
         that needs each, and returns the buckets captured: for sequences of up to ``max_len`` positions, or, by
-        default, for every class of sequence length the context allows (one, up to a context of 16 k positions).
+        default, for every class of sequence length the context allows (one, up to a context of 8 k positions).
         A capture runs the model three times on padded rows that belong to no request, so it needs no live request
         and disturbs none; a server that wants no pause at the first step of each batch size calls this once after
         loading (the reference captures all of its buckets when the runner is built:

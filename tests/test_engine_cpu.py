@@ -79,8 +79,8 @@ def test_decode_splits_follow_the_clusters_that_fit():
     assert pick(32) == choose_decode_splits(32, 8, 4096) == 7 and pick(64) == 4       # no cluster fits: the wave rule
     assert choose_decode_splits(8, 8, 4096) == 6 and choose_decode_splits(0, 8, 4096) == 1
     # a few long rows: a cluster's 16 blocks leave the device idle, one full wave through scratch does not
-    assert [pick(1, ctx) for ctx in (16384, 24576, 32768, 131072)] == [16, 16, 55, 55]
-    assert [pick(2, ctx) for ctx in (16384, 24576, 131072)] == [16, 27, 27]
+    assert [pick(1, ctx) for ctx in (8192, 16384, 24576, 32768, 131072)] == [16, 32, 48, 55, 55]
+    assert [pick(2, ctx) for ctx in (12288, 16384, 24576, 131072)] == [16, 27, 27, 27]
     assert [pick(4, ctx) for ctx in (8192, 16384, 131072)] == [10, 13, 13]
     assert [pick(b, 131072) for b in (5, 6, 8, 16)] == [9, 8, 6, 3]                    # the clusters fill the device already
 

@@ -97,15 +97,15 @@ def test_decode_graphs_captured_ahead():
 
 
 def test_decode_graphs_come_in_classes_of_length():
-    """With a context past 16 k positions the captured decode steps come in classes of sequence length, each planned
+    """With a context past 8 k positions the captured decode steps come in classes of sequence length, each planned
     for its own bound: a short request decodes through the first class (key ranges merged inside clusters), one that
-    has passed 16 k positions through the next (one full wave of ranges), and both agree with the plain implementation
+    has passed 16 k positions through the third (one full wave of ranges), and both agree with the plain implementation
     on the device."""
     cfg = dict(tiny_models.MID_QWEN3, num_attention_heads=8, num_key_value_heads=8, max_position_embeddings=40000)
     with tempfile.TemporaryDirectory() as tmp:
         path, weights = model_dir(cfg, 37, tmp)
         runner = make_runner(path, dtype="bfloat16", device="cuda", page_size=64, max_tokens=20000, context_length=40000)
-        assert runner.length_classes == [16384, 32768, 40000]
+        assert runner.length_classes == [8192, 16384, 32768, 40000]
         dev_weights = {k: v.cuda() for k, v in rounded(weights, "bfloat16").items()}
         plans = {}
         for n in (300, 16500):
@@ -119,8 +119,8 @@ def test_decode_graphs_come_in_classes_of_length():
             cls = runner._length_class(n + 6)
             graph = runner._graphs[(1, cls)]
             plans[cls] = next(iter(graph.batch.plans.values())).decode
-        assert sorted(runner._graphs) == [(1, 16384), (1, 32768)] and runner.graph_steps == 12
-        assert plans[16384].arm == "cluster" and plans[32768].arm == "wave" and plans[32768].splits > plans[16384].splits
+        assert sorted(runner._graphs) == [(1, 8192), (1, 32768)] and runner.graph_steps == 12
+        assert plans[8192].arm == "cluster" and plans[32768].arm == "wave" and plans[32768].splits > plans[8192].splits
         assert runner.capture_decode_graphs([1], max_len=33000) == [1] and (1, 40000) in runner._graphs
         assert runner.cache.held_pages() == [0]
 
