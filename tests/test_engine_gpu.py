@@ -120,7 +120,9 @@ def test_decode_graphs_come_in_classes_of_length():
             graph = runner._graphs[(1, cls)]
             plans[cls] = next(iter(graph.batch.plans.values())).decode
         assert sorted(runner._graphs) == [(1, 8192), (1, 32768)] and runner.graph_steps == 12
-        assert plans[8192].arm == "cluster" and plans[32768].arm == "wave" and plans[32768].splits > plans[8192].splits
+        clusters = os.environ.get("LILY_B200_DECODE_CLUSTER") != "0"
+        assert plans[8192].arm == ("cluster" if clusters else "wave") and plans[32768].arm == "wave"
+        assert plans[32768].splits > plans[8192].splits
         assert runner.capture_decode_graphs([1], max_len=33000) == [1] and (1, 40000) in runner._graphs
         assert runner.cache.held_pages() == [0]
 
