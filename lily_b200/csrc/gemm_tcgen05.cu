@@ -493,7 +493,12 @@ template <int EPI>
 static int launch(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldc,
                   cudaStream_t stream) {
     const int sms = sm_count();
-    if (pair_enabled() && M > BM) {
+    // The pair form works on 256 rows at a time: an odd number of 128-row blocks costs it a whole block of padding,
+    // which up to some 2,000 rows is more than the pair's better rate gives back (gate/up product of Qwen3-8B, pair /
+    // one block, us: 320 rows 76.5 / 64.7, 384 78.5 / 66.5, 896 149.2 / 140.1, 1152 179.6 / 170.2; even counts: 448
+    // 80.5 / 84.7, 768 112.9 / 117.7, 1536 211.2 / 220.9).
+    const int row_blocks = (M + BM - 1) / BM;
+    if (pair_enabled() && M > BM && !(row_blocks % 2 == 1 && row_blocks <= 15)) {
         // pairs of blocks on 256 x 256 tiles
         CUtensorMap ma, mb;
         if (make_map(&ma, A, M, K, lda, BM)) return 1;

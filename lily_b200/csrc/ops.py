@@ -295,6 +295,20 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
 
 TC_MIN_ROWS = 65          # products of more rows than this go to the tcgen05 kernel when it takes the shape
+
+
+def gate_up_fused_pays(rows: int, fused_rows: int) -> bool:
+    """Whether the tcgen05 gate/up product with the SiLU*mul epilogue is the faster way for ``rows`` tokens and a
+    fused matrix of ``fused_rows`` rows (gate and up together), against the library product followed by the SiLU*mul
+    kernel.  It is, except for 129 to 256 tokens where its 256-wide tiles fill the last round of block pairs badly
+    (Qwen3-8B, 96 tiles on 74 pairs: 56 against 47 us at 192 tokens, 57 against 54 at 256; equal from 65 to 128 and
+    from 384 on, where the epilogue saves the [tokens, 2 I] intermediate)."""
+    if rows < TC_MIN_ROWS:
+        return False
+    if 128 < rows <= 256:
+        tiles, pairs = -(-fused_rows // 256), max(1, sm_count() // 2)
+        return -(-tiles // pairs) * pairs < 1.3 * tiles
+    return True
 # LILY_B200_PLAIN_GEMM=tcgen05 sends the plain bfloat16 products of 65 rows and more (QKV, output, down in prefill) to
 # this package's tcgen05 kernel too instead of the library, which is 8 to 10 % faster on them and therefore the default.
 _OWN_PLAIN_GEMM = os.environ.get("LILY_B200_PLAIN_GEMM", "") == "tcgen05"

@@ -65,7 +65,7 @@ class SwiGLU(FeedForward):
             # a few tokens: one kernel streams the fused matrix and applies SiLU*mul to its own sums
             act = ops.swiglu_skinny(x, self.w_gate_up, self.block, batch.workspace.floats("swiglu", few[0]),
                                     batch.workspace.counters("swiglu", few[1]))
-        elif self.block and x.shape[0] >= ops.TC_MIN_ROWS and ops.gemm_tc_takes(x, self.w_gate_up):
+        elif self.block and ops.gate_up_fused_pays(x.shape[0], self.w_gate_up.shape[0]) and ops.gemm_tc_takes(x, self.w_gate_up):
             act = ops.gemm_tc(x, self.w_gate_up, silu_mul_block=True)
         else:
             act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, block=self.block)

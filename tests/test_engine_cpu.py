@@ -85,6 +85,17 @@ def test_decode_splits_follow_the_clusters_that_fit():
     assert [pick(b, 131072) for b in (5, 6, 8, 16)] == [9, 8, 6, 3]                    # the clusters fill the device already
 
 
+def test_gate_up_rule_sends_badly_filled_rounds_to_the_library(monkeypatch):
+    """129 to 256 tokens are one pair of row blocks: the fused kernel pays only if its column tiles fill the block pairs."""
+    from lily_b200.csrc import ops
+    monkeypatch.setattr(ops, "sm_count", lambda: 148)
+    pays = ops.gate_up_fused_pays
+    assert not pays(64, 24576) and pays(65, 24576) and pays(128, 24576) and pays(257, 24576) and pays(2048, 24576)
+    assert not pays(129, 24576) and not pays(256, 24576)          # 96 tiles on 74 pairs: the second round is a third full
+    assert not pays(200, 28672)                                   # 112 tiles: half full
+    assert pays(200, 51200) and pays(200, 2 * 18944)              # 200 and 148 tiles: 0.9 and all of three and two rounds
+
+
 def test_both_forms_of_the_decode_step_agree(setup, monkeypatch):
     """A step in which every request brings one token may start its attention from the qkv product or run the
     norm / rotation / cache-write kernel first: same logits, same cache."""
