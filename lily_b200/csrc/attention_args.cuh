@@ -33,6 +33,8 @@ struct AttnArgs {
     const float* sin_t;
     int rd;                   // rotary width
     int write_kv;             // 0: the cache already holds this position (a layer that reads another layer's cache)
+    int stages;               // decode, tensor-core kernel: key/value tiles a block keeps in shared memory (0: the default, 2;
+                              // 3: two blocks a SM instead of three, each with two tiles in flight; head sizes up to 128)
 };
 
 }  // namespace lily

@@ -8,7 +8,7 @@
 extern "C" int lily_attention_decode_simt(const void*, const void*, void*, const int*, int, const int*, float*, int, int,
                                           int, int, int, int, int, float, int, cudaStream_t);
 extern "C" int lily_attention_decode_mma(const void*, const void*, void*, const int*, int, const int*, float*, int, int,
-                                         int, int, int, int, int, float, cudaStream_t);
+                                         int, int, int, int, int, float, int, cudaStream_t);
 extern "C" int lily_attention_mma_supports(int);
 
 // Partial (output, max, sum) of every split of the last call.  In host code this name is only a
@@ -71,7 +71,7 @@ LILY_API int lily_attention_decode_static(const void* q, const void* kv, void* o
     if (dtype == lily::kBF16 && lily_attention_mma_supports(d)) {
         // merges the splits itself: inside a cluster, or by the combine kernel behind it
         return lily_attention_decode_mma(q, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv,
-                                         d, page_size, window, scale, stream);
+                                         d, page_size, window, scale, 0, stream);
     }
     return lily_attention_decode_simt(q, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv,
                                       d, page_size, window, scale, dtype, stream);

@@ -705,7 +705,7 @@ static int launch(const AttnArgs& a, dim3 grid, int page_shift, cudaStream_t str
     size_t smem = stage_bytes<D, STAGES>(DECODE);
     // clusters pay when all of them are resident at once; over several rounds of blocks their placement costs
     // more than the combine kernel (measured: 32 requests x 8 kv heads x 7 splits 116 against 103 us)
-    if (DECODE && a.splits >= 2 && a.splits <= MAX_CLUSTER && cluster_enabled()) {
+    if (DECODE && STAGES == (D <= 128 ? LILY_DECODE_STAGES : 2) && a.splits >= 2 && a.splits <= MAX_CLUSTER && cluster_enabled()) {
         const int rows = a.nq / a.nkv < 16 ? a.nq / a.nkv : 16;
         const size_t with_recv = smem + ((size_t)a.splits * cluster_share(rows, D, a.splits) + (size_t)a.splits * 16 * 2) * sizeof(float);
         if ((long)grid.x * grid.y <= cluster_capacity<D, DECODE ? STAGES : 2>(a.splits, with_recv)) {
@@ -757,6 +757,20 @@ static int dispatch(const AttnArgs& a, dim3 grid, cudaStream_t stream, bool* mer
         return 1;
     }
     constexpr int ST = DECODE ? LILY_DECODE_STAGES : 2;
+    if (DECODE && a.stages != 0 && a.stages != ST) {
+        // a third stage: 96 KB a block at head size 128, so two blocks a SM, each with two tiles on their way while it
+        // works on a third.  Measured on a B200 (8 kv heads of 4 query heads, head size 128, one range a row, us, two
+        // stages / three): 32 rows of 4,096 keys 109 / 82 (and 96 in 7 ranges with the combine kernel), 64 rows 181 in
+        // 4 ranges / 168, 32 rows of 1,024 keys 31.6 / 24.2, 64 rows 58.7 / 48.0; 20 rows of 4,096 keys 89.5 / 78.9
+        // (61.0 in two ranges of two stages: too few blocks for three stages).  Four stages, one block a SM: slower
+        // everywhere (32 rows of 4,096 keys 122 us).
+        if (a.stages != 3 || a.d > 128) {
+            set_error("attention_mma: %d key/value stages at head size %d (2 everywhere, 3 up to head size 128)", a.stages, a.d);
+            return 1;
+        }
+        if (a.d == 64) return launch<64, DECODE, DECODE ? 3 : 2>(a, grid, page_shift, stream, merged);
+        return launch<128, DECODE, DECODE ? 3 : 2>(a, grid, page_shift, stream, merged);
+    }
     switch (a.d) {
         case 64: return launch<64, DECODE, ST>(a, grid, page_shift, stream, merged);
         case 128: return launch<128, DECODE, ST>(a, grid, page_shift, stream, merged);
@@ -828,8 +842,9 @@ LILY_API int lily_attention_decode_mma_clusters(int d, int splits, int group) {
 
 static int decode_mma(AttnArgs& a, const void* q, const void* kv, void* out, const int* block_table, int bt_stride,
                       const int* seq_lens, float* scratch, int requests, int splits, int nq, int nkv, int d, int page_size,
-                      int window, float scale, cudaStream_t stream) {
+                      int window, float scale, int stages, cudaStream_t stream) {
     if (requests == 0) return 0;
+    a.stages = stages;
     LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_decode: %d query heads over %d kv heads", nq, nkv);
     LILY_REQUIRE(splits >= 1 && splits <= 65535 && page_size > 0, "attention_decode: splits=%d page_size=%d", splits, page_size);
     LILY_REQUIRE(splits == 1 || scratch != nullptr, "attention_decode: splits need scratch");
@@ -851,13 +866,14 @@ static int decode_mma(AttnArgs& a, const void* q, const void* kv, void* out, con
 // clusters resident at once) the blocks of a (request, kv head) form a cluster and merge their results through
 // distributed shared memory; else the partial results go to `scratch` in the layout of attention_simt.cu
 // ([requests, nq, splits, d] outputs, then [requests, nq, splits, 2] (max, sum)) and the combine kernel is launched behind.
+// `stages`: 0, or the key/value tiles a block holds (3, up to head size 128: two blocks a SM, no clusters).
 LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out, const int* block_table,
                                        int bt_stride, const int* seq_lens, float* scratch, int requests, int splits,
-                                       int nq, int nkv, int d, int page_size, int window, float scale,
+                                       int nq, int nkv, int d, int page_size, int window, float scale, int stages,
                                        cudaStream_t stream) {
     AttnArgs a{};
     return decode_mma(a, q, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv, d, page_size,
-                      window, scale, stream);
+                      window, scale, stages, stream);
 }
 
 // The same from the qkv product itself ([planes][requests, (nq + 2 nkv) d], float32 partial sums or bfloat16 with
@@ -869,7 +885,8 @@ LILY_API int lily_attention_decode_mma_fused(const void* qkv, int qkv_planes, si
                                              const float* cos_t, const float* sin_t, int rd, int write_kv,
                                              void* kv, void* out, const int* block_table, int bt_stride,
                                              const int* seq_lens, float* scratch, int requests, int splits, int nq,
-                                             int nkv, int d, int page_size, int window, float scale, cudaStream_t stream) {
+                                             int nkv, int d, int page_size, int window, float scale, int stages,
+                                             cudaStream_t stream) {
     LILY_REQUIRE(qkv != nullptr && qkv_planes >= 1 && (qkv_dtype == kF32 || qkv_planes == 1),
                  "attention_decode_fused: %d planes of dtype %d", qkv_planes, qkv_dtype);
     LILY_REQUIRE(rd >= 0 && rd <= d && rd % 2 == 0, "attention_decode_fused: rotary_dim %d does not fit head_dim %d", rd, d);
@@ -880,5 +897,5 @@ LILY_API int lily_attention_decode_mma_fused(const void* qkv, int qkv_planes, si
     a.q_gain = q_gain; a.k_gain = k_gain; a.gain_f32 = gain_dtype == kF32; a.eps = eps;
     a.cos_t = cos_t; a.sin_t = sin_t; a.rd = cos_t ? rd : 0; a.write_kv = write_kv;
     return decode_mma(a, nullptr, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv, d,
-                      page_size, window, scale, stream);
+                      page_size, window, scale, stages, stream);
 }

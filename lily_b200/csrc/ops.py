@@ -40,9 +40,9 @@ _SIGNATURES = {
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
-    "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "lily_attention_decode_mma_fused": [_vp, _i, _sz, _i, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp,
-                                        _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+                                        _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_top_logprobs": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
@@ -509,9 +509,10 @@ def decode_scratch_floats(requests: int, nq: int, d: int, splits: int) -> int:
 
 def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
                      out: torch.Tensor, scratch: Optional[torch.Tensor], splits: int, nq: int, nkv: int, d: int,
-                     page_size: int, scale: float, window: Optional[int] = None) -> None:
+                     page_size: int, scale: float, window: Optional[int] = None, stages: int = 0) -> None:
     """One query token per request (rows of ``q`` [requests, nq * d]) over ``seq_lens`` cached
-    positions, keys cut into ``splits`` ranges merged through ``scratch`` (float32)."""
+    positions, keys cut into ``splits`` ranges merged through ``scratch`` (float32).  ``stages`` (tensor-core
+    kernel only): the key/value tiles a block holds, 0 for the default (``DecodePlan.stages``)."""
     _dev(q, kv_layer, block_table, seq_lens, out, scratch)
     requests = q.shape[0]
     if q.dtype != kv_layer.dtype or out.dtype != q.dtype:
@@ -523,10 +524,12 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
               _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0),
               float(scale))
     if uses_tensor_cores(q.dtype, d):
-        _call("lily_attention_decode_mma", *common, _stream())       # merges the splits itself (cluster, or combine behind)
-        if splits > 1 and requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv):
+        _call("lily_attention_decode_mma", *common, int(stages), _stream())   # merges the splits itself (cluster, or combine behind)
+        if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
             launches["count"] += 1                                   # the combine kernel, launched inside
     else:
+        if stages:
+            raise KernelError(f"attention_decode: {stages} stages are the tensor-core kernel's; {q.dtype}, head size {d} runs on CUDA cores")
         _call("lily_attention_decode_simt", *common, _dt(q), _stream())
         if splits > 1:
             launches["count"] += 1          # the combine kernel, launched inside
@@ -584,27 +587,57 @@ class DecodePlan:
     splits: int                 # key ranges per (request, kv head)
     fused: bool                 # the attention kernel starts from the qkv product (norm, rotation, cache write inside)
     scratch_floats: int         # float32 scratch the split ranges are merged through (0: merged inside clusters)
-    arm: str                    # which rule chose the splits: "cluster", "wave" or "single"
+    arm: str                    # which rule chose the splits: "cluster", "wave", "single" or "whole rows"
+    stages: int = 0             # key/value tiles a block of the tensor-core kernel holds (0: its default)
 
 
-def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, d: int, max_seq_len: int) -> DecodePlan:
+def whole_rows_pay(pairs: int, sm_count: int = 148) -> bool:
+    """Whether ``pairs`` blocks of the tensor-core kernel with three key/value stages, one block for all keys of a
+    (request, kv head), beat ranges of two stages: two such blocks fit a SM, and they keep the memory busy once three
+    quarters of those places are taken.  A last round that is less than 45 % full costs more than it saves (a block
+    alone on its SM takes about 1.2 us a tile of 64 keys whatever the others do), and past three rounds the ranges
+    of two stages are as good or better.
+    Measured on a B200, head size 128, 8 kv heads of 4 query heads, decode steps of Qwen3-8B sizes with and without
+    (same run, ms): context 4,096: 28 rows 6.66 / 6.45, 32 rows 7.02 / 6.72, 64 rows 10.51 / 10.37, 96 rows 14.36 / 14.13,
+    128 rows 17.33 / 17.60; context 1,024: 32 rows 4.67 / 4.44, 64 rows 5.85 / 5.58, 128 rows 7.93 / 7.77, 256 rows 11.94 /
+    12.22.  The kernel alone, us, against the best plan of two stages: 32 rows of 4,096 keys 82 against 96, of 1,024 keys
+    24 against 32, 64 rows of 1,024 keys 48 against 58; 20 rows of 4,096 keys 79 against 61 (too few blocks)."""
+    places = 2 * sm_count
+    if pairs < 0.75 * places or pairs > 3 * places + 0.5 * places:
+        return False
+    last = pairs % places
+    return last == 0 or last >= 0.45 * places
+
+
+def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, d: int, max_seq_len: int,
+                          even: bool = False) -> DecodePlan:
     """The plan for ``requests`` rows that bring one token each, none longer than ``max_seq_len`` positions.
     A step in which every request brings one token may hand the qkv product straight to the attention kernel
     (``fused``): every block then finishes its own queries, which costs less than a kernel of its own while all
     blocks are resident at once (three a SM) and more when they run in several rounds (measured at batch 64:
-    2 % of the step)."""
+    2 % of the step).
+    ``even``: the caller knows that the rows are about equally long (the longest at most an eighth over their
+    mean).  Then, and when ``whole_rows_pay``, a block
+    takes all keys of its row with three stages; rows of very different lengths keep their ranges, which spread a
+    long row over many blocks."""
     if requests == 0:
         return DecodePlan(1, False, 0, "single")
     group = nq // nkv
     tensor_cores = uses_tensor_cores(dtype, d)
-    room = (lambda s: decode_clusters(d, s, group)) if tensor_cores else None
-    splits = choose_decode_splits(requests, nkv, max_seq_len, sm_count=sm_count(), clusters=room)
     row_blocks = -(-group // 16)                 # the tensor-core kernel takes 16 query heads of a kv head a block
     pairs = requests * nkv * row_blocks
+    if even and tensor_cores and d <= 128 and _WHOLE_ROWS and whole_rows_pay(pairs, sm_count()):
+        return DecodePlan(1, pairs <= 2 * sm_count(), 0, "whole rows", 3)
+    room = (lambda s: decode_clusters(d, s, group)) if tensor_cores else None
+    splits = choose_decode_splits(requests, nkv, max_seq_len, sm_count=sm_count(), clusters=room)
     in_clusters = tensor_cores and splits > 1 and pairs <= decode_clusters(d, splits, group)
     fused = tensor_cores and pairs * splits <= 3 * sm_count()
     arm = "single" if splits == 1 else ("cluster" if in_clusters else "wave")
     return DecodePlan(splits, fused, decode_scratch_floats(requests, nq, d, splits), arm)
+
+
+_WHOLE_ROWS = os.environ.get("LILY_B200_DECODE_WHOLE_ROWS", "1") != "0"
+
 
 
 def prefill_tiles(prefix_lens: Sequence[int], new_lens: Sequence[int], first: int, rows: int,
@@ -623,7 +656,8 @@ def attention_decode_fused(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_
                            cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], kv_layer: torch.Tensor,
                            block_table: torch.Tensor, seq_lens: torch.Tensor, out: torch.Tensor,
                            scratch: Optional[torch.Tensor], splits: int, nq: int, nkv: int, d: int, rotary_dim: int,
-                           page_size: int, scale: float, window: Optional[int] = None, write_kv: bool = True) -> None:
+                           page_size: int, scale: float, window: Optional[int] = None, write_kv: bool = True,
+                           stages: int = 0) -> None:
     """``qk_norm_rope_write`` and ``attention_decode`` of a step in which every request brings one token, as one
     kernel: ``qkv`` is the projection's result ([requests, (nq + 2 nkv) d] in the cache's dtype, or float32 partial
     sums [splits, requests, ...]); the attention blocks finish their own query heads, and the block whose key range
@@ -645,8 +679,8 @@ def attention_decode_fused(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_
     _call("lily_attention_decode_mma_fused", _p(qkv), planes, stride, _dt(qkv), _p(q_gain), _p(k_gain),
           _dt(q_gain) if q_gain is not None else _F32, float(eps), _p(cos), _p(sin), int(rotary_dim), int(write_kv),
           _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1], _i32(seq_lens, "seq_lens"),
-          _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0), float(scale), _stream())
-    if splits > 1 and requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv):
+          _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0), float(scale), int(stages), _stream())
+    if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
         launches["count"] += 1                                       # the combine kernel, launched inside
 
 

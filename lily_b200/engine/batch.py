@@ -93,6 +93,8 @@ class StepBatch:
     h_slots: List[int]
     max_seq_len: int                                 # the longest sequence after the step (a bound, in a captured batch)
     max_decode_len: int = 0                          # the same over the requests that bring one token
+    decode_even: bool = False                        # those requests are about equally long (``rows_are_even``); a mixer
+    even_asked: bool = False                         # may plan by it, and says here that its plan depended on it
     workspace: Optional[Workspace] = None
     future_tokens: Optional[torch.Tensor] = None     # int32 [request slots]: what negative token ids stand for
     plans: Dict[Any, Any] = field(default_factory=dict)
@@ -117,6 +119,11 @@ class StepBatch:
         if key not in self.plans:
             self.plans[key] = make(self)
         return self.plans[key]
+
+
+def rows_are_even(lengths: Sequence[int]) -> bool:
+    """Whether the longest of these rows is at most an eighth longer than their mean."""
+    return len(lengths) > 0 and 8 * max(lengths) * len(lengths) <= 9 * sum(lengths)
 
 
 def order_entries(entries: Sequence[StepEntry]) -> List[int]:
@@ -194,4 +201,4 @@ def build_step_batch(entries: Sequence[StepEntry], prefix_lens: Sequence[int],
         block_tables=[parts[8 + i].view(b, w) for i, w in enumerate(widths)],
         h_new_lens=new_lens, h_prefix_lens=list(prefix_lens), h_slots=[e.slot for e in entries],
         max_seq_len=max_seq, max_decode_len=max((seq_lens[i] for i in range(num_decode)), default=0),
-        workspace=workspace)
+        decode_even=rows_are_even([seq_lens[i] for i in range(num_decode)]), workspace=workspace)

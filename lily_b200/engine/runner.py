@@ -25,7 +25,7 @@ from lily_b200.config.model_config import read_model_dir
 from lily_b200.config.registry import resolve_architecture
 from lily_b200.config.server_args import ServerArgs
 from lily_b200.engine import check
-from lily_b200.engine.batch import FUTURE, StepBatch, StepEntry, Workspace, build_step_batch, order_entries
+from lily_b200.engine.batch import FUTURE, StepBatch, StepEntry, Workspace, build_step_batch, order_entries, rows_are_even
 from lily_b200.engine.profiler import DecodeProfiler
 from lily_b200.models.assembled import AssembledModel
 from lily_b200.parts.base import BuildContext, ModelSpec
@@ -63,14 +63,16 @@ class _PinnedRing:
 
 
 class _DecodeGraph:
-    """One captured decode step for up to ``bucket`` requests of up to ``max_len`` positions.  Its metadata lives
+    """One captured decode step for up to ``bucket`` requests of up to ``max_len`` positions, about equally long
+    (``even``) or not; ``even_matters`` says whether some part planned by that.  Its metadata lives
     in one static int32 buffer that every replay overwrites; rows beyond the live requests point at slot 0 and
     page 0, which no request owns (lily/model_executor/cuda_graph_runner.py:53-65,153-186 pads
     the same way)."""
 
-    def __init__(self, runner: "ModelRunner", bucket: int, max_len: int):
+    def __init__(self, runner: "ModelRunner", bucket: int, max_len: int, even: bool = False):
         self.bucket = b = bucket
         self.max_len = max_len
+        self.even = even
         self.widths = [runner.cache.max_pages_per_request for _ in runner.cache.groups]
         self.sizes = [b, b, b, b + 1, b, b, b, b] + [b * w for w in self.widths]
         total = sum(self.sizes)
@@ -84,6 +86,7 @@ class _DecodeGraph:
             block_tables=[parts[8 + i].view(b, w) for i, w in enumerate(self.widths)],
             h_new_lens=[1] * b, h_prefix_lens=[0] * b, h_slots=[0] * b, max_seq_len=max_len,
             max_decode_len=max_len,                     # the mixers plan for the longest sequence a replay may bring
+            decode_even=even,
             workspace=Workspace(runner.device),         # scratch of its own: the graph holds its address
             future_tokens=runner.future_tokens)
         # views of the pinned copy, field by field; what never changes is written once, here
@@ -114,6 +117,7 @@ class _DecodeGraph:
             self.logits = runner.model.forward(self.batch, runner.cache)
         self.kernels = counter["count"] - before        # this package's kernels in one replay
         self._counter = counter
+        self.even_matters = self.batch.even_asked
 
     def fill(self, tokens: Sequence[int], prefix: Sequence[int], tables, slots: Sequence[int], stamps) -> None:
         """Writes a decode batch (padded to the bucket) into the pinned host copy.  The short fields are written
@@ -206,7 +210,7 @@ class ModelRunner:
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
-        self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}      # by (batch bucket, length class)
+        self._graphs: Dict[Tuple[int, int, bool], _DecodeGraph] = {}      # by (batch bucket, length class, rows even)
         self.use_graphs = self.device.type == "cuda" and not args.disable_cuda_graph and self.model.graph_safe
         max_bs = args.cuda_graph_max_bs or min(self.max_requests, 256)
         self.graph_buckets = sorted(set(args.cuda_graph_bs or
@@ -350,11 +354,22 @@ class ModelRunner:
         done = []
         for bucket in want:
             for cls in classes:
-                if (bucket, cls) not in self._graphs:
-                    self._graphs[(bucket, cls)] = _DecodeGraph(self, bucket, cls)
-                    if bucket not in done:
-                        done.append(bucket)
+                for even in (False, True):
+                    if (bucket, cls, even) not in self._graphs:
+                        self._graph_for(bucket, cls, even)
+                        if bucket not in done:
+                            done.append(bucket)
         return done
+
+    def _graph_for(self, bucket: int, cls: int, even: bool) -> _DecodeGraph:
+        """The captured step for this bucket, length class and kind of batch; one capture serves both kinds when
+        no part planned by the rows' evenness."""
+        graph = self._graphs.get((bucket, cls, even))
+        if graph is None:
+            graph = self._graphs[(bucket, cls, even)] = _DecodeGraph(self, bucket, cls, even)
+            if not graph.even_matters:
+                self._graphs[(bucket, cls, not even)] = graph
+        return graph
 
     def _decode_with_graph(self, entries: Sequence[StepEntry], bucket: int) -> torch.Tensor:
         """A step of one token per request, each wanting its logits, through a captured graph."""
@@ -376,10 +391,7 @@ class ModelRunner:
             self.cache.grow(slot, new_len)
         if check.ENABLED:
             check.check_entries(self, entries)
-        key = (bucket, self._length_class(max(n for _, n in wants)))
-        graph = self._graphs.get(key)
-        if graph is None:
-            graph = self._graphs[key] = _DecodeGraph(self, *key)
+        graph = self._graph_for(bucket, self._length_class(max(n for _, n in wants)), rows_are_even([n for _, n in wants]))
         groups = range(len(self.cache.groups))
         tables = [[self.cache.block_table(g, e.slot) for e in entries] for g in groups]
         stamps = [[self.cache.table_stamp(g, e.slot) for e in entries] for g in groups]

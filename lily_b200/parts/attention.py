@@ -121,7 +121,11 @@ class Attention(Mixer):
 
         def make(b):
             nd = b.num_decode
-            decode = ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len)
+            decode = ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
+                                               even=b.decode_even)
+            if decode != ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
+                                                   even=not b.decode_even):
+                b.even_asked = True              # a captured step with this plan serves batches of this kind only
             rows = tiles = None
             if b.num_requests > nd:
                 rows = ops.prefill_tile_rows(dtype, s.head_dim, page, b.num_tokens - nd)
@@ -144,7 +148,7 @@ class Attention(Mixer):
             out = torch.empty((nd, s.num_heads * s.head_dim), dtype=cache.data.dtype, device=cache.data.device)
             ops.attention_decode_fused(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, cache.data, table, batch.seq_lens,
                                        out, scratch, dec.splits, s.num_heads, s.num_kv_heads, s.head_dim, rotary_dim, page,
-                                       self.scale, s.window, write_kv=write_cache)
+                                       self.scale, s.window, write_kv=write_cache, stages=dec.stages)
             return ops.linear_auto(out, self.w_o, self.b_o)
         q = ops.qk_norm_rope_write(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, batch.positions,
                                    batch.token_req, table, cache.data, s.num_heads, s.num_kv_heads, s.head_dim,
@@ -152,7 +156,7 @@ class Attention(Mixer):
         out = torch.empty_like(q)       # [tokens, heads * head_dim]
         if nd:
             ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out[:nd], scratch, dec.splits,
-                                 s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window)
+                                 s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window, stages=dec.stages)
         if batch.num_requests > nd:
             tile_req, tile_start = plan.tiles
             ops.attention_prefill(q, cache.data, table, batch.cu_seqlens, batch.prefix_lens, tile_req, tile_start,

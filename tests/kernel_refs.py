@@ -14,6 +14,10 @@ import torch
 
 launches = {"count": 0}        # the kernels' Python faces count their launches here; these statements launch nothing
 TC_MIN_ROWS = 65               # as the kernels: products of this many rows and more take the fused gate/up epilogue
+
+
+def gate_up_fused_pays(rows, fused_rows):
+    return rows >= TC_MIN_ROWS
 FUSE_DECODE = True             # tests flip this to send all-decode steps through either form of the attention
 
 
@@ -194,9 +198,10 @@ class DecodePlan:
     fused: bool
     scratch_floats: int
     arm: str
+    stages: int = 0
 
 
-def plan_decode_attention(dtype, requests, nq, nkv, d, max_seq_len):
+def plan_decode_attention(dtype, requests, nq, nkv, d, max_seq_len, even=False):
     if requests == 0:
         return DecodePlan(1, False, 0, "single")
     splits = 2 if max_seq_len >= 32 else 1
@@ -240,7 +245,7 @@ def attention_prefill(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_re
 
 
 def attention_decode(q, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv, d, page_size, scale,
-                     window=None):
+                     window=None, stages=0):
     for r in range(q.shape[0]):
         n = int(seq_lens[r])
         k, v = _gather_kv(kv_layer, block_table[r], n, page_size)
@@ -249,7 +254,7 @@ def attention_decode(q, kv_layer, block_table, seq_lens, out, scratch, splits, n
 
 
 def attention_decode_fused(qkv, q_gain, k_gain, eps, cos, sin, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv,
-                           d, rotary_dim, page_size, scale, window=None, write_kv=True):
+                           d, rotary_dim, page_size, scale, window=None, write_kv=True, stages=0):
     """What the one kernel does, as the two statements it replaces: every request brings one token, at position
     seq_len - 1."""
     qkv = _sum(qkv)

@@ -85,6 +85,24 @@ def test_decode_splits_follow_the_clusters_that_fit():
     assert [pick(b, 131072) for b in (5, 6, 8, 16)] == [9, 8, 6, 3]                    # the clusters fill the device already
 
 
+def test_whole_rows_rule():
+    """One block a (request, kv head) with three stages: from three quarters of the 296 places up to three and a half
+    rounds of them, unless the last round would be less than 45 % full."""
+    from lily_b200.csrc.ops import whole_rows_pay
+    pays = lambda requests: whole_rows_pay(requests * 8)
+    assert not pays(1) and not pays(8) and not pays(20) and not pays(27)
+    assert pays(28) and pays(32) and pays(37)                      # 224 to 296 blocks: one round
+    assert not pays(38) and not pays(48) and pays(56) and pays(64) and pays(74)
+    assert not pays(80) and pays(96) and pays(128) and not pays(130) and not pays(148) and not pays(256)
+
+
+def test_rows_are_even():
+    from lily_b200.engine.batch import rows_are_even
+    assert rows_are_even([4096] * 32) and rows_are_even([4000, 4096, 4200, 3900]) and rows_are_even([7])
+    assert not rows_are_even([]) and not rows_are_even([100, 4096]) and not rows_are_even([3000] * 31 + [4096])
+    assert rows_are_even([3700] * 31 + [4096])
+
+
 def test_gate_up_rule_sends_badly_filled_rounds_to_the_library(monkeypatch):
     """129 to 256 tokens are one pair of row blocks: the fused kernel pays only if its column tiles fill the block pairs."""
     from lily_b200.csrc import ops

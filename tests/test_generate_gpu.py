@@ -206,14 +206,46 @@ def test_a_long_request_beside_short_ones_through_the_engine():
         prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], 400 + n) for n in (300, 16500, 40)]
         outs = [o["output_ids"] for o in eng.generate(prompts, SamplingParams(max_new_tokens=32, ignore_eos=True))]
         report = check_greedy(eng, prompts, outs)
-        long_classes = sorted({cls for _, cls in eng.runner._graphs})
+        long_classes = sorted({cls for _, cls, _ in eng.runner._graphs})
         short = [prompts[0], prompts[2]]                   # the short ones alone: the first class's graphs
         again = [o["output_ids"] for o in eng.generate(short, SamplingParams(max_new_tokens=32, ignore_eos=True))]
-        classes = sorted({cls for _, cls in eng.runner._graphs})
+        classes = sorted({cls for _, cls, _ in eng.runner._graphs})
     assert report["tokens"] == 3 * 32 and report["max_gap"] < 3e-2, report
     assert long_classes == [32768] and classes == [8192, 32768], (long_classes, classes)
     # beside the long request or alone, through either class of graphs: the same tokens up to near-ties
     assert sum(a != b for x, y in zip(again, (outs[0], outs[2])) for a, b in zip(x, y)) <= 2
+
+
+def test_many_rows_of_one_length_take_whole_rows_and_uneven_ones_keep_their_ranges():
+    """32 requests over 8 kv heads: while they are about equally long a block of the decode attention takes a whole
+    row (three stages, no scratch), and with one much longer request among them the rows keep their key ranges; each
+    kind of batch has its own graph, and every generated token is the prefill path's argmax either way."""
+    from lily_b200 import Engine, EngineConfig, SamplingParams
+    from lily_b200.bench.check_greedy import check_greedy
+    from lily_b200.csrc import ops
+    if not ops._WHOLE_ROWS:
+        pytest.skip("whole rows are switched off")
+    cfg = dict(tiny_models.MID_QWEN3, num_attention_heads=16, num_key_value_heads=8)
+    even = ops.plan_decode_attention(torch.bfloat16, 32, 16, 8, 128, 8192, even=True)
+    uneven = ops.plan_decode_attention(torch.bfloat16, 32, 16, 8, 128, 8192)
+    assert (even.arm, even.splits, even.stages, even.scratch_floats, even.fused) == ("whole rows", 1, 3, 0, True)
+    assert uneven.arm == "wave" and uneven.splits > 1 and uneven.stages == 0
+    with tempfile.TemporaryDirectory() as tmp:
+        path, _ = model_dir(cfg, 66, tmp)
+        eng = Engine(EngineConfig(path, dtype="bfloat16", max_total_tokens=32 * 512 + 2048, max_running_requests=32))
+        prompts = [tiny_models.random_tokens(190 + n % 7, cfg["vocab_size"], 500 + n) for n in range(32)]
+        outs = [o["output_ids"] for o in eng.generate(prompts, SamplingParams(max_new_tokens=24, ignore_eos=True))]
+        report = check_greedy(eng, prompts, outs)
+        cls = eng.runner.length_classes[0]
+        kinds = sorted(k for k in eng.runner._graphs if k[0] == 32)
+        assert kinds == [(32, cls, True)] and eng.runner._graphs[kinds[0]].even_matters, kinds
+        prompts[5] = tiny_models.random_tokens(700, cfg["vocab_size"], 77)
+        outs2 = [o["output_ids"] for o in eng.generate(prompts, SamplingParams(max_new_tokens=24, ignore_eos=True))]
+        report2 = check_greedy(eng, prompts, outs2)
+        kinds2 = sorted(k for k in eng.runner._graphs if k[0] == 32)
+    assert report["tokens"] == 32 * 24 and report["max_gap"] < 3e-2, (report, [len(o) for o in outs])
+    assert report2["tokens"] == 32 * 24 and report2["max_gap"] < 3e-2, (report2, [len(o) for o in outs2])
+    assert kinds2 == [(32, cls, False), (32, cls, True)], kinds2
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

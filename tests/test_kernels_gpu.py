@@ -422,6 +422,55 @@ def test_attention_decode(dtype, splits, nq, nkv, d, page, window):
     torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("from_projection", [False, True])
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 128, 64, None), (8, 2, 64, 16, None), (40, 2, 64, 16, 70), (5, 1, 128, 8, 300)])
+def test_attention_decode_with_three_stages(from_projection, splits, nq, nkv, d, page, window):
+    """The tensor-core kernel with three key/value tiles a block (the plan's form for many rows of about one length):
+    rows of one tile, of two, of exactly the three that are asked for ahead, and longer; a spike in every row; from
+    finished queries and from the projection, where the block with the new position writes its key and value first."""
+    o = ops()
+    dtype = torch.bfloat16
+    seqs = [1, 64, 65, 128, 129, 192, 193, 500, 1000, 3, 257]
+    cache, table, q, cu, pre = _attention_case(dtype, nq, nkv, d, page, [n - 1 for n in seqs], [1] * len(seqs), window, seed=17, spike=True)
+    seq_t = torch.tensor(seqs, device=DEV, dtype=torch.int32)
+    scratch = torch.full((max(o.decode_scratch_floats(len(seqs), nq, d, splits), 1),), float("nan"), device=DEV)
+    got, want = torch.zeros_like(q), torch.zeros_like(q)
+    if not from_projection:
+        o.attention_decode(q, cache, table, seq_t, got, scratch, splits, nq, nkv, d, page, d ** -0.5, window, stages=3)
+        ref.attention_decode(q, cache, table, seq_t, want, None, splits, nq, nkv, d, page, d ** -0.5, window)
+    else:
+        g = torch.Generator(device=DEV).manual_seed(171)
+        qkv = torch.cat([q, torch.randn(len(seqs), 2 * nkv * d, device=DEV, generator=g).to(dtype)], 1)
+        gain = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)).to(dtype)
+        cos, sin = torch.rand(1100, d // 2, device=DEV, generator=g), torch.rand(1100, d // 2, device=DEV, generator=g)
+        one, two = cache.clone(), cache.clone()
+        o.attention_decode_fused(qkv, gain, gain, 1e-6, cos, sin, one, table, seq_t, got, scratch, splits, nq, nkv, d, d, page,
+                                 d ** -0.5, window, stages=3)
+        o.attention_decode_fused(qkv, gain, gain, 1e-6, cos, sin, two, table, seq_t, want, scratch, splits, nq, nkv, d, d, page,
+                                 d ** -0.5, window)
+        ref_out = torch.zeros_like(q)
+        ref.attention_decode_fused(qkv, gain, gain, 1e-6, cos, sin, cache.clone(), table, seq_t, ref_out, None, splits, nq, nkv, d,
+                                   d, page, d ** -0.5, window)
+        assert torch.equal(one, two)                                   # the same key and value written
+        torch.testing.assert_close(want.float(), ref_out.float(), **tol(dtype))
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    with pytest.raises(Exception, match="stages"):
+        o.attention_decode(q, cache, table, seq_t, got, scratch, splits, nq, nkv, d, page, d ** -0.5, window, stages=4)
+
+
+def test_three_stages_are_refused_where_they_do_not_fit():
+    o = ops()
+    nq, nkv, d, page = 2, 2, 256, 16
+    cache, table, q, cu, pre = _attention_case(torch.bfloat16, nq, nkv, d, page, [99], [1], None, seed=3)
+    seq_t = torch.tensor([100], device=DEV, dtype=torch.int32)
+    with pytest.raises(Exception, match="stages"):
+        o.attention_decode(q, cache, table, seq_t, torch.zeros_like(q), None, 1, nq, nkv, d, page, d ** -0.5, stages=3)
+    cache, table, q, cu, pre = _attention_case(torch.float32, 4, 2, 16, 16, [99], [1], None, seed=3)
+    with pytest.raises(Exception, match="stages"):
+        o.attention_decode(q, cache, table, seq_t, torch.zeros_like(q), None, 1, 4, 2, 16, 16, 0.25, stages=3)
+
+
 @pytest.mark.parametrize("requests,longest", [(1, 40000), (2, 30000), (4, 20000)])
 def test_attention_decode_of_a_few_long_rows(requests, longest):
     """A few rows of tens of thousands of keys: the plan leaves the clusters (16 blocks a row at most) for one full
