@@ -17,6 +17,11 @@ from L2, results as achieved GB/s or TFLOP/s and as a fraction of the measured p
 Sizes default to the Qwen3-8B layer (32 query heads, 8 kv heads, head size 128, width 4096,
 intermediate 12288); every size is a flag.  ``--reps 1 --copies 1`` gives a run small enough for a
 profiler capture.
+
+The launches of a timing loop follow one another under programmatic dependent launch, so the blocks of the next
+launch fill the places that a ragged last round of this one leaves idle: a kernel that runs in one and a bit rounds
+of blocks looks better here than between other kernels of a step (decode attention of 64 rows in one block a row:
+168 us here, 179 us in the step).  What decides a plan is the step (``bench.step_profile``).
 """
 
 from __future__ import annotations
