@@ -123,7 +123,7 @@ def test_decode_graphs_come_in_classes_of_length():
         assert sorted({k[:2] for k in runner._graphs}) == [(1, 8192), (1, 32768)] and runner.graph_steps == 12
         clusters = os.environ.get("LILY_B200_DECODE_CLUSTER") != "0"
         assert plans[8192].arm == ("cluster" if clusters else "wave") and plans[32768].arm == "wave"
-        assert plans[32768].splits > plans[8192].splits
+        assert plans[32768].splits > plans[8192].splits if clusters else plans[32768].splits >= plans[8192].splits
         assert runner.capture_decode_graphs([1], max_len=33000) == [1] and (1, 40000, False) in runner._graphs
         assert runner.cache.held_pages() == [0]
 
