@@ -104,6 +104,7 @@ def main() -> int:
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--page", type=int, default=64)
     ap.add_argument("--splits", type=int, default=0, help="0: the engine's choice")
+    ap.add_argument("--stages", type=int, default=0, help="attention_decode: key/value tiles a block holds (0: the default; 3)")
     ap.add_argument("--reps", type=int, default=50)
     ap.add_argument("--copies", type=int, default=4)
     ap.add_argument("--no-graph", action="store_true", help="launch from the host each time instead of replaying a graph")
@@ -142,10 +143,11 @@ def main() -> int:
                     sin = torch.rand(a.ctx, a.d // 2, device=dev, generator=g)
                     fns.append(lambda qkv=qkv, gain=gain, cos=cos, sin=sin, cache=cache, table=table, seq=seq, out=out,
                                scratch=scratch: ops.attention_decode_fused(qkv, gain, gain, 1e-6, cos, sin, cache, table, seq, out,
-                                                                           scratch, splits, a.nq, a.nkv, a.d, a.d, a.page, a.d ** -0.5))
+                                                                           scratch, splits, a.nq, a.nkv, a.d, a.d, a.page, a.d ** -0.5,
+                                                                           stages=a.stages))
                     continue
                 fns.append(lambda q=q, cache=cache, table=table, seq=seq, out=out, scratch=scratch: ops.attention_decode(
-                    q, cache, table, seq, out, scratch, splits, a.nq, a.nkv, a.d, a.page, a.d ** -0.5))
+                    q, cache, table, seq, out, scratch, splits, a.nq, a.nkv, a.d, a.page, a.d ** -0.5, stages=a.stages))
             else:
                 q = torch.randn(a.tokens, a.nq * a.d, device=dev, generator=g).to(dt)
                 out = torch.empty_like(q)
