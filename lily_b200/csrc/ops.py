@@ -595,15 +595,15 @@ def whole_rows_pay(pairs: int, sm_count: int = 148) -> bool:
     """Whether ``pairs`` blocks of the tensor-core kernel with three key/value stages, one block for all keys of a
     (request, kv head), beat ranges of two stages: two such blocks fit a SM, and they keep the memory busy once three
     quarters of those places are taken.  A last round that is less than 45 % full costs more than it saves (a block
-    alone on its SM takes about 1.2 us a tile of 64 keys whatever the others do), and past three rounds the ranges
-    of two stages are as good or better.
+    alone on its SM takes about 1.2 us a tile of 64 keys whatever the others do), and past three and a half rounds
+    the ranges of two stages are as good or better.
     Measured on a B200, head size 128, 8 kv heads of 4 query heads, decode steps of Qwen3-8B sizes with and without
     (same run, ms): context 4,096: 28 rows 6.66 / 6.45, 32 rows 7.02 / 6.72, 64 rows 10.51 / 10.37, 96 rows 14.36 / 14.13,
     128 rows 17.33 / 17.60; context 1,024: 32 rows 4.67 / 4.44, 64 rows 5.85 / 5.58, 128 rows 7.93 / 7.77, 256 rows 11.94 /
     12.22.  The kernel alone, us, against the best plan of two stages: 32 rows of 4,096 keys 82 against 96, of 1,024 keys
     24 against 32, 64 rows of 1,024 keys 48 against 58; 20 rows of 4,096 keys 79 against 61 (too few blocks)."""
     places = 2 * sm_count
-    if pairs < 0.75 * places or pairs > 3 * places + 0.5 * places:
+    if pairs < 0.75 * places or pairs > 3.5 * places:
         return False
     last = pairs % places
     return last == 0 or last >= 0.45 * places

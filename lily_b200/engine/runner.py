@@ -341,7 +341,8 @@ class ModelRunner:
                               max_len: Optional[int] = None) -> List[int]:
         """Captures the decode graphs for these batch sizes now (default: every bucket) instead of at the first step
         that needs each, and returns the buckets captured: for sequences of up to ``max_len`` positions, or, by
-        default, for every class of sequence length the context allows (one, up to a context of 8 k positions).
+        default, for every class of sequence length the context allows (one, up to a context of 8 k positions); where
+        a part plans by whether the rows are about equally long, for both kinds of batch.
         A capture runs the model three times on padded rows that belong to no request, so it needs no live request
         and disturbs none; a server that wants no pause at the first step of each batch size calls this once after
         loading (the reference captures all of its buckets when the runner is built:
