@@ -140,6 +140,28 @@ def test_bfloat16_layouts_on_the_host(setup):
         assert float(err.max()) < 2e-2 * scale and float(err.mean()) < 3e-3 * scale
 
 
+def test_one_capture_serves_both_kinds_of_batch_unless_a_part_plans_by_evenness(setup, monkeypatch):
+    """The table of captured decode steps, with a stand-in for the capture itself: a step whose parts did not plan by
+    the rows' evenness is stored for even and for uneven batches; one whose parts did is captured once for each."""
+    from lily_b200.engine import runner as runner_module
+    cfg, weights, path = setup
+    runner = make_runner(path)
+    made = []
+
+    class Captured:
+        def __init__(self, owner, bucket, cls, even):
+            self.key, self.even_matters = (bucket, cls, even), bucket >= 32
+            made.append(self.key)
+    monkeypatch.setattr(runner_module, "_DecodeGraph", Captured)
+    small = runner._graph_for(8, 8192, True)
+    assert runner._graph_for(8, 8192, False) is small and made == [(8, 8192, True)]
+    large = runner._graph_for(32, 8192, False)
+    other = runner._graph_for(32, 8192, True)
+    assert other is not large and runner._graph_for(32, 8192, False) is large and runner._graph_for(32, 8192, True) is other
+    assert made == [(8, 8192, True), (32, 8192, False), (32, 8192, True)]
+    assert sorted(runner._graphs) == [(8, 8192, False), (8, 8192, True), (32, 8192, False), (32, 8192, True)]
+
+
 def test_step_checks_catch_what_the_kernels_would_trust(setup):
     """With LILY_B200_CHECK_STEPS on (the tests switch it on) a page id beyond the pool, a page held twice, a
     request whose length the cache manager does not know of, and a stale row are refused before anything runs."""
